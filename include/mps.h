@@ -1,0 +1,173 @@
+/*
+ * mps.h - C ABI of the B200 merge-path CSR SpMM library (libmps_b200.so).
+ *
+ * C = A * B with A sparse (CSR, int32 row_ptr / col_idx, optional values), B and C dense
+ * row-major with `dim` columns.  The reference (cag-uconn/MergePath-SpMM) has no function-level
+ * API: its boundary is the two-line `.csr` text file and the process entry point
+ * `MergePathSpMM <file> <dim> <cost> <threads_per_warp> <repeat>`.  Each entry point below names
+ * the piece of the reference program it replaces (file:line inside the reference tree).
+ *
+ * Conventions
+ *   - every function returns an mps_status (0 = ok, negative = error); nothing throws, nothing
+ *     calls exit(); mps_last_error() gives the message of the calling thread's last failure;
+ *   - device pointers are caller-owned; a plan owns only its scratch (tile coordinates, carry
+ *     rows, status word) on the device that was current when it was created;
+ *   - `stream` is a cudaStream_t passed as void* (NULL = legacy default stream);
+ *   - launches are asynchronous; mps_plan_sync_check() waits and reports device-side errors;
+ *   - there is no CPU fallback: without a usable CUDA device the compute calls fail with
+ *     MPS_ERR_CUDA.
+ */
+#ifndef MPS_B200_H
+#define MPS_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+/* Every entry point is exported from a library otherwise built with hidden visibility. */
+#define MPS_API __attribute__((visibility("default")))
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+    MPS_OK = 0,
+    MPS_ERR_ARG = -1,         /* NULL pointer, negative size, cost < 1, dim < 1 ...            */
+    MPS_ERR_IO = -2,          /* file missing / unreadable / short write                        */
+    MPS_ERR_FORMAT = -3,      /* .csr text does not follow the grammar                          */
+    MPS_ERR_CUDA = -4,        /* a CUDA runtime call failed (message has the CUDA error string) */
+    MPS_ERR_UNSUPPORTED = -5, /* shape outside what the kernels cover (e.g. N+1+nnz >= 2^31)    */
+    MPS_ERR_NOMEM = -6,
+    MPS_ERR_DEVICE = -7,      /* a kernel reported a bounded wait that ran out                  */
+    MPS_ERR_ALIGN = -8,       /* a device pointer is not aligned to its element size            */
+    MPS_ERR_STATE = -9        /* e.g. mps_spmm before mps_plan_partition                        */
+} mps_status;
+
+typedef enum { MPS_F32 = 0, MPS_F16 = 1 } mps_dtype;
+
+MPS_API const char *mps_last_error(void);
+MPS_API const char *mps_version(void);
+
+/* ------------------------------------------------------------------ .csr files (host) ---- */
+
+/* A graph as the reference's loader leaves it in memory (src/MergePathSpMM.cu:26-35,143-173):
+ * N = cells(line 1) - 1, nnz = last cell of line 1.  Arrays are malloc'ed by the library. */
+typedef struct {
+    int32_t n_rows;
+    int32_t nnz;
+    int32_t *row_ptr; /* n_rows + 1 */
+    int32_t *col_idx; /* nnz        */
+} mps_csr;
+
+/* Replaces the two-pass getline/stringstream/stoi loader (src/MergePathSpMM.cu:119-173).
+ * Same grammar: line 1 = row_ptr, line 2 = col_idx, decimal integers separated by ',', trailing
+ * ',' optional, final newline optional, blanks before a number allowed, '\r' rejected.
+ * Unlike the reference a missing file, a malformed cell, a cell count that disagrees with nnz, a
+ * decreasing row_ptr or a column index outside [0, n_rows) is an error.  n_threads <= 0 picks
+ * the hardware concurrency. */
+MPS_API int mps_csr_load(const char *path, int n_threads, mps_csr *out);
+MPS_API void mps_csr_free(mps_csr *csr);
+
+/* Replaces the writers scripts/npz_to_csr.py:21-28 and scripts/fetch_dataset.py:14-21:
+ * every cell followed by ',', one '\n' between the lines, none at the end. */
+MPS_API int mps_csr_save(const char *path, int32_t n_rows, const int32_t *row_ptr, const int32_t *col_idx);
+
+/* Binary sidecar (no reference counterpart; the text format cannot carry values and a
+ * 10^9-nnz graph is ~10 GB of text): 32-byte header, then raw row_ptr, col_idx and, when
+ * val_bytes != 0, values of that element size (4 = fp32, 2 = fp16).  Load mallocs the arrays. */
+MPS_API int mps_csr_save_bin(const char *path, int32_t n_rows, const int32_t *row_ptr, const int32_t *col_idx,
+                     const void *val, int val_bytes);
+MPS_API int mps_csr_load_bin(const char *path, mps_csr *out, void **val, int *val_bytes);
+
+/* ------------------------------------------------------------------ partition ------------ */
+
+/* Chunk count and items per chunk for a cost, exactly the reference's integer arithmetic:
+ * P = max(1024, (N+1+nnz-1)/cost)  (src/MergePathSpMM.cu:138-139),
+ * ipt = ceil((N+1+nnz)/P)          (src/MergePathSpMM.cu:327-328). */
+MPS_API int mps_chunk_count(int32_t n_rows, int32_t nnz, int32_t cost, int32_t *n_chunks, int32_t *items_per_chunk);
+
+/* Replaces MergePathSearch called over all chunk boundaries (src/MergePathSpMM.cu:280-297,
+ * 330-334), on the device: d_xy receives n_chunks + 1 interleaved (x, y) pairs for the diagonals
+ * min(ipt * t, N+1+nnz), t = 0..n_chunks, in the reference's convention (x counts row_ptr
+ * entries including row_ptr[0], y counts non-zeros).  Bit-exact with the reference. */
+MPS_API int mps_partition_device(const int32_t *d_row_ptr, int32_t n_rows, int32_t nnz, int32_t n_chunks,
+                         int32_t *d_xy, void *stream);
+
+/* Replaces generate_mp_sched (src/MergePathSpMM.cu:300-385), on the device: the six int arrays
+ * of n_chunks entries each, written to d_six in the reference's return order (feature_start,
+ * feature_start_num, feature_end, feature_end_num, start_row, end_row), bit-exact including the
+ * zero-sentinel behaviour, so that they can be handed to the reference's own kernels. */
+MPS_API int mps_schedule_device(const int32_t *d_row_ptr, int32_t n_rows, int32_t nnz, int32_t n_chunks,
+                        int32_t *d_six, void *stream);
+
+/* ------------------------------------------------------------------ SpMM plan ------------ */
+
+typedef struct mps_plan mps_plan;
+
+/* Replaces the set-up part of main() (src/MergePathSpMM.cu:138-139,192-228): fixes N, nnz, dim,
+ * element type and the reference's two tuning arguments.  `cost` = merge items per chunk as in
+ * the reference.  `threads_per_warp` is accepted for command-line compatibility; where the
+ * reference exits when it exceeds 32/dim (:224-228) the value is clamped instead (the number of
+ * chunks a warp walks at once is fixed by the 128-bit row loads: 128/dim chunks for fp32).
+ * Allocates the plan's device scratch on the current device. */
+MPS_API int mps_plan_create(int32_t n_rows, int32_t nnz, int32_t dim, int dtype, int32_t cost,
+                    int32_t threads_per_warp, mps_plan **out);
+MPS_API void mps_plan_destroy(mps_plan *plan);
+
+/* Optional tuning before mps_plan_partition: chunks per tile (0 = automatic), gather unroll
+ * (4 or 8, 0 = automatic), staging through bulk async copies (1, default) or plain loads (0). */
+MPS_API int mps_plan_tune(mps_plan *plan, int32_t chunks_per_tile, int32_t unroll, int32_t bulk_staging);
+
+/* Replaces the call of generate_mp_sched and the eleven uploads that follow it
+ * (src/MergePathSpMM.cu:192-220): searches the tile boundaries on the device and lists the rows
+ * whose carries span many tiles.  Must be called once per row_ptr before mps_spmm; synchronises
+ * the stream once (it reads back one counter). */
+MPS_API int mps_plan_partition(mps_plan *plan, const int32_t *d_row_ptr, void *stream);
+
+/* Replaces one iteration of the launch loops (src/MergePathSpMM.cu:230-243, 249-263) and the
+ * kernels spmm_merge_path / spmm_merge_path_64 (:388-574; fp16: MergePathSpMM_fp16.cu:389-575).
+ * d_val == NULL means every stored value is 1 (the .csr file has no values).  For MPS_F16 plans
+ * val, B and C hold IEEE fp16 and all sums are kept in fp32 until the single rounding of C.
+ * Every row of C is written exactly once per call - nothing has to be zeroed and repeated calls
+ * do not accumulate (the reference's atomics do, :204,231).  Rows split across chunks are
+ * combined in a fixed order, so results are bitwise reproducible. */
+MPS_API int mps_spmm(mps_plan *plan, const int32_t *d_row_ptr, const int32_t *d_col_idx, const void *d_val,
+             const void *d_B, void *d_C, void *stream);
+
+/* Waits for the stream and returns MPS_ERR_DEVICE if any kernel of this plan gave up a wait. */
+MPS_API int mps_plan_sync_check(mps_plan *plan, void *stream);
+
+/* Facts about a plan: what[0]=n_chunks what[1]=items_per_chunk what[2]=chunks_per_tile
+ * what[3]=n_tiles what[4]=lanes_per_chunk what[5]=elements_per_lane what[6]=unroll
+ * what[7]=shared_bytes_per_block what[8]=long_rows what[9]=effective threads_per_warp
+ * what[10]=kernels per mps_spmm call what[11]=long_chain threshold. */
+MPS_API int mps_plan_info(const mps_plan *plan, int64_t what[12]);
+
+/* Algorithmic bytes of one SpMM: 4(N+1) + nnz(4 + s_val) + nnz*dim*s + N*dim*s, s = 4 or 2;
+ * has_val = 0 drops the value term. */
+MPS_API int64_t mps_algorithmic_bytes(int32_t n_rows, int32_t nnz, int32_t dim, int dtype, int has_val);
+
+/* ------------------------------------------------------------------ host-buffer call ----- */
+
+/* The whole reference program body on HOST buffers (src/MergePathSpMM.cu:187-267): upload A and
+ * B, partition, multiply once, download C.  Device buffers live in a per-thread workspace that
+ * only grows, so repeated calls do not reallocate.  Blocking. */
+MPS_API int mps_spmm_host(int32_t n_rows, int32_t nnz, int32_t dim, int dtype, int32_t cost,
+                  int32_t threads_per_warp, const int32_t *row_ptr, const int32_t *col_idx,
+                  const void *val, const void *B, void *C);
+MPS_API void mps_host_workspace_release(void);
+
+/* ------------------------------------------------------------------ multi-GPU slabs ------ */
+
+/* Row slabs of equal non-zero count for n_slabs devices (no reference counterpart - the
+ * reference is single-GPU): bounds[g] = first row whose start offset is >= g*nnz/n_slabs,
+ * bounds[0] = 0, bounds[n_slabs] = n_rows.  Host row_ptr. */
+MPS_API int mps_slab_bounds(const int32_t *row_ptr, int32_t n_rows, int32_t n_slabs, int32_t *bounds);
+
+/* Slab g of a host CSR with row_ptr rebased to 0: writes row1 - row0 + 1 entries. */
+MPS_API int mps_slab_rebase(const int32_t *row_ptr, int32_t row0, int32_t row1, int32_t *out_row_ptr);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MPS_B200_H */

@@ -1,0 +1,229 @@
+"""B200-native merge-path CSR SpMM: host-side mirror of the reference program's interface.
+
+The reference (cag-uconn/MergePath-SpMM) is a command-line program: load `<graph>.csr`, build the
+merge-path schedule for `<cost>`, multiply `<repeat>` times (src/MergePathSpMM.cu:110-277).  The
+same steps are exposed here as functions over torch CUDA tensors (torch only owns the memory and
+the stream), each a thin wrapper of one C-ABI entry point of libmps_b200.so (include/mps.h):
+
+    load_csr / save_csr            the `.csr` text format                (ref :119-173)
+    chunk_count                    P and items per chunk for a cost      (ref :138-139, :327-328)
+    partition_device               MergePathSearch over all boundaries   (ref :280-297)
+    schedule_device                generate_mp_sched's six arrays        (ref :300-385)
+    Plan / spmm                    the kernels and their launch loops    (ref :223-264, :388-574)
+    spmm_host                      the whole program body on host arrays (ref :187-267)
+    slab_bounds                    nnz-balanced row slabs for several GPUs (new)
+
+Nothing here computes on the CPU; without the CUDA library these calls raise.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import capi
+from .capi import F16, F32, MpsError  # noqa: F401
+
+try:
+    import torch
+except Exception:  # pragma: no cover
+    torch = None
+
+__all__ = ["Plan", "spmm", "spmm_host", "partition_device", "schedule_device", "chunk_count", "load_csr", "save_csr",
+           "save_csr_bin", "load_csr_bin", "slab_bounds", "slab_rebase", "algorithmic_bytes", "F32", "F16", "MpsError"]
+
+
+def _stream_ptr(stream=None):
+    if stream is None:
+        stream = torch.cuda.current_stream()
+    return C.c_void_p(stream.cuda_stream)
+
+
+def _dev_ptr(t):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def _need_cuda(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise ValueError("expected CUDA tensors (there is no CPU path)")
+        if t is not None and not t.is_contiguous():
+            raise ValueError("expected contiguous tensors")
+
+
+def chunk_count(n_rows: int, nnz: int, cost: int) -> tuple[int, int]:
+    p, ipt = C.c_int32(), C.c_int32()
+    capi.check(capi.lib().mps_chunk_count(n_rows, nnz, cost, C.byref(p), C.byref(ipt)))
+    return p.value, ipt.value
+
+
+def algorithmic_bytes(n_rows: int, nnz: int, dim: int, dtype=F32, has_val: bool = True) -> int:
+    return int(capi.lib().mps_algorithmic_bytes(n_rows, nnz, dim, dtype, int(has_val)))
+
+
+def partition_device(row_ptr, n_chunks: int, stream=None):
+    """(n_chunks+1, 2) int32 CUDA tensor of (x, y) in the reference's convention."""
+    _need_cuda(row_ptr)
+    n_rows = row_ptr.numel() - 1
+    nnz = int(row_ptr[-1].item())
+    out = torch.empty((n_chunks + 1, 2), dtype=torch.int32, device=row_ptr.device)
+    with torch.cuda.device(row_ptr.device):
+        capi.check(capi.lib().mps_partition_device(_dev_ptr(row_ptr), n_rows, nnz, n_chunks, _dev_ptr(out), _stream_ptr(stream)))
+    return out
+
+
+def schedule_device(row_ptr, n_chunks: int, stream=None):
+    """(6, n_chunks) int32 CUDA tensor in generate_mp_sched's return order."""
+    _need_cuda(row_ptr)
+    n_rows = row_ptr.numel() - 1
+    nnz = int(row_ptr[-1].item())
+    out = torch.empty((6, n_chunks), dtype=torch.int32, device=row_ptr.device)
+    with torch.cuda.device(row_ptr.device):
+        capi.check(capi.lib().mps_schedule_device(_dev_ptr(row_ptr), n_rows, nnz, n_chunks, _dev_ptr(out), _stream_ptr(stream)))
+    return out
+
+
+class Plan:
+    """Shape-bound plan: create -> (tune) -> partition(row_ptr) -> spmm(...) any number of times."""
+
+    INFO = ("n_chunks", "items_per_chunk", "chunks_per_tile", "n_tiles", "lanes_per_chunk", "elements_per_lane", "unroll",
+            "shared_bytes", "long_rows", "threads_per_warp", "kernels_per_call", "long_chain")
+
+    def __init__(self, n_rows: int, nnz: int, dim: int, dtype=F32, cost: int = 8, threads_per_warp: int = 1, device=None):
+        self._h = C.c_void_p()
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        self.n_rows, self.nnz, self.dim, self.dtype, self.cost = n_rows, nnz, dim, dtype, cost
+        with torch.cuda.device(self.device):
+            capi.check(capi.lib().mps_plan_create(n_rows, nnz, dim, dtype, cost, threads_per_warp, C.byref(self._h)))
+
+    def close(self):
+        if getattr(self, "_h", None) is not None and self._h:
+            capi.lib().mps_plan_destroy(self._h)
+            self._h = C.c_void_p()
+
+    __del__ = close
+
+    def tune(self, chunks_per_tile: int = 0, unroll: int = 0, bulk_staging: bool = True):
+        with torch.cuda.device(self.device):
+            capi.check(capi.lib().mps_plan_tune(self._h, chunks_per_tile, unroll, int(bulk_staging)))
+        return self
+
+    def partition(self, row_ptr, stream=None):
+        _need_cuda(row_ptr)
+        with torch.cuda.device(self.device):
+            capi.check(capi.lib().mps_plan_partition(self._h, _dev_ptr(row_ptr), _stream_ptr(stream)))
+        return self
+
+    def spmm(self, row_ptr, col_idx, val, B, out=None, stream=None):
+        _need_cuda(row_ptr, col_idx, val, B, out)
+        if out is None:
+            out = torch.empty((self.n_rows, self.dim), dtype=B.dtype, device=B.device)
+        with torch.cuda.device(self.device):
+            capi.check(capi.lib().mps_spmm(self._h, _dev_ptr(row_ptr), _dev_ptr(col_idx), _dev_ptr(val), _dev_ptr(B), _dev_ptr(out),
+                                           _stream_ptr(stream)))
+        return out
+
+    def sync_check(self, stream=None):
+        with torch.cuda.device(self.device):
+            capi.check(capi.lib().mps_plan_sync_check(self._h, _stream_ptr(stream)))
+
+    def info(self) -> dict:
+        arr = (C.c_int64 * 12)()
+        capi.check(capi.lib().mps_plan_info(self._h, arr))
+        return dict(zip(self.INFO, [int(v) for v in arr]))
+
+
+def spmm(row_ptr, col_idx, val, B, cost: int = 8, threads_per_warp: int = 1):
+    """One-shot C = A @ B on CUDA tensors (plans, partitions, multiplies, checks)."""
+    n_rows = row_ptr.numel() - 1
+    dtype = F16 if B.dtype == torch.float16 else F32
+    plan = Plan(n_rows, col_idx.numel(), B.shape[1], dtype, cost, threads_per_warp, device=B.device)
+    try:
+        plan.partition(row_ptr)
+        out = plan.spmm(row_ptr, col_idx, val, B)
+        plan.sync_check()
+    finally:
+        plan.close()
+    return out
+
+
+def spmm_host(row_ptr, col_idx, val, B, out=None, cost: int = 8, threads_per_warp: int = 1):
+    """The reference program's body on host (numpy or pinned torch CPU) arrays: upload, partition,
+    multiply, download.  Returns C as a numpy array (or fills `out`)."""
+    def host_ptr(a):
+        if a is None:
+            return None
+        if torch is not None and isinstance(a, torch.Tensor):
+            return C.c_void_p(a.data_ptr())
+        return a.ctypes.data_as(C.c_void_p)
+
+    n_rows = int(row_ptr.shape[0]) - 1
+    nnz = int(col_idx.shape[0])
+    dim = int(B.shape[1])
+    is_half = str(B.dtype).endswith("float16")
+    if out is None:
+        out = np.empty((n_rows, dim), np.float16 if is_half else np.float32)
+    capi.check(capi.lib().mps_spmm_host(n_rows, nnz, dim, F16 if is_half else F32, cost, threads_per_warp, host_ptr(row_ptr),
+                                        host_ptr(col_idx), host_ptr(val), host_ptr(B), host_ptr(out)))
+    return out
+
+
+def load_csr(path: str, threads: int = 0):
+    """Reads a `.csr` text file; returns (row_ptr, col_idx) as int32 numpy arrays."""
+    csr = capi.Csr()
+    capi.check(capi.lib().mps_csr_load(path.encode(), threads, C.byref(csr)))
+    try:
+        rp = np.ctypeslib.as_array(csr.row_ptr, shape=(csr.n_rows + 1,)).copy()
+        col = np.ctypeslib.as_array(csr.col_idx, shape=(csr.nnz,)).copy() if csr.nnz else np.empty(0, np.int32)
+    finally:
+        capi.lib().mps_csr_free(C.byref(csr))
+    return rp, col
+
+
+def save_csr(path: str, row_ptr, col_idx) -> None:
+    rp = np.ascontiguousarray(row_ptr, np.int32)
+    col = np.ascontiguousarray(col_idx, np.int32)
+    capi.check(capi.lib().mps_csr_save(path.encode(), len(rp) - 1, rp.ctypes.data_as(C.c_void_p), col.ctypes.data_as(C.c_void_p)))
+
+
+def save_csr_bin(path: str, row_ptr, col_idx, val=None) -> None:
+    rp = np.ascontiguousarray(row_ptr, np.int32)
+    col = np.ascontiguousarray(col_idx, np.int32)
+    vb, vp = 0, None
+    if val is not None:
+        val = np.ascontiguousarray(val)
+        vb, vp = val.dtype.itemsize, val.ctypes.data_as(C.c_void_p)
+    capi.check(capi.lib().mps_csr_save_bin(path.encode(), len(rp) - 1, rp.ctypes.data_as(C.c_void_p), col.ctypes.data_as(C.c_void_p), vp, vb))
+
+
+def load_csr_bin(path: str):
+    csr, val, vb = capi.Csr(), C.c_void_p(), C.c_int()
+    capi.check(capi.lib().mps_csr_load_bin(path.encode(), C.byref(csr), C.byref(val), C.byref(vb)))
+    libc = C.CDLL(None)
+    libc.free.argtypes = [C.c_void_p]
+    try:
+        rp = np.ctypeslib.as_array(csr.row_ptr, shape=(csr.n_rows + 1,)).copy()
+        col = np.ctypeslib.as_array(csr.col_idx, shape=(csr.nnz,)).copy() if csr.nnz else np.empty(0, np.int32)
+        v = None
+        if val.value and vb.value:
+            dt = np.float16 if vb.value == 2 else np.float32
+            v = np.frombuffer((C.c_char * (vb.value * csr.nnz)).from_address(val.value), dtype=dt).copy()
+    finally:
+        capi.lib().mps_csr_free(C.byref(csr))
+        if val.value:
+            libc.free(val)
+    return rp, col, v
+
+
+def slab_bounds(row_ptr, n_slabs: int):
+    rp = np.ascontiguousarray(row_ptr, np.int32)
+    b = np.empty(n_slabs + 1, np.int32)
+    capi.check(capi.lib().mps_slab_bounds(rp.ctypes.data_as(C.c_void_p), len(rp) - 1, n_slabs, b.ctypes.data_as(C.c_void_p)))
+    return b
+
+
+def slab_rebase(row_ptr, row0: int, row1: int):
+    rp = np.ascontiguousarray(row_ptr, np.int32)
+    out = np.empty(row1 - row0 + 1, np.int32)
+    capi.check(capi.lib().mps_slab_rebase(rp.ctypes.data_as(C.c_void_p), row0, row1, out.ctypes.data_as(C.c_void_p)))
+    return out

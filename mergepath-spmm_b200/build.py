@@ -1,0 +1,66 @@
+"""In-tree build of libmps_b200.so and the MergePathSpMM command-line program (nvcc, sm_100a only)."""
+from __future__ import annotations
+
+import os
+import shutil
+import subprocess
+
+PKG = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(PKG)
+CSRC = os.path.join(PKG, "csrc")
+LIBDIR = os.path.join(PKG, "lib")
+LIB = os.path.join(LIBDIR, "libmps_b200.so")
+CLI = os.path.join(LIBDIR, "MergePathSpMM")
+
+ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
+COMMON = ["-O3", "-std=c++17", "-lineinfo", "-I" + os.path.join(ROOT, "include"), "-I" + CSRC]
+
+
+def _nvcc() -> str:
+    exe = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(exe):
+        raise RuntimeError("nvcc not found; libmps_b200.so cannot be built")
+    return exe
+
+
+def _newer(target: str, sources) -> bool:
+    if not os.path.exists(target):
+        return False
+    t = os.path.getmtime(target)
+    return all(os.path.getmtime(s) <= t for s in sources)
+
+
+def _sources(names):
+    return [os.path.join(CSRC, n) for n in names]
+
+
+def build_library(force: bool = False, verbose: bool = False) -> str:
+    srcs = _sources(["mps_api.cu", "csr_io.cpp"])
+    deps = srcs + _sources(["mps_kernels.cuh", "mps_internal.h"]) + [os.path.join(ROOT, "include", "mps.h")]
+    if not force and _newer(LIB, deps):
+        return LIB
+    os.makedirs(LIBDIR, exist_ok=True)
+    cmd = [_nvcc()] + ARCH + COMMON + ["-shared", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
+                                      "-Xcompiler", "-pthread", "-o", LIB] + srcs
+    if verbose:
+        cmd.insert(1, "-Xptxas=-v")
+    subprocess.run(cmd, check=True)
+    return LIB
+
+
+def build_cli(force: bool = False) -> str:
+    src = os.path.join(CSRC, "bench_main.cpp")
+    if not os.path.exists(src):
+        return ""
+    build_library(force)
+    if not force and _newer(CLI, [src, LIB]):
+        return CLI
+    cmd = [_nvcc()] + ARCH + COMMON + ["-Xcompiler", "-pthread", "-o", CLI, src, "-L" + LIBDIR, "-lmps_b200",
+                                      "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN"]
+    subprocess.run(cmd, check=True)
+    return CLI
+
+
+if __name__ == "__main__":
+    print(build_library(force=True, verbose=False))
+    print(build_cli(force=True))

@@ -1,0 +1,80 @@
+"""ctypes bindings of libmps_b200.so - one Python function per symbol of include/mps.h.
+
+There is no CPU fallback: if the shared library cannot be loaded (and cannot be built with nvcc)
+importing this module's `lib()` raises, and every compute call needs a CUDA device.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+from . import build as _build
+
+OK = 0
+ERR_ARG, ERR_IO, ERR_FORMAT, ERR_CUDA, ERR_UNSUPPORTED, ERR_NOMEM, ERR_DEVICE, ERR_ALIGN, ERR_STATE = range(-1, -10, -1)
+F32, F16 = 0, 1
+
+SYMBOLS = [
+    "mps_last_error", "mps_version", "mps_csr_load", "mps_csr_free", "mps_csr_save", "mps_csr_save_bin",
+    "mps_csr_load_bin", "mps_chunk_count", "mps_partition_device", "mps_schedule_device", "mps_plan_create",
+    "mps_plan_destroy", "mps_plan_tune", "mps_plan_partition", "mps_spmm", "mps_plan_sync_check", "mps_plan_info",
+    "mps_algorithmic_bytes", "mps_spmm_host", "mps_host_workspace_release", "mps_slab_bounds", "mps_slab_rebase",
+]
+
+
+class MpsError(RuntimeError):
+    def __init__(self, code: int, message: str):
+        super().__init__(f"mps error {code}: {message}")
+        self.code = code
+
+
+class Csr(C.Structure):
+    _fields_ = [("n_rows", C.c_int32), ("nnz", C.c_int32),
+                ("row_ptr", C.POINTER(C.c_int32)), ("col_idx", C.POINTER(C.c_int32))]
+
+
+_lib = None
+
+
+def lib():
+    """The loaded library; builds it in-tree first if the .so is absent."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    path = _build.LIB
+    if not os.path.exists(path):
+        path = _build.build_library()
+    L = C.CDLL(path)
+    vp, i32, i64 = C.c_void_p, C.c_int32, C.c_int64
+    L.mps_last_error.restype = C.c_char_p
+    L.mps_version.restype = C.c_char_p
+    L.mps_csr_load.argtypes = [C.c_char_p, C.c_int, C.POINTER(Csr)]
+    L.mps_csr_free.argtypes = [C.POINTER(Csr)]
+    L.mps_csr_free.restype = None
+    L.mps_csr_save.argtypes = [C.c_char_p, i32, vp, vp]
+    L.mps_csr_save_bin.argtypes = [C.c_char_p, i32, vp, vp, vp, C.c_int]
+    L.mps_csr_load_bin.argtypes = [C.c_char_p, C.POINTER(Csr), C.POINTER(vp), C.POINTER(C.c_int)]
+    L.mps_chunk_count.argtypes = [i32, i32, i32, C.POINTER(i32), C.POINTER(i32)]
+    L.mps_partition_device.argtypes = [vp, i32, i32, i32, vp, vp]
+    L.mps_schedule_device.argtypes = [vp, i32, i32, i32, vp, vp]
+    L.mps_plan_create.argtypes = [i32, i32, i32, C.c_int, i32, i32, C.POINTER(vp)]
+    L.mps_plan_destroy.argtypes = [vp]
+    L.mps_plan_destroy.restype = None
+    L.mps_plan_tune.argtypes = [vp, i32, i32, i32]
+    L.mps_plan_partition.argtypes = [vp, vp, vp]
+    L.mps_spmm.argtypes = [vp, vp, vp, vp, vp, vp, vp]
+    L.mps_plan_sync_check.argtypes = [vp, vp]
+    L.mps_plan_info.argtypes = [vp, C.POINTER(i64)]
+    L.mps_algorithmic_bytes.argtypes = [i32, i32, i32, C.c_int, C.c_int]
+    L.mps_algorithmic_bytes.restype = i64
+    L.mps_spmm_host.argtypes = [i32, i32, i32, C.c_int, i32, i32, vp, vp, vp, vp, vp]
+    L.mps_host_workspace_release.restype = None
+    L.mps_slab_bounds.argtypes = [vp, i32, i32, vp]
+    L.mps_slab_rebase.argtypes = [vp, i32, i32, vp]
+    _lib = L
+    return L
+
+
+def check(rc: int) -> None:
+    if rc != OK:
+        raise MpsError(rc, lib().mps_last_error().decode("utf-8", "replace"))

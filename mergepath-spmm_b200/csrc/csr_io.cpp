@@ -1,0 +1,302 @@
+// `.csr` text files and the binary sidecar (host only).
+//
+// Text grammar = what the reference's loader accepts and its writers emit
+// (src/MergePathSpMM.cu:130-173; scripts/npz_to_csr.py:21-28): two lines of decimal integers
+// separated by ','.  The reference makes two passes with getline/stringstream/stoi on one thread
+// and holds two copies of each line; here the file is mapped once and the cells of a line are
+// counted and parsed by all cores in place.
+#include "mps.h"
+
+#include <fcntl.h>
+#include <sys/mman.h>
+#include <sys/stat.h>
+#include <unistd.h>
+
+#include <atomic>
+#include <cerrno>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <string>
+#include <thread>
+#include <vector>
+
+#include "mps_internal.h"
+
+using mps::fail;
+
+namespace {
+
+struct Span { const char *b, *e; };
+
+int worker_count(int requested, size_t bytes) {
+    int n = requested > 0 ? requested : (int)std::thread::hardware_concurrency();
+    if (n < 1) n = 1;
+    const size_t by_size = bytes / (1 << 16) + 1;  // no point in a thread per few KB
+    if ((size_t)n > by_size) n = (int)by_size;
+    return n;
+}
+
+// Cuts [b,e) into n pieces that end just after a ','.
+std::vector<Span> cut_at_commas(const char *b, const char *e, int n) {
+    std::vector<Span> out;
+    const char *at = b;
+    for (int i = 1; i <= n && at < e; ++i) {
+        const char *stop = i == n ? e : b + (size_t)(e - b) * i / n;
+        if (stop < at) stop = at;
+        if (i != n) {
+            const void *c = memchr(stop, ',', (size_t)(e - stop));
+            stop = c ? (const char *)c + 1 : e;
+        }
+        if (stop > at) out.push_back({at, stop});
+        at = stop;
+    }
+    return out;
+}
+
+// A piece holds one cell per ',' plus one more if text follows its last ','.
+size_t count_cells(Span s) {
+    size_t n = 0;
+    const char *p = s.b;
+    while (p < s.e) {
+        const void *c = memchr(p, ',', (size_t)(s.e - p));
+        if (!c) { ++n; break; }
+        ++n;
+        p = (const char *)c + 1;
+    }
+    return n;
+}
+
+// Parses the cells of a piece into out[]; returns the offset of the first bad byte or -1.
+long parse_cells(Span s, int32_t *out) {
+    const char *p = s.b;
+    while (p < s.e) {
+        while (p < s.e && (*p == ' ' || *p == '\t')) ++p;
+        bool neg = false;
+        if (p < s.e && (*p == '-' || *p == '+')) { neg = *p == '-'; ++p; }
+        if (p >= s.e || *p < '0' || *p > '9') return (long)(p - s.b);
+        int64_t v = 0;
+        while (p < s.e && *p >= '0' && *p <= '9') {
+            v = v * 10 + (*p - '0');
+            if (v > (int64_t)INT32_MAX + 1) return (long)(p - s.b);
+            ++p;
+        }
+        if (neg) v = -v;
+        if (v > INT32_MAX || v < INT32_MIN) return (long)(p - s.b);
+        *out++ = (int32_t)v;
+        if (p < s.e) {
+            if (*p != ',') return (long)(p - s.b);
+            ++p;
+        }
+    }
+    return -1;
+}
+
+// One line -> malloc'ed int32 array.
+int parse_line(const char *b, const char *e, int n_threads, int32_t **out, size_t *count, const char *what) {
+    std::vector<Span> pieces = cut_at_commas(b, e, worker_count(n_threads, (size_t)(e - b)));
+    const size_t np = pieces.size();
+    std::vector<size_t> cells(np + 1, 0);
+    {
+        std::vector<std::thread> th;
+        for (size_t i = 1; i < np; ++i) th.emplace_back([&, i] { cells[i + 1] = count_cells(pieces[i]); });
+        if (np) cells[1] = count_cells(pieces[0]);
+        for (auto &t : th) t.join();
+    }
+    for (size_t i = 0; i < np; ++i) cells[i + 1] += cells[i];
+    const size_t total = cells[np];
+    if (total > (size_t)INT32_MAX) return fail(MPS_ERR_UNSUPPORTED, "%s has %zu cells, more than int32 holds", what, total);
+    int32_t *arr = (int32_t *)malloc(sizeof(int32_t) * (total ? total : 1));
+    if (!arr) return fail(MPS_ERR_NOMEM, "out of memory for %zu cells of %s", total, what);
+    std::atomic<long> bad_at(-1);
+    auto run = [&](size_t i) {
+        long r = parse_cells(pieces[i], arr + cells[i]);
+        if (r >= 0) {
+            long want = -1;
+            bad_at.compare_exchange_strong(want, (long)(pieces[i].b - b) + r);
+        }
+    };
+    {
+        std::vector<std::thread> th;
+        for (size_t i = 1; i < np; ++i) th.emplace_back(run, i);
+        if (np) run(0);
+        for (auto &t : th) t.join();
+    }
+    if (bad_at.load() >= 0) {
+        free(arr);
+        return fail(MPS_ERR_FORMAT, "%s: not a decimal int32 cell at byte %ld of the line", what, bad_at.load());
+    }
+    *out = arr;
+    *count = total;
+    return MPS_OK;
+}
+
+struct Mapping {
+    const char *data = nullptr;
+    size_t size = 0;
+    int fd = -1;
+    ~Mapping() {
+        if (data && size) munmap((void *)data, size);
+        if (fd >= 0) close(fd);
+    }
+};
+
+}  // namespace
+
+extern "C" void mps_csr_free(mps_csr *csr) {
+    if (!csr) return;
+    free(csr->row_ptr);
+    free(csr->col_idx);
+    csr->row_ptr = csr->col_idx = nullptr;
+    csr->n_rows = csr->nnz = 0;
+}
+
+extern "C" int mps_csr_load(const char *path, int n_threads, mps_csr *out) {
+    if (!path || !out) return fail(MPS_ERR_ARG, "mps_csr_load: NULL argument");
+    memset(out, 0, sizeof *out);
+    Mapping m;
+    m.fd = open(path, O_RDONLY);
+    if (m.fd < 0) return fail(MPS_ERR_IO, "cannot open %s: %s", path, strerror(errno));
+    struct stat st;
+    if (fstat(m.fd, &st) != 0) return fail(MPS_ERR_IO, "cannot stat %s: %s", path, strerror(errno));
+    m.size = (size_t)st.st_size;
+    if (m.size == 0) return fail(MPS_ERR_FORMAT, "%s is empty", path);
+    void *map = mmap(nullptr, m.size, PROT_READ, MAP_PRIVATE, m.fd, 0);
+    if (map == MAP_FAILED) { m.size = 0; return fail(MPS_ERR_IO, "cannot map %s: %s", path, strerror(errno)); }
+    m.data = (const char *)map;
+    madvise(map, m.size, MADV_SEQUENTIAL);
+
+    const char *end = m.data + m.size;
+    const char *nl1 = (const char *)memchr(m.data, '\n', m.size);
+    const char *l1e = nl1 ? nl1 : end;
+    const char *l2b = nl1 ? nl1 + 1 : end;
+    const char *nl2 = l2b < end ? (const char *)memchr(l2b, '\n', (size_t)(end - l2b)) : nullptr;
+    const char *l2e = nl2 ? nl2 : end;
+
+    int32_t *rp = nullptr, *col = nullptr;
+    size_t n_rp = 0, n_col = 0;
+    if (int rc = parse_line(m.data, l1e, n_threads, &rp, &n_rp, "line 1 (row_ptr)")) return rc;
+    if (n_rp == 0) { free(rp); return fail(MPS_ERR_FORMAT, "%s: line 1 holds no row_ptr cell", path); }
+    if (int rc = parse_line(l2b, l2e, n_threads, &col, &n_col, "line 2 (col_idx)")) { free(rp); return rc; }
+
+    const int64_t n_rows = (int64_t)n_rp - 1, nnz = rp[n_rp - 1];
+    int rc = MPS_OK;
+    if (nnz < 0 || (size_t)nnz != n_col)
+        rc = fail(MPS_ERR_FORMAT, "%s: last row_ptr cell says %lld non-zeros, line 2 has %zu cells", path, (long long)nnz, n_col);
+    else if (rp[0] != 0)
+        rc = fail(MPS_ERR_FORMAT, "%s: row_ptr[0] is %d, expected 0", path, rp[0]);
+    else if (n_rows + 1 + nnz >= (int64_t)1 << 31)
+        rc = fail(MPS_ERR_UNSUPPORTED, "%s: N+1+nnz = %lld does not fit 31 bits", path, (long long)(n_rows + 1 + nnz));
+    for (int64_t i = 0; rc == MPS_OK && i < n_rows; ++i)
+        if (rp[i + 1] < rp[i]) rc = fail(MPS_ERR_FORMAT, "%s: row_ptr decreases at row %lld", path, (long long)i);
+    for (int64_t k = 0; rc == MPS_OK && k < nnz; ++k)
+        if (col[k] < 0 || col[k] >= n_rows) rc = fail(MPS_ERR_FORMAT, "%s: col_idx[%lld] = %d outside [0, %lld)", path, (long long)k, col[k], (long long)n_rows);
+    if (rc != MPS_OK) { free(rp); free(col); return rc; }
+    out->n_rows = (int32_t)n_rows;
+    out->nnz = (int32_t)nnz;
+    out->row_ptr = rp;
+    out->col_idx = col;
+    return MPS_OK;
+}
+
+namespace {
+// Formats cells [b,e) of a, each followed by ','.
+void format_cells(const int32_t *a, size_t b, size_t e, std::string &s) {
+    s.clear();
+    s.reserve((e - b) * 8);
+    char tmp[16];
+    for (size_t i = b; i < e; ++i) {
+        int n = snprintf(tmp, sizeof tmp, "%d,", a[i]);
+        s.append(tmp, (size_t)n);
+    }
+}
+int write_line(FILE *f, const int32_t *a, size_t n) {
+    const size_t block = 1 << 20;
+    const int nt = worker_count(0, n * 8);
+    std::vector<std::string> bufs((size_t)nt);
+    for (size_t base = 0; base < n; base += block * (size_t)nt) {
+        std::vector<std::thread> th;
+        for (int t = 0; t < nt; ++t) {
+            const size_t b = base + block * (size_t)t, e = b + block < n ? b + block : n;
+            if (b >= n) { bufs[(size_t)t].clear(); continue; }
+            th.emplace_back(format_cells, a, b, e, std::ref(bufs[(size_t)t]));
+        }
+        for (auto &t : th) t.join();
+        for (int t = 0; t < nt; ++t)
+            if (!bufs[(size_t)t].empty() && fwrite(bufs[(size_t)t].data(), 1, bufs[(size_t)t].size(), f) != bufs[(size_t)t].size()) return -1;
+    }
+    return 0;
+}
+}  // namespace
+
+extern "C" int mps_csr_save(const char *path, int32_t n_rows, const int32_t *row_ptr, const int32_t *col_idx) {
+    if (!path || !row_ptr || n_rows < 0) return fail(MPS_ERR_ARG, "mps_csr_save: bad argument");
+    const int32_t nnz = row_ptr[n_rows];
+    if (nnz < 0 || (nnz > 0 && !col_idx)) return fail(MPS_ERR_ARG, "mps_csr_save: bad nnz / col_idx");
+    FILE *f = fopen(path, "wb");
+    if (!f) return fail(MPS_ERR_IO, "cannot create %s: %s", path, strerror(errno));
+    int bad = write_line(f, row_ptr, (size_t)n_rows + 1);
+    if (!bad) bad = fputc('\n', f) == EOF;
+    if (!bad) bad = write_line(f, col_idx, (size_t)nnz);
+    if (fclose(f) != 0) bad = 1;
+    if (bad) return fail(MPS_ERR_IO, "short write to %s", path);
+    return MPS_OK;
+}
+
+namespace {
+struct BinHeader {
+    char magic[8];
+    int32_t n_rows, nnz, val_bytes;
+    int32_t reserved[3];
+};
+static_assert(sizeof(BinHeader) == 32, "sidecar header is 32 bytes");
+const char kMagic[8] = {'M', 'P', 'S', 'C', 'S', 'R', '0', '1'};
+}  // namespace
+
+extern "C" int mps_csr_save_bin(const char *path, int32_t n_rows, const int32_t *row_ptr, const int32_t *col_idx, const void *val,
+                                int val_bytes) {
+    if (!path || !row_ptr || n_rows < 0) return fail(MPS_ERR_ARG, "mps_csr_save_bin: bad argument");
+    if (!(val_bytes == 0 || val_bytes == 2 || val_bytes == 4) || (val_bytes && !val)) return fail(MPS_ERR_ARG, "mps_csr_save_bin: val_bytes must be 0, 2 or 4");
+    BinHeader h;
+    memset(&h, 0, sizeof h);
+    memcpy(h.magic, kMagic, 8);
+    h.n_rows = n_rows; h.nnz = row_ptr[n_rows]; h.val_bytes = val_bytes;
+    FILE *f = fopen(path, "wb");
+    if (!f) return fail(MPS_ERR_IO, "cannot create %s: %s", path, strerror(errno));
+    bool ok = fwrite(&h, sizeof h, 1, f) == 1;
+    ok = ok && fwrite(row_ptr, 4, (size_t)n_rows + 1, f) == (size_t)n_rows + 1;
+    ok = ok && (h.nnz == 0 || fwrite(col_idx, 4, (size_t)h.nnz, f) == (size_t)h.nnz);
+    ok = ok && (!val_bytes || h.nnz == 0 || fwrite(val, (size_t)val_bytes, (size_t)h.nnz, f) == (size_t)h.nnz);
+    if (fclose(f) != 0) ok = false;
+    if (!ok) return fail(MPS_ERR_IO, "short write to %s", path);
+    return MPS_OK;
+}
+
+extern "C" int mps_csr_load_bin(const char *path, mps_csr *out, void **val, int *val_bytes) {
+    if (!path || !out) return fail(MPS_ERR_ARG, "mps_csr_load_bin: NULL argument");
+    memset(out, 0, sizeof *out);
+    if (val) *val = nullptr;
+    if (val_bytes) *val_bytes = 0;
+    FILE *f = fopen(path, "rb");
+    if (!f) return fail(MPS_ERR_IO, "cannot open %s: %s", path, strerror(errno));
+    BinHeader h;
+    if (fread(&h, sizeof h, 1, f) != 1 || memcmp(h.magic, kMagic, 8) != 0 || h.n_rows < 0 || h.nnz < 0 ||
+        !(h.val_bytes == 0 || h.val_bytes == 2 || h.val_bytes == 4)) {
+        fclose(f);
+        return fail(MPS_ERR_FORMAT, "%s: not a csr sidecar", path);
+    }
+    int32_t *rp = (int32_t *)malloc(4 * ((size_t)h.n_rows + 1));
+    int32_t *col = (int32_t *)malloc(4 * ((size_t)h.nnz ? (size_t)h.nnz : 1));
+    void *v = (h.val_bytes && val) ? malloc((size_t)h.val_bytes * ((size_t)h.nnz ? (size_t)h.nnz : 1)) : nullptr;
+    bool ok = rp && col && (!(h.val_bytes && val) || v);
+    ok = ok && fread(rp, 4, (size_t)h.n_rows + 1, f) == (size_t)h.n_rows + 1;
+    ok = ok && (h.nnz == 0 || fread(col, 4, (size_t)h.nnz, f) == (size_t)h.nnz);
+    if (ok && v) ok = h.nnz == 0 || fread(v, (size_t)h.val_bytes, (size_t)h.nnz, f) == (size_t)h.nnz;
+    fclose(f);
+    if (ok && (rp[0] != 0 || rp[h.n_rows] != h.nnz)) ok = false;
+    if (!ok) { free(rp); free(col); free(v); return fail(MPS_ERR_FORMAT, "%s: truncated or inconsistent sidecar", path); }
+    out->n_rows = h.n_rows; out->nnz = h.nnz; out->row_ptr = rp; out->col_idx = col;
+    if (val) *val = v;
+    if (val_bytes) *val_bytes = v ? h.val_bytes : 0;
+    return MPS_OK;
+}

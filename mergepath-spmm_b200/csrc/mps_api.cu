@@ -1,0 +1,425 @@
+// C ABI of the B200 merge-path CSR SpMM library: plans, launches, the host-buffer call.
+// Declarations and the reference interface each entry point replaces: include/mps.h.
+#include "mps.h"
+
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <new>
+#include <string>
+
+#include "mps_internal.h"
+#include "mps_kernels.cuh"
+
+namespace mps {
+
+static thread_local std::string g_error;
+
+int fail(int code, const char *fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    g_error = buf;
+    return code;
+}
+
+#define MPS_CUDA(call)                                                                              \
+    do {                                                                                            \
+        cudaError_t e_ = (call);                                                                    \
+        if (e_ != cudaSuccess) return fail(MPS_ERR_CUDA, "%s: %s", #call, cudaGetErrorString(e_)); \
+    } while (0)
+
+static int check_shape(int64_t n_rows, int64_t nnz) {
+    if (n_rows < 0 || nnz < 0) return fail(MPS_ERR_ARG, "negative size (n_rows=%lld nnz=%lld)", (long long)n_rows, (long long)nnz);
+    if (n_rows + 1 + nnz >= (int64_t)1 << 31)
+        return fail(MPS_ERR_UNSUPPORTED, "N+1+nnz = %lld does not fit 31 bits", (long long)(n_rows + 1 + nnz));
+    return MPS_OK;
+}
+
+static void chunking(int n_rows, int nnz, int cost, int *n_chunks, int *ipt) {
+    const long long total = (long long)n_rows + 1 + nnz;
+    long long p = (total - 1) / cost;  // the reference's (N+1 + nnz - 1) / cost
+    if (p < 1024) p = 1024;
+    *n_chunks = (int)p;
+    *ipt = (int)((total + p - 1) / p);
+}
+
+}  // namespace mps
+
+using namespace mps;
+
+struct mps_plan {
+    int n_rows, nnz, dim, dtype, cost, tpw_requested, tpw_effective;
+    int n_chunks, ipt;
+    int vec, gl, unroll, slab_cols, n_col_slabs;
+    int nch, n_tiles, smem_bytes;
+    int bulk;
+    int long_chain, n_long, long_capacity;
+    int device;
+    bool user_nch, user_unroll;
+    bool partitioned;
+    int2 *d_tile_xy;
+    float *d_tcarry, *d_thead;
+    int *d_status, *d_long_list, *d_long_count;
+};
+
+extern "C" const char *mps_last_error(void) { return g_error.c_str(); }
+extern "C" const char *mps_version(void) { return "mps_b200 0.1 (sm_100a)"; }
+
+extern "C" int mps_chunk_count(int32_t n_rows, int32_t nnz, int32_t cost, int32_t *n_chunks, int32_t *items_per_chunk) {
+    if (cost < 1 || !n_chunks || !items_per_chunk) return fail(MPS_ERR_ARG, "mps_chunk_count: cost must be >= 1 and outputs non-NULL");
+    if (int rc = check_shape(n_rows, nnz)) return rc;
+    chunking(n_rows, nnz, cost, n_chunks, items_per_chunk);
+    return MPS_OK;
+}
+
+extern "C" int64_t mps_algorithmic_bytes(int32_t n_rows, int32_t nnz, int32_t dim, int dtype, int has_val) {
+    const int64_t s = dtype == MPS_F16 ? 2 : 4;
+    return 4 * ((int64_t)n_rows + 1) + (int64_t)nnz * (4 + (has_val ? s : 0)) + (int64_t)nnz * dim * s + (int64_t)n_rows * dim * s;
+}
+
+extern "C" int mps_partition_device(const int32_t *d_row_ptr, int32_t n_rows, int32_t nnz, int32_t n_chunks, int32_t *d_xy,
+                                    void *stream) {
+    if (!d_row_ptr || !d_xy || n_chunks < 1) return fail(MPS_ERR_ARG, "mps_partition_device: bad argument");
+    if (int rc = check_shape(n_rows, nnz)) return rc;
+    if (((uintptr_t)d_xy & 7) != 0) return fail(MPS_ERR_ALIGN, "mps_partition_device: d_xy must be 8-byte aligned");
+    const long long total = (long long)n_rows + 1 + nnz;
+    const long long ipt = (total + n_chunks - 1) / n_chunks;
+    const int count = n_chunks + 1;
+    partition_kernel<<<(count + 255) / 256, 256, 0, (cudaStream_t)stream>>>(d_row_ptr, n_rows, nnz, ipt, total, count,
+                                                                           reinterpret_cast<int2 *>(d_xy));
+    MPS_CUDA(cudaGetLastError());
+    return MPS_OK;
+}
+
+extern "C" int mps_schedule_device(const int32_t *d_row_ptr, int32_t n_rows, int32_t nnz, int32_t n_chunks, int32_t *d_six,
+                                   void *stream) {
+    if (!d_row_ptr || !d_six || n_chunks < 1) return fail(MPS_ERR_ARG, "mps_schedule_device: bad argument");
+    if (int rc = check_shape(n_rows, nnz)) return rc;
+    const long long total = (long long)n_rows + 1 + nnz;
+    const long long ipt = (total + n_chunks - 1) / n_chunks;
+    schedule_kernel<<<(n_chunks + 255) / 256, 256, 0, (cudaStream_t)stream>>>(d_row_ptr, n_rows, nnz, ipt, total, n_chunks, d_six);
+    MPS_CUDA(cudaGetLastError());
+    return MPS_OK;
+}
+
+// ------------------------------------------------------------------------------------- plan
+
+static int pow2_at_least(int v) {
+    int p = 1;
+    while (p < v) p <<= 1;
+    return p;
+}
+
+static const int kSmemTarget = 44 * 1024;   // keeps five tile blocks resident per SM
+static const int kSmemLimit = 200 * 1024;
+
+static int plan_layout(mps_plan *p) {
+    const int elem = p->dtype == MPS_F16 ? 2 : 4;
+    const int gpc = kBlock / p->gl;
+    if (!p->user_unroll) p->unroll = p->ipt >= 8 ? 8 : 4;
+    if (p->vec == 1) p->unroll = 4;
+    if (!p->user_nch) {
+        int rounds = 8;
+        while (rounds > 1 && TileSmem(gpc * rounds, p->ipt, p->slab_cols, elem).bytes > kSmemTarget) rounds >>= 1;
+        p->nch = gpc * rounds;
+    }
+    p->smem_bytes = TileSmem(p->nch, p->ipt, p->slab_cols, elem).bytes;
+    if (p->smem_bytes > kSmemLimit)
+        return fail(MPS_ERR_UNSUPPORTED, "tile of %d chunks x %d items needs %d bytes of shared memory", p->nch, p->ipt, p->smem_bytes);
+    p->n_tiles = (p->n_chunks + p->nch - 1) / p->nch;
+    return MPS_OK;
+}
+
+static void plan_free_scratch(mps_plan *p) {
+    cudaFree(p->d_tile_xy); cudaFree(p->d_tcarry); cudaFree(p->d_thead);
+    cudaFree(p->d_status); cudaFree(p->d_long_list); cudaFree(p->d_long_count);
+    p->d_tile_xy = nullptr; p->d_tcarry = p->d_thead = nullptr;
+    p->d_status = p->d_long_list = p->d_long_count = nullptr;
+}
+
+static int plan_alloc_scratch(mps_plan *p) {
+    plan_free_scratch(p);
+    p->long_capacity = p->n_tiles / p->long_chain + 2;
+    const size_t rows = (size_t)p->n_tiles * p->dim * sizeof(float);
+    MPS_CUDA(cudaMalloc(&p->d_tile_xy, sizeof(int2) * ((size_t)p->n_tiles + 1)));
+    MPS_CUDA(cudaMalloc(&p->d_tcarry, rows ? rows : 4));
+    MPS_CUDA(cudaMalloc(&p->d_thead, rows ? rows : 4));
+    MPS_CUDA(cudaMalloc(&p->d_status, sizeof(int)));
+    MPS_CUDA(cudaMalloc(&p->d_long_list, sizeof(int) * (size_t)p->long_capacity));
+    MPS_CUDA(cudaMalloc(&p->d_long_count, sizeof(int)));
+    MPS_CUDA(cudaMemset(p->d_status, 0, sizeof(int)));
+    return MPS_OK;
+}
+
+extern "C" int mps_plan_create(int32_t n_rows, int32_t nnz, int32_t dim, int dtype, int32_t cost, int32_t threads_per_warp,
+                               mps_plan **out) {
+    if (!out) return fail(MPS_ERR_ARG, "mps_plan_create: out is NULL");
+    *out = nullptr;
+    if (dim < 1 || cost < 1) return fail(MPS_ERR_ARG, "mps_plan_create: dim and cost must be >= 1 (dim=%d cost=%d)", dim, cost);
+    if (dtype != MPS_F32 && dtype != MPS_F16) return fail(MPS_ERR_ARG, "mps_plan_create: unknown dtype %d", dtype);
+    if (int rc = check_shape(n_rows, nnz)) return rc;
+    mps_plan *p = new (std::nothrow) mps_plan();
+    if (!p) return fail(MPS_ERR_NOMEM, "mps_plan_create: out of host memory");
+    memset(p, 0, sizeof *p);
+    p->n_rows = n_rows; p->nnz = nnz; p->dim = dim; p->dtype = dtype; p->cost = cost;
+    p->tpw_requested = threads_per_warp;
+    // the reference exits when tpw > 32/dim (src/MergePathSpMM.cu:224-228) and ignores it for dim > 32
+    const int tpw_max = dim <= 32 ? 32 / dim : 1;
+    p->tpw_effective = threads_per_warp < 1 ? 1 : (threads_per_warp > tpw_max ? tpw_max : threads_per_warp);
+    chunking(n_rows, nnz, cost, &p->n_chunks, &p->ipt);
+    const int full_vec = dtype == MPS_F16 ? 8 : 4;
+    if (dim % full_vec == 0) {
+        p->vec = full_vec;
+        int lanes = dim / full_vec;
+        p->gl = lanes >= 32 ? 32 : pow2_at_least(lanes < 2 ? 2 : lanes);
+    } else {
+        p->vec = 1;
+        p->gl = 32;
+    }
+    p->slab_cols = p->gl * p->vec;
+    p->n_col_slabs = (dim + p->slab_cols - 1) / p->slab_cols;
+    p->bulk = 1;
+    p->long_chain = 32;
+    MPS_CUDA(cudaGetDevice(&p->device));
+    int rc = plan_layout(p);
+    if (rc == MPS_OK) rc = plan_alloc_scratch(p);
+    if (rc != MPS_OK) { plan_free_scratch(p); delete p; return rc; }
+    *out = p;
+    return MPS_OK;
+}
+
+extern "C" void mps_plan_destroy(mps_plan *plan) {
+    if (!plan) return;
+    plan_free_scratch(plan);
+    delete plan;
+}
+
+extern "C" int mps_plan_tune(mps_plan *p, int32_t chunks_per_tile, int32_t unroll, int32_t bulk_staging) {
+    if (!p) return fail(MPS_ERR_ARG, "mps_plan_tune: plan is NULL");
+    if (unroll != 0 && unroll != 4 && unroll != 8) return fail(MPS_ERR_ARG, "mps_plan_tune: unroll must be 0, 4 or 8");
+    if (chunks_per_tile < 0 || chunks_per_tile > 4096) return fail(MPS_ERR_ARG, "mps_plan_tune: chunks_per_tile out of range");
+    const int old_tiles = p->n_tiles;
+    p->user_nch = chunks_per_tile > 0;
+    if (p->user_nch) p->nch = chunks_per_tile;
+    p->user_unroll = unroll != 0;
+    if (p->user_unroll) p->unroll = unroll;
+    p->bulk = bulk_staging ? 1 : 0;
+    if (int rc = plan_layout(p)) return rc;
+    p->partitioned = false;
+    if (p->n_tiles != old_tiles) return plan_alloc_scratch(p);
+    return MPS_OK;
+}
+
+extern "C" int mps_plan_partition(mps_plan *p, const int32_t *d_row_ptr, void *stream) {
+    if (!p || !d_row_ptr) return fail(MPS_ERR_ARG, "mps_plan_partition: NULL argument");
+    cudaStream_t st = (cudaStream_t)stream;
+    const long long total = (long long)p->n_rows + 1 + p->nnz;
+    const int count = p->n_tiles + 1;
+    partition_kernel<<<(count + 255) / 256, 256, 0, st>>>(d_row_ptr, p->n_rows, p->nnz, (long long)p->ipt * p->nch, total, count,
+                                                         p->d_tile_xy);
+    MPS_CUDA(cudaGetLastError());
+    MPS_CUDA(cudaMemsetAsync(p->d_long_count, 0, sizeof(int), st));
+    if (p->n_tiles > 1) {
+        fixup_list_long_kernel<<<(p->n_tiles - 1 + 255) / 256, 256, 0, st>>>(p->d_tile_xy, d_row_ptr, p->n_tiles, p->long_chain,
+                                                                            p->d_long_list, p->d_long_count, p->long_capacity);
+        MPS_CUDA(cudaGetLastError());
+    }
+    int n_long = 0;
+    MPS_CUDA(cudaMemcpyAsync(&n_long, p->d_long_count, sizeof(int), cudaMemcpyDeviceToHost, st));
+    MPS_CUDA(cudaStreamSynchronize(st));
+    if (n_long > p->long_capacity) return fail(MPS_ERR_STATE, "mps_plan_partition: %d long rows exceed the list capacity %d", n_long, p->long_capacity);
+    p->n_long = n_long;
+    p->partitioned = true;
+    return MPS_OK;
+}
+
+template <typename T, int VEC, int GL, int U>
+static int launch_tile(const mps_plan *p, const TileParams &tp, cudaStream_t st) {
+    auto kern = spmm_tile_kernel<T, VEC, GL, U>;
+    if (p->smem_bytes > 48 * 1024) MPS_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, p->smem_bytes));
+    dim3 grid((unsigned)p->n_tiles, (unsigned)p->n_col_slabs);
+    kern<<<grid, kBlock, p->smem_bytes, st>>>(tp);
+    MPS_CUDA(cudaGetLastError());
+    return MPS_OK;
+}
+
+template <typename T, int VEC, int GL>
+static int launch_tile_u(const mps_plan *p, const TileParams &tp, cudaStream_t st) {
+    if (p->unroll == 8) return launch_tile<T, VEC, GL, 8>(p, tp, st);
+    return launch_tile<T, VEC, GL, 4>(p, tp, st);
+}
+
+template <typename T, int VEC>
+static int launch_tile_gl(const mps_plan *p, const TileParams &tp, cudaStream_t st) {
+    switch (p->gl) {
+        case 2: return launch_tile_u<T, VEC, 2>(p, tp, st);
+        case 4: return launch_tile_u<T, VEC, 4>(p, tp, st);
+        case 8: return launch_tile_u<T, VEC, 8>(p, tp, st);
+        case 16: return launch_tile_u<T, VEC, 16>(p, tp, st);
+        case 32: return launch_tile_u<T, VEC, 32>(p, tp, st);
+    }
+    return fail(MPS_ERR_STATE, "no kernel for %d lanes per chunk", p->gl);
+}
+
+template <typename T, int FULLVEC>
+static int spmm_typed(mps_plan *p, const TileParams &tp, cudaStream_t st) {
+    int rc;
+    if (p->vec == 1) rc = launch_tile<T, 1, 32, 4>(p, tp, st);
+    else rc = launch_tile_gl<T, FULLVEC>(p, tp, st);
+    if (rc != MPS_OK) return rc;
+    if (p->n_tiles > 1) {
+        const int warps = p->n_tiles - 1;
+        fixup_short_kernel<T><<<(warps + 7) / 8, 256, 0, st>>>(p->d_tile_xy, tp.rp, p->d_tcarry, p->d_thead, static_cast<T *>(tp.C),
+                                                              p->n_tiles, p->dim, p->long_chain);
+        MPS_CUDA(cudaGetLastError());
+    }
+    if (p->n_long > 0) {
+        fixup_long_kernel<T><<<p->n_long, kStrands * 32, 0, st>>>(p->d_tile_xy, tp.rp, p->d_tcarry, p->d_thead, static_cast<T *>(tp.C),
+                                                                 p->d_long_list, p->dim);
+        MPS_CUDA(cudaGetLastError());
+    }
+    return MPS_OK;
+}
+
+extern "C" int mps_spmm(mps_plan *p, const int32_t *d_row_ptr, const int32_t *d_col_idx, const void *d_val, const void *d_B,
+                        void *d_C, void *stream) {
+    if (!p || !d_row_ptr || !d_B || !d_C || (!d_col_idx && p->nnz > 0)) return fail(MPS_ERR_ARG, "mps_spmm: NULL argument");
+    if (!p->partitioned) return fail(MPS_ERR_STATE, "mps_spmm: call mps_plan_partition first");
+    const uintptr_t elem = p->dtype == MPS_F16 ? 2 : 4;
+    const uintptr_t need = p->vec > 1 ? 16 : elem;
+    if (((uintptr_t)d_B % need) || ((uintptr_t)d_C % need))
+        return fail(MPS_ERR_ALIGN, "mps_spmm: B and C must be %d-byte aligned for dim=%d", (int)need, p->dim);
+    if (((uintptr_t)d_row_ptr % 4) || ((uintptr_t)d_col_idx % 4) || ((uintptr_t)d_val % elem))
+        return fail(MPS_ERR_ALIGN, "mps_spmm: row_ptr/col_idx/val not aligned to their element size");
+    TileParams tp;
+    tp.rp = d_row_ptr; tp.col = d_col_idx; tp.val = d_val; tp.B = d_B; tp.C = d_C;
+    tp.tile_xy = p->d_tile_xy; tp.tcarry = p->d_tcarry; tp.thead = p->d_thead; tp.status = p->d_status;
+    tp.total = (long long)p->n_rows + 1 + p->nnz;
+    tp.n_rows = p->n_rows; tp.nnz = p->nnz; tp.dim = p->dim;
+    tp.ipt = p->ipt; tp.nch = p->nch; tp.n_tiles = p->n_tiles;
+    const bool aligned16 = !((uintptr_t)d_row_ptr % 16) && !((uintptr_t)d_col_idx % 16) && !((uintptr_t)d_val % 16);
+    tp.bulk = (p->bulk && aligned16) ? 1 : 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (p->dtype == MPS_F16) return spmm_typed<__half, 8>(p, tp, st);
+    return spmm_typed<float, 4>(p, tp, st);
+}
+
+extern "C" int mps_plan_sync_check(mps_plan *p, void *stream) {
+    if (!p) return fail(MPS_ERR_ARG, "mps_plan_sync_check: plan is NULL");
+    int status = 0;
+    MPS_CUDA(cudaMemcpyAsync(&status, p->d_status, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+    MPS_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+    if (status != kDevOk) {
+        cudaMemsetAsync(p->d_status, 0, sizeof(int), (cudaStream_t)stream);
+        return fail(MPS_ERR_DEVICE, "a tile block gave up waiting for its staged window (status %d)", status);
+    }
+    return MPS_OK;
+}
+
+extern "C" int mps_plan_info(const mps_plan *p, int64_t what[12]) {
+    if (!p || !what) return fail(MPS_ERR_ARG, "mps_plan_info: NULL argument");
+    what[0] = p->n_chunks; what[1] = p->ipt; what[2] = p->nch; what[3] = p->n_tiles;
+    what[4] = p->gl; what[5] = p->vec; what[6] = p->unroll; what[7] = p->smem_bytes;
+    what[8] = p->n_long; what[9] = p->tpw_effective;
+    what[10] = 1 + (p->n_tiles > 1 ? 1 : 0) + (p->n_long > 0 ? 1 : 0);
+    what[11] = p->long_chain;
+    return MPS_OK;
+}
+
+// ------------------------------------------------------------------------------------- host-buffer call
+
+namespace {
+struct HostWorkspace {
+    void *buf[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};  // rp, col, val, B, C
+    size_t cap[5] = {0, 0, 0, 0, 0};
+    mps_plan *plan = nullptr;
+    cudaStream_t stream = nullptr;
+    int device = -1;
+    void release() {
+        for (int i = 0; i < 5; ++i) { cudaFree(buf[i]); buf[i] = nullptr; cap[i] = 0; }
+        mps_plan_destroy(plan); plan = nullptr;
+        if (stream) cudaStreamDestroy(stream);
+        stream = nullptr; device = -1;
+    }
+};
+thread_local HostWorkspace g_ws;
+}  // namespace
+
+static int ws_reserve(int i, size_t bytes) {
+    if (g_ws.cap[i] >= bytes) return MPS_OK;
+    cudaFree(g_ws.buf[i]);
+    g_ws.buf[i] = nullptr; g_ws.cap[i] = 0;
+    MPS_CUDA(cudaMalloc(&g_ws.buf[i], bytes ? bytes : 16));
+    g_ws.cap[i] = bytes;
+    return MPS_OK;
+}
+
+extern "C" void mps_host_workspace_release(void) { g_ws.release(); }
+
+extern "C" int mps_spmm_host(int32_t n_rows, int32_t nnz, int32_t dim, int dtype, int32_t cost, int32_t threads_per_warp,
+                             const int32_t *row_ptr, const int32_t *col_idx, const void *val, const void *B, void *C) {
+    if (!row_ptr || !B || !C || (!col_idx && nnz > 0)) return fail(MPS_ERR_ARG, "mps_spmm_host: NULL argument");
+    if (dim < 1 || cost < 1) return fail(MPS_ERR_ARG, "mps_spmm_host: dim and cost must be >= 1");
+    if (dtype != MPS_F32 && dtype != MPS_F16) return fail(MPS_ERR_ARG, "mps_spmm_host: unknown dtype %d", dtype);
+    if (int rc = check_shape(n_rows, nnz)) return rc;
+    int dev = 0;
+    MPS_CUDA(cudaGetDevice(&dev));
+    if (g_ws.device != dev) { g_ws.release(); g_ws.device = dev; }
+    if (!g_ws.stream) MPS_CUDA(cudaStreamCreateWithFlags(&g_ws.stream, cudaStreamNonBlocking));
+    const size_t elem = dtype == MPS_F16 ? 2 : 4;
+    const size_t n_b_rows = (size_t)n_rows;  // A is square by the file format's convention
+    const size_t bytes[5] = {4 * ((size_t)n_rows + 1), 4 * (size_t)nnz, val ? elem * (size_t)nnz : 0, elem * n_b_rows * dim,
+                             elem * (size_t)n_rows * dim};
+    for (int i = 0; i < 5; ++i)
+        if (int rc = ws_reserve(i, bytes[i])) return rc;
+    mps_plan *p = g_ws.plan;
+    if (!p || p->n_rows != n_rows || p->nnz != nnz || p->dim != dim || p->dtype != dtype || p->cost != cost) {
+        mps_plan_destroy(p);
+        g_ws.plan = nullptr;
+        if (int rc = mps_plan_create(n_rows, nnz, dim, dtype, cost, threads_per_warp, &p)) return rc;
+        g_ws.plan = p;
+    }
+    cudaStream_t st = g_ws.stream;
+    MPS_CUDA(cudaMemcpyAsync(g_ws.buf[0], row_ptr, bytes[0], cudaMemcpyHostToDevice, st));
+    if (int rc = mps_plan_partition(p, (const int32_t *)g_ws.buf[0], st)) return rc;  // overlaps nothing yet: needs row_ptr only
+    if (bytes[1]) MPS_CUDA(cudaMemcpyAsync(g_ws.buf[1], col_idx, bytes[1], cudaMemcpyHostToDevice, st));
+    if (bytes[2]) MPS_CUDA(cudaMemcpyAsync(g_ws.buf[2], val, bytes[2], cudaMemcpyHostToDevice, st));
+    MPS_CUDA(cudaMemcpyAsync(g_ws.buf[3], B, bytes[3], cudaMemcpyHostToDevice, st));
+    if (int rc = mps_spmm(p, (const int32_t *)g_ws.buf[0], (const int32_t *)g_ws.buf[1], val ? g_ws.buf[2] : nullptr, g_ws.buf[3],
+                          g_ws.buf[4], st))
+        return rc;
+    if (bytes[4]) MPS_CUDA(cudaMemcpyAsync(C, g_ws.buf[4], bytes[4], cudaMemcpyDeviceToHost, st));
+    return mps_plan_sync_check(p, st);
+}
+
+// ------------------------------------------------------------------------------------- slabs (host)
+
+extern "C" int mps_slab_bounds(const int32_t *row_ptr, int32_t n_rows, int32_t n_slabs, int32_t *bounds) {
+    if (!row_ptr || !bounds || n_rows < 0 || n_slabs < 1) return fail(MPS_ERR_ARG, "mps_slab_bounds: bad argument");
+    const long long nnz = row_ptr[n_rows];
+    bounds[0] = 0;
+    for (int g = 1; g < n_slabs; ++g) {
+        const long long want = nnz * g / n_slabs;
+        int lo = 0, hi = n_rows;
+        while (lo < hi) {
+            const int mid = (lo + hi) >> 1;
+            if (row_ptr[mid] < want) lo = mid + 1;
+            else hi = mid;
+        }
+        bounds[g] = lo;
+    }
+    bounds[n_slabs] = n_rows;
+    return MPS_OK;
+}
+
+extern "C" int mps_slab_rebase(const int32_t *row_ptr, int32_t row0, int32_t row1, int32_t *out_row_ptr) {
+    if (!row_ptr || !out_row_ptr || row0 < 0 || row1 < row0) return fail(MPS_ERR_ARG, "mps_slab_rebase: bad argument");
+    const int32_t base = row_ptr[row0];
+    for (int32_t i = row0; i <= row1; ++i) out_row_ptr[i - row0] = row_ptr[i] - base;
+    return MPS_OK;
+}

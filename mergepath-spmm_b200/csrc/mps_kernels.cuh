@@ -1,0 +1,521 @@
+// Device code of the B200 merge-path CSR SpMM (sm_100a).
+//
+// Work decomposition (all diagonals are the reference's: chunk c covers merge items
+// [ipt*c, ipt*(c+1)) of the merge of row_ptr[0..N] with 0..nnz-1, src/MergePathSpMM.cu:327-334):
+//
+//   tile   = `nch` consecutive chunks, one thread block.  Its two boundary coordinates come from
+//            the plan (searched once per row_ptr by partition_kernel); the block stages the tile's
+//            row_ptr / col_idx / val windows into shared memory with bulk async copies that
+//            complete on an mbarrier, then re-searches the nch-1 interior diagonals in shared memory.
+//   chunk  = walked by one group of GL lanes; a lane owns VEC adjacent columns and gathers its part
+//            of every B row of the chunk with one 128-bit load, U loads in flight before the first
+//            fused multiply-add.  Rows that end inside the chunk and began there are stored
+//            directly; a row that began earlier leaves its share as the chunk's "head", what is left
+//            at the chunk's end is the chunk's "carry" (both in shared memory, fp32).
+//   fix-up = inside the tile, in chunk order, by the group that ended the row; across tiles by
+//            fixup kernels that add the tiles' carry rows in tile order.  No atomics touch C, every
+//            row of C is stored exactly once, sums are bitwise reproducible.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace mps {
+
+constexpr int kBlock = 256;          // threads per tile block
+constexpr int kStrands = 16;         // interleaved partial sums of the long-row fix-up
+constexpr int kAlign = 8;            // staging windows start on multiples of 8 elements (>= 16 bytes)
+constexpr int kWaitPolls = 1 << 22;  // bounded mbarrier wait
+
+enum DeviceStatus : int { kDevOk = 0, kDevStageTimeout = 1 };
+
+struct TileParams {
+    const int *rp;
+    const int *col;
+    const void *val;  // nullptr: all ones
+    const void *B;
+    void *C;
+    const int2 *tile_xy;  // n_tiles + 1 boundary coordinates, reference convention
+    float *tcarry;        // n_tiles x dim
+    float *thead;         // n_tiles x dim
+    int *status;
+    long long total;  // N + 1 + nnz
+    int n_rows, nnz, dim;
+    int ipt, nch, n_tiles;
+    int bulk;  // 1: bulk async staging (needs 16-byte aligned rp/col/val)
+};
+
+// ---------------------------------------------------------------------------------------------
+// merge-path search, reference convention (src/MergePathSpMM.cu:280-297 with list B = identity)
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ int2 merge_path_search_global(long long diag, const int *__restrict__ rp, int n_list_a, int nnz) {
+    long long lo = diag - nnz;
+    if (lo < 0) lo = 0;
+    long long hi = diag < n_list_a ? diag : n_list_a;
+    while (lo < hi) {
+        long long mid = (lo + hi) >> 1;
+        if ((long long)__ldg(rp + mid) <= diag - mid - 1) lo = mid + 1;
+        else hi = mid;
+    }
+    if (lo > n_list_a) lo = n_list_a;
+    return make_int2((int)lo, (int)(diag - lo));
+}
+
+// count coordinates for diagonals min(step * t, total), t = 0..count-1
+__global__ void partition_kernel(const int *__restrict__ rp, int n_rows, int nnz, long long step, long long total,
+                                 int count, int2 *__restrict__ out) {
+    int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= count) return;
+    long long d = step * (long long)t;
+    if (d > total) d = total;
+    out[t] = merge_path_search_global(d, rp, n_rows + 1, nnz);
+}
+
+// The reference's six per-chunk arrays (src/MergePathSpMM.cu:336-376), one thread per chunk.
+__global__ void schedule_kernel(const int *__restrict__ rp, int n_rows, int nnz, long long ipt, long long total,
+                                int n_chunks, int *__restrict__ six) {
+    int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= n_chunks) return;
+    long long d0 = ipt * (long long)t;
+    if (d0 > total) d0 = total;
+    long long d1 = d0 + ipt;
+    if (d1 > total) d1 = total;
+    const int2 a = merge_path_search_global(d0, rp, n_rows + 1, nnz);
+    const int2 b = merge_path_search_global(d1, rp, n_rows + 1, nnz);
+    const int first = a.x > 0 ? a.x - 1 : 0;
+    const int last = b.x - 1;
+    const int rp_first = __ldg(rp + first), rp_last = __ldg(rp + last);
+    int head_at = (rp_first == a.y || t == 0) ? 0 : a.y;
+    int tail_at = (rp_last == b.y) ? 0 : b.y;
+    int head_len = 0, tail_len = 0;
+    if (head_at != 0) {
+        if (first == last && tail_at != 0) { head_len = tail_at - head_at; tail_at = 0; }
+        else head_len = __ldg(rp + first + 1) - head_at;
+    }
+    if (tail_at != 0) { tail_len = tail_at - rp_last; tail_at = rp_last; }  // 0 stays the "none" mark
+    const size_t p = (size_t)n_chunks;
+    six[t] = head_at;
+    six[p + t] = head_len;
+    six[2 * p + t] = tail_at;
+    six[3 * p + t] = tail_len;
+    six[4 * p + t] = first;
+    six[5 * p + t] = last;
+}
+
+// ---------------------------------------------------------------------------------------------
+// mbarrier / bulk-copy wrappers (1-D bulk copy global -> shared of this block, completion counted
+// in bytes on an mbarrier; source, destination and size are multiples of 16 bytes)
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+                 "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Returns false when the phase did not complete within the poll limit.
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
+    for (int i = 0; i < kWaitPolls; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (i > 32) __nanosleep(64);
+    }
+    return false;
+}
+
+// ---------------------------------------------------------------------------------------------
+// per-lane column vectors
+// ---------------------------------------------------------------------------------------------
+template <typename T, int VEC>
+struct Lane;
+
+template <>
+struct Lane<float, 4> {
+    typedef float4 raw;
+    static __device__ __forceinline__ raw load(const float *p) { return __ldg(reinterpret_cast<const float4 *>(p)); }
+    static __device__ __forceinline__ void fma(float (&acc)[4], float a, const raw &b) {
+        acc[0] = fmaf(a, b.x, acc[0]); acc[1] = fmaf(a, b.y, acc[1]);
+        acc[2] = fmaf(a, b.z, acc[2]); acc[3] = fmaf(a, b.w, acc[3]);
+    }
+    static __device__ __forceinline__ void store(float *p, const float (&v)[4]) {
+        __stcs(reinterpret_cast<float4 *>(p), make_float4(v[0], v[1], v[2], v[3]));
+    }
+};
+template <>
+struct Lane<float, 1> {
+    typedef float raw;
+    static __device__ __forceinline__ raw load(const float *p) { return __ldg(p); }
+    static __device__ __forceinline__ void fma(float (&acc)[1], float a, const raw &b) { acc[0] = fmaf(a, b, acc[0]); }
+    static __device__ __forceinline__ void store(float *p, const float (&v)[1]) { __stcs(p, v[0]); }
+};
+template <>
+struct Lane<__half, 8> {
+    typedef uint4 raw;
+    static __device__ __forceinline__ raw load(const __half *p) { return __ldg(reinterpret_cast<const uint4 *>(p)); }
+    static __device__ __forceinline__ void fma(float (&acc)[8], float a, const raw &b) {
+        const __half2 *h = reinterpret_cast<const __half2 *>(&b);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 f = __half22float2(h[i]);
+            acc[2 * i] = fmaf(a, f.x, acc[2 * i]);
+            acc[2 * i + 1] = fmaf(a, f.y, acc[2 * i + 1]);
+        }
+    }
+    static __device__ __forceinline__ void store(__half *p, const float (&v)[8]) {
+        uint4 o;
+        __half2 *h = reinterpret_cast<__half2 *>(&o);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+        __stcs(reinterpret_cast<uint4 *>(p), o);
+    }
+};
+template <>
+struct Lane<__half, 1> {
+    typedef __half raw;
+    static __device__ __forceinline__ raw load(const __half *p) { return __ldg(p); }
+    static __device__ __forceinline__ void fma(float (&acc)[1], float a, const raw &b) { acc[0] = fmaf(a, __half2float(b), acc[0]); }
+    static __device__ __forceinline__ void store(__half *p, const float (&v)[1]) { *p = __float2half_rn(v[0]); }
+};
+
+__device__ __forceinline__ float to_float(float v) { return v; }
+__device__ __forceinline__ float to_float(__half v) { return __half2float(v); }
+
+template <int VEC>
+__device__ __forceinline__ void smem_put(float *dst, const float (&v)[VEC]) {
+    if constexpr (VEC % 4 == 0) {
+#pragma unroll
+        for (int i = 0; i < VEC; i += 4) *reinterpret_cast<float4 *>(dst + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+    } else {
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) dst[i] = v[i];
+    }
+}
+template <int VEC>
+__device__ __forceinline__ void vec_add(float (&acc)[VEC], const float *src) {
+    if constexpr (VEC % 4 == 0) {
+#pragma unroll
+        for (int i = 0; i < VEC; i += 4) {
+            const float4 f = *reinterpret_cast<const float4 *>(src + i);
+            acc[i] += f.x; acc[i + 1] += f.y; acc[i + 2] += f.z; acc[i + 3] += f.w;
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) acc[i] += src[i];
+    }
+}
+template <int VEC>
+__device__ __forceinline__ void gmem_put_f32(float *dst, const float (&v)[VEC]) {
+    if constexpr (VEC % 4 == 0) {
+#pragma unroll
+        for (int i = 0; i < VEC; i += 4) *reinterpret_cast<float4 *>(dst + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+    } else {
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) dst[i] = v[i];
+    }
+}
+
+// Shared-memory layout of one tile block, shared by host (size) and device (offsets).
+struct TileSmem {
+    int off_fx, off_fy, off_rp, off_col, off_val, off_carry, off_head, bytes;
+    __host__ __device__ static int up16(int v) { return (v + 15) & ~15; }
+    __host__ __device__ TileSmem(int nch, int ipt, int slab_cols, int elem_bytes) {
+        const int win = nch * ipt + 2 * kAlign + 8;  // window plus alignment slack on both sides
+        int o = 16;                                  // mbarrier
+        off_fx = o; o = up16(o + 4 * (nch + 1));
+        off_fy = o; o = up16(o + 4 * (nch + 1));
+        off_rp = o; o = up16(o + 4 * win);
+        off_col = o; o = up16(o + 4 * win);
+        off_val = o; o = up16(o + elem_bytes * win);
+        off_carry = o; o = up16(o + 4 * nch * slab_cols);
+        off_head = o; o = up16(o + 4 * nch * slab_cols);
+        bytes = o;
+    }
+};
+
+// Staging of elements [base, hi) of a global array of arr_len elements so that element i lands at
+// s_dst[i - base]; base is a multiple of kAlign.  The 16-byte-granular part [base, bulk_end) goes
+// through one bulk copy; the ragged end (at most the array's last kAlign-1 elements) is fetched
+// with plain loads.
+__device__ __forceinline__ long long bulk_end_of(long long base, long long hi, long long arr_len) {
+    if (hi <= base) return base;
+    long long e = (hi + kAlign - 1) & ~(long long)(kAlign - 1);
+    const long long cap = arr_len & ~(long long)(kAlign - 1);
+    if (e > cap) e = cap;
+    return e > base ? e : base;
+}
+template <typename E>
+__device__ __forceinline__ void stage_ragged(E *s_dst, const E *g_src, long long base, long long bulk_end, long long hi, int tid) {
+    const long long i = bulk_end + tid;
+    if (i < hi) s_dst[i - base] = g_src[i];
+}
+
+// ---------------------------------------------------------------------------------------------
+// the tile kernel
+// ---------------------------------------------------------------------------------------------
+template <typename T, int VEC, int GL, int U>
+__global__ void __launch_bounds__(kBlock) spmm_tile_kernel(const TileParams p) {
+    constexpr int GPC = kBlock / GL;   // groups (chunks walked at once) per block
+    constexpr int SLAB = GL * VEC;     // columns covered by one block
+    extern __shared__ __align__(128) unsigned char smem[];
+    const TileSmem L(p.nch, p.ipt, SLAB, (int)sizeof(T));
+    uint64_t *s_bar = reinterpret_cast<uint64_t *>(smem);
+    int *s_fx = reinterpret_cast<int *>(smem + L.off_fx);
+    int *s_fy = reinterpret_cast<int *>(smem + L.off_fy);
+    int *s_rp = reinterpret_cast<int *>(smem + L.off_rp);
+    int *s_col = reinterpret_cast<int *>(smem + L.off_col);
+    T *s_val = reinterpret_cast<T *>(smem + L.off_val);
+    float *s_carry = reinterpret_cast<float *>(smem + L.off_carry);
+    float *s_head = reinterpret_cast<float *>(smem + L.off_head);
+
+    const int tid = threadIdx.x;
+    const int g = tid / GL, l = tid % GL;
+    const int t = blockIdx.x;
+    const int coff = blockIdx.y * SLAB + l * VEC;  // first column of this lane
+    const bool active = coff < p.dim;
+    const bool has_val = p.val != nullptr;
+    const T *__restrict__ Bm = static_cast<const T *>(p.B);
+    T *__restrict__ Cm = static_cast<T *>(p.C);
+
+    const int2 c0 = __ldg(p.tile_xy + t), c1 = __ldg(p.tile_xy + t + 1);
+    const int X0 = c0.x, Y0 = c0.y, X1 = c1.x, Y1 = c1.y;
+    // row_ptr entries [max(X0-1,0), X1) and non-zeros [Y0, Y1) are what this tile touches
+    const int rp_first = X0 > 0 ? X0 - 1 : 0;
+    const int rp_base = rp_first & ~(kAlign - 1);
+    const int y_base = Y0 & ~(kAlign - 1);
+
+    // ---- stage the tile's windows ----
+    if (p.bulk) {
+        const uint32_t bar = smem_u32(s_bar);
+        if (tid == 0) mbar_init(bar, 1);
+        __syncthreads();
+        const long long rp_be = bulk_end_of(rp_base, X1, (long long)p.n_rows + 1);
+        const long long y_be = bulk_end_of(y_base, Y1, p.nnz);
+        if (tid == 0) {
+            const uint32_t n_rp = (uint32_t)(rp_be - rp_base) * 4u;
+            const uint32_t n_col = (uint32_t)(y_be - y_base) * 4u;
+            const uint32_t n_val = has_val ? (uint32_t)(y_be - y_base) * (uint32_t)sizeof(T) : 0u;
+            mbar_arrive_expect(bar, n_rp + n_col + n_val);  // the single arrival the phase waits for
+            if (n_rp) bulk_g2s(smem_u32(s_rp), p.rp + rp_base, n_rp, bar);
+            if (n_col) bulk_g2s(smem_u32(s_col), p.col + y_base, n_col, bar);
+            if (n_val) bulk_g2s(smem_u32(s_val), static_cast<const T *>(p.val) + y_base, n_val, bar);
+        }
+        stage_ragged<int>(s_rp, p.rp, rp_base, rp_be, X1, tid);
+        stage_ragged<int>(s_col, p.col, y_base, y_be, Y1, tid);
+        if (has_val) stage_ragged<T>(s_val, static_cast<const T *>(p.val), y_base, y_be, Y1, tid);
+        bool ok = mbar_wait_bounded(bar, 0);
+        if (!ok) {
+            atomicExch(p.status, (int)kDevStageTimeout);
+            ok = mbar_wait_bounded(bar, 0);  // give copies in flight one more bounded chance to land
+        }
+        if (__syncthreads_or(!ok)) return;
+    } else {
+        for (int i = rp_base + tid; i < X1; i += kBlock) s_rp[i - rp_base] = p.rp[i];
+        for (int i = y_base + tid; i < Y1; i += kBlock) s_col[i - y_base] = p.col[i];
+        if (has_val)
+            for (int i = y_base + tid; i < Y1; i += kBlock) s_val[i - y_base] = static_cast<const T *>(p.val)[i];
+        __syncthreads();
+    }
+
+    // ---- interior diagonals, searched in the staged row_ptr window ----
+    for (int c = tid; c <= p.nch; c += kBlock) {
+        int2 r;
+        if (c == 0) r = c0;
+        else if (c == p.nch) r = c1;
+        else {
+            long long d = (long long)p.ipt * ((long long)t * p.nch + c);
+            if (d > p.total) d = p.total;
+            long long lo = d - Y1 > X0 ? d - Y1 : X0;
+            long long hi = d - Y0 < X1 ? d - Y0 : X1;
+            while (lo < hi) {
+                const long long mid = (lo + hi) >> 1;
+                if ((long long)s_rp[mid - rp_base] <= d - mid - 1) lo = mid + 1;
+                else hi = mid;
+            }
+            r = make_int2((int)lo, (int)(d - lo));
+        }
+        s_fx[c] = r.x;
+        s_fy[c] = r.y;
+    }
+    __syncthreads();
+
+    // ---- walk the chunks ----
+    for (int c = g; c < p.nch; c += GPC) {
+        const int x0 = s_fx[c], y0 = s_fy[c], x1 = s_fx[c + 1], y1 = s_fy[c + 1];
+        bool head_pending = x0 >= 1 && y0 > s_rp[x0 - 1 - rp_base];  // first row began in an earlier chunk
+        int x = x0;
+        int next_mark = x < x1 ? s_rp[x - rp_base] : 0x7fffffff;  // non-zero index that marker x precedes
+        float acc[VEC];
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) acc[i] = 0.0f;
+
+        auto end_row = [&]() {
+            if (x >= 1) {  // marker x ends row x-1 (marker 0 ends nothing)
+                if (head_pending) {
+                    smem_put<VEC>(s_head + (size_t)c * SLAB + l * VEC, acc);
+                    head_pending = false;
+                } else if (active) {
+                    Lane<T, VEC>::store(Cm + (size_t)(x - 1) * p.dim + coff, acc);
+                }
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) acc[i] = 0.0f;
+            }
+            ++x;
+            next_mark = x < x1 ? s_rp[x - rp_base] : 0x7fffffff;
+        };
+
+        for (int k = y0; k < y1; k += U) {
+            typename Lane<T, VEC>::raw b[U];
+            float a[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                if (k + u < y1) {
+                    const int ci = s_col[k + u - y_base];
+                    a[u] = has_val ? to_float(s_val[k + u - y_base]) : 1.0f;
+                    if (active) b[u] = Lane<T, VEC>::load(Bm + (size_t)ci * p.dim + coff);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                if (k + u < y1) {
+                    while (next_mark <= k + u) end_row();
+                    if (active) Lane<T, VEC>::fma(acc, a[u], b[u]);
+                }
+            }
+        }
+        while (x < x1) end_row();
+        smem_put<VEC>(s_carry + (size_t)c * SLAB + l * VEC, acc);
+    }
+    __syncthreads();
+
+    // ---- in-tile fix-up: the group that walked chunk c finishes the row chunk c ended first ----
+    for (int c = g; c < p.nch; c += GPC) {
+        const int x0 = s_fx[c], x1 = s_fx[c + 1], y0 = s_fy[c];
+        if (!(x0 >= 1 && x1 > x0 && y0 > s_rp[x0 - 1 - rp_base])) continue;
+        int s = c;
+        while (s > 0 && s_fx[s] == x0) --s;
+        const bool from_prev = s_fx[0] == x0 && Y0 > s_rp[X0 - 1 - rp_base];  // row began before this tile
+        float sum[VEC];
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) sum[i] = 0.0f;
+        for (int q = s; q < c; ++q) vec_add<VEC>(sum, s_carry + (size_t)q * SLAB + l * VEC);
+        vec_add<VEC>(sum, s_head + (size_t)c * SLAB + l * VEC);
+        if (active) {
+            if (from_prev) gmem_put_f32<VEC>(p.thead + (size_t)t * p.dim + coff, sum);
+            else Lane<T, VEC>::store(Cm + (size_t)(x0 - 1) * p.dim + coff, sum);
+        }
+    }
+    // ---- tile carry: everything after the last marker of the tile ----
+    if (g == GPC - 1) {
+        const int xe = s_fx[p.nch];
+        int s = p.nch;
+        while (s > 0 && s_fx[s] == xe) --s;
+        float sum[VEC];
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) sum[i] = 0.0f;
+        for (int q = s; q < p.nch; ++q) vec_add<VEC>(sum, s_carry + (size_t)q * SLAB + l * VEC);
+        if (active) gmem_put_f32<VEC>(p.tcarry + (size_t)t * p.dim + coff, sum);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// cross-tile fix-up
+// ---------------------------------------------------------------------------------------------
+// Tile t needs a cross-tile fix-up when it ends (consumes a marker of) a row that began in an
+// earlier tile.  Returns that row, and in `s` the first tile whose carry belongs to it.
+__device__ __forceinline__ int fixup_candidate(const int2 *__restrict__ xy, const int *__restrict__ rp, int t, int &s) {
+    const int2 a = __ldg(xy + t), b = __ldg(xy + t + 1);
+    if (!(a.x >= 1 && b.x > a.x && a.y > __ldg(rp + a.x - 1))) return -1;
+    // f = first tile that starts with x == a.x (tiles f..t start inside the row); f >= 1
+    int lo = 0, hi = t;
+    if (__ldg(xy + t - 1).x != a.x) lo = t;
+    while (lo < hi) {
+        const int mid = (lo + hi) >> 1;
+        if (__ldg(xy + mid).x < a.x) lo = mid + 1;
+        else hi = mid;
+    }
+    s = lo - 1;
+    return a.x - 1;
+}
+
+__device__ __forceinline__ void store_c(float *p, float v) { *p = v; }
+__device__ __forceinline__ void store_c(__half *p, float v) { *p = __float2half_rn(v); }
+
+// one warp per tile; chains of up to long_chain tiles
+template <typename T>
+__global__ void fixup_short_kernel(const int2 *__restrict__ xy, const int *__restrict__ rp, const float *__restrict__ tcarry,
+                                   const float *__restrict__ thead, T *__restrict__ C, int n_tiles, int dim, int long_chain) {
+    const int t = 1 + (blockIdx.x * blockDim.x + threadIdx.x) / 32;
+    const int lane = threadIdx.x % 32;
+    if (t >= n_tiles) return;
+    int s;
+    const int row = fixup_candidate(xy, rp, t, s);
+    if (row < 0 || t - s > long_chain) return;
+    for (int j = lane; j < dim; j += 32) {
+        float sum = 0.0f;
+        for (int q = s; q < t; ++q) sum += tcarry[(size_t)q * dim + j];
+        sum += thead[(size_t)t * dim + j];
+        store_c(C + (size_t)row * dim + j, sum);
+    }
+}
+
+// lists the tiles whose chain is longer than long_chain (plan time)
+__global__ void fixup_list_long_kernel(const int2 *__restrict__ xy, const int *__restrict__ rp, int n_tiles, int long_chain,
+                                       int *__restrict__ list, int *__restrict__ count, int capacity) {
+    const int t = 1 + blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= n_tiles) return;
+    int s;
+    const int row = fixup_candidate(xy, rp, t, s);
+    if (row < 0 || t - s <= long_chain) return;
+    const int at = atomicAdd(count, 1);
+    if (at < capacity) list[at] = t;
+}
+
+// one block of kStrands warps per listed tile: strand g adds carries s+g, s+g+16, ... in order,
+// then strand 0 adds the strands in order and the tile's head last
+template <typename T>
+__global__ void __launch_bounds__(kStrands * 32) fixup_long_kernel(const int2 *__restrict__ xy, const int *__restrict__ rp,
+                                                                    const float *__restrict__ tcarry, const float *__restrict__ thead,
+                                                                    T *__restrict__ C, const int *__restrict__ list, int dim) {
+    __shared__ float part[kStrands][32];
+    const int t = list[blockIdx.x];
+    const int g = threadIdx.x / 32, lane = threadIdx.x % 32;
+    int s;
+    const int row = fixup_candidate(xy, rp, t, s);
+    if (row < 0) return;  // cannot happen for a listed tile
+    for (int j0 = 0; j0 < dim; j0 += 32) {
+        const int j = j0 + lane;
+        float sg = 0.0f;
+        if (j < dim)
+            for (int q = s + g; q < t; q += kStrands) sg += tcarry[(size_t)q * dim + j];
+        part[g][lane] = sg;
+        __syncthreads();
+        if (g == 0 && j < dim) {
+            float sum = 0.0f;
+#pragma unroll
+            for (int k = 0; k < kStrands; ++k) sum += part[k][lane];
+            sum += thead[(size_t)t * dim + j];
+            store_c(C + (size_t)row * dim + j, sum);
+        }
+        __syncthreads();
+    }
+}
+
+}  // namespace mps

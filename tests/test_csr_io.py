@@ -1,0 +1,128 @@
+"""The `.csr` text loader/writer and the binary sidecar (host code of the C ABI; no GPU needed).
+Grammar facts come from the reference's loader (src/MergePathSpMM.cu:130-173) and writers
+(scripts/npz_to_csr.py:21-28)."""
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+import cases
+
+
+def _write(path, text):
+    with open(path, "w", newline="") as f:
+        f.write(text)
+
+
+def test_reads_the_writers_format(tmp_path, mps):
+    p = str(tmp_path / "g.csr")
+    _write(p, "0,2,3,3,5,\n1,2,0,0,3,")  # trailing commas, no final newline
+    rp, col = mps.load_csr(p)
+    assert rp.tolist() == [0, 2, 3, 3, 5] and col.tolist() == [1, 2, 0, 0, 3]
+    assert rp.dtype == np.int32 and col.dtype == np.int32
+
+
+@pytest.mark.parametrize("text", [
+    "0,2,3,3,5\n1,2,0,0,3",        # no trailing commas
+    "0,2,3,3,5,\n1,2,0,0,3,\n",    # final newline
+    " 0, 2,\t3,3, 5,\n 1,2, 0,0,3,\nignored third line",  # blanks before numbers, extra line
+    "+0,2,3,3,5,\n1,2,0,0,3,",
+])
+def test_accepted_variants(tmp_path, mps, text):
+    p = str(tmp_path / "g.csr")
+    _write(p, text)
+    rp, col = mps.load_csr(p)
+    assert rp.tolist() == [0, 2, 3, 3, 5] and col.tolist() == [1, 2, 0, 0, 3]
+
+
+@pytest.mark.parametrize("text,code", [
+    ("0,2,3,3,5,\r\n1,2,0,0,3,", "FORMAT"),   # CRLF: the reference's stoi throws on the "\r" cell
+    ("0,2,,3,5,\n1,2,0,0,3,", "FORMAT"),      # empty cell
+    ("0,2,x,3,5,\n1,2,0,0,3,", "FORMAT"),
+    ("0,2,3,3,5,\n1,2,0,0,", "FORMAT"),       # nnz disagrees with line 2
+    ("0,2,1,3,5,\n1,2,0,0,3,", "FORMAT"),     # row_ptr decreases
+    ("0,2,3,3,5,\n1,2,0,0,4,", "FORMAT"),     # column out of range
+    ("1,2,3,3,5,\n1,2,0,0,3,", "FORMAT"),     # row_ptr[0] != 0
+    ("0,99999999999,\n1,", "FORMAT"),         # does not fit int32
+    ("", "FORMAT"),
+])
+def test_rejected_inputs(tmp_path, mps, text, code):
+    p = str(tmp_path / "g.csr")
+    _write(p, text)
+    with pytest.raises(mps.MpsError) as e:
+        mps.load_csr(p)
+    assert e.value.code == getattr(mps.capi, "ERR_" + code)
+
+
+def test_missing_file_is_an_error_not_minus_one_rows(tmp_path, mps):
+    with pytest.raises(mps.MpsError) as e:
+        mps.load_csr(str(tmp_path / "absent.csr"))
+    assert e.value.code == mps.capi.ERR_IO
+
+
+def test_empty_graph_and_no_nonzeros(tmp_path, mps):
+    p = str(tmp_path / "g.csr")
+    _write(p, "0,0,0,\n")
+    rp, col = mps.load_csr(p)
+    assert rp.tolist() == [0, 0, 0] and len(col) == 0
+
+
+def test_round_trip_and_writer_bytes(tmp_path, mps):
+    rp, col = cases.c1_rmat()
+    p = str(tmp_path / "c1.csr")
+    mps.save_csr(p, rp, col)
+    raw = open(p, "rb").read()
+    assert raw.count(b"\n") == 1 and raw.endswith(b",") and b"\r" not in raw
+    first, second = raw.split(b"\n")
+    assert first == (",".join(map(str, rp.tolist())) + ",").encode()   # what the reference's writers emit
+    assert second == (",".join(map(str, col.tolist())) + ",").encode()
+    for threads in (1, 3, 8):
+        rp2, col2 = mps.load_csr(p, threads)
+        assert np.array_equal(rp, rp2) and np.array_equal(col, col2)
+
+
+def test_parallel_parse_matches_single_thread_on_a_larger_file(tmp_path, mps, graphs):
+    rp, col = graphs.rmat_csr(15, 16, seed=4)   # ~0.5M nnz, several MB of text => many pieces
+    p = str(tmp_path / "big.csr")
+    mps.save_csr(p, rp, col)
+    a = mps.load_csr(p, 1)
+    b = mps.load_csr(p, 8)
+    assert np.array_equal(a[0], rp) and np.array_equal(a[1], col)
+    assert np.array_equal(b[0], rp) and np.array_equal(b[1], col)
+
+
+def test_reads_the_reference_converter_output(tmp_path, mps):
+    """The independent writer: scipy's coo->csr plus the cell-by-cell text of the reference's
+    scripts/npz_to_csr.py:13-28, restated here (the script itself is not shipped)."""
+    import scipy.sparse as sp
+    rng = np.random.default_rng(0)
+    src, dst = rng.integers(0, 300, 4000), rng.integers(0, 300, 4000)
+    m = sp.coo_matrix((np.ones(len(src)), (src, dst)), shape=(300, 300)).tocsr()
+    p = str(tmp_path / "conv.csr")
+    with open(p, "w") as f:
+        for e in m.indptr:
+            f.write(str(e) + ",")
+        f.write("\n")
+        for e in m.indices:
+            f.write(str(e) + ",")
+    rp, col = mps.load_csr(p)
+    assert np.array_equal(rp, m.indptr) and np.array_equal(col, m.indices)
+
+
+def test_binary_sidecar_round_trip(tmp_path, mps, graphs):
+    rp, col = cases.c2_batched(50)
+    val = graphs.gcn_values(rp, col)
+    p = str(tmp_path / "g.csr.bin")
+    mps.save_csr_bin(p, rp, col, val)
+    rp2, col2, val2 = mps.load_csr_bin(p)
+    assert np.array_equal(rp, rp2) and np.array_equal(col, col2) and np.array_equal(val, val2)
+    mps.save_csr_bin(p, rp, col, val.astype(np.float16))
+    assert mps.load_csr_bin(p)[2].dtype == np.float16
+    mps.save_csr_bin(p, rp, col, None)
+    assert mps.load_csr_bin(p)[2] is None
+    with open(p, "r+b") as f:
+        f.truncate(100)
+    with pytest.raises(mps.MpsError):
+        mps.load_csr_bin(p)

@@ -1,0 +1,331 @@
+"""Parity of the CUDA path (through the C ABI) with the oracle, on a B200.
+
+Three gates per case:
+  1. partition coordinates and the six schedule arrays: bit-exact with the reference's own
+     functions (golden vectors) and with the oracle's restatement;
+  2. C bit-exact with the CPU model of the kernel's summation order (oracle section 5);
+  3. C within tolerance of the fp64 loop: fp32 |d| <= 1e-6 + 1e-5*scale, fp16 1e-2, where
+     scale = sum_k |a_ik b_kj| (element-wise relative error is unbounded under cancellation; the
+     fraction of elements that also meet the literal |d| <= 1e-6 + 1e-5*|ref| form is reported
+     for the benchmark configurations).
+"""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import cases
+
+pytestmark = pytest.mark.gpu
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "reference_partition.npz")
+
+
+def _dev(a, cuda):
+    return None if a is None else torch.from_numpy(np.ascontiguousarray(a)).to(cuda)
+
+
+def _bits(a):
+    return a.view(np.uint16 if a.dtype == np.float16 else np.uint32)
+
+
+def _run(mps, cuda, rp, col, val, B, cost, tune=None, tpw=1):
+    n, nnz, dim = len(rp) - 1, len(col), B.shape[1]
+    half = B.dtype == np.float16
+    plan = mps.Plan(n, nnz, dim, mps.F16 if half else mps.F32, cost, tpw, device=cuda)
+    if tune:
+        plan.tune(**tune)
+    d_rp, d_col, d_val, d_B = _dev(rp, cuda), _dev(col, cuda), _dev(val, cuda), _dev(B, cuda)
+    plan.partition(d_rp)
+    out = torch.full((n, dim), float("nan"), dtype=d_B.dtype, device=cuda)  # every element must be overwritten
+    plan.spmm(d_rp, d_col, d_val, d_B, out=out)
+    plan.sync_check()
+    info = plan.info()
+    plan.close()
+    return out.cpu().numpy(), info
+
+
+def _check(orc, rp, col, val, B, got, info, cost, tol):
+    half = B.dtype == np.float16
+    model = orc.tile_model(rp, col, val, B, cost, info["chunks_per_tile"], info["long_chain"], is_half=half)
+    assert not np.isnan(got.astype(np.float32)).any(), "some element of C was never written"
+    same = _bits(got) == _bits(model)
+    assert same.all(), f"{(~same).sum()} elements differ from the CPU model (first at {np.argwhere(~same)[0]})"
+    ref = orc.spmm_f64(rp, col, val, B, is_half=half)
+    scale = orc.spmm_abs_f64(rp, col, val, B, is_half=half)
+    err = np.abs(got.astype(np.float64) - ref)
+    bound = 1e-6 + tol * (np.maximum(scale, np.abs(ref)) if half else scale)
+    assert (err <= bound).all(), f"max error {err.max()} beyond tolerance"
+    return float((err <= 1e-6 + tol * np.abs(ref)).mean())
+
+
+# ------------------------------------------------------------------ partition / schedule
+
+def test_partition_and_schedule_bit_exact_with_reference_vectors(mps, orc, cuda):
+    g = np.load(GOLDEN)
+    names = sorted({k.split("/")[0] for k in g.files})
+    checked = 0
+    for name in names:
+        rp = g[f"{name}/row_ptr"]
+        d_rp = _dev(rp, cuda)
+        for key in [k for k in g.files if k.startswith(name + "/cost") and k.endswith("/xy")]:
+            cost = int(key.split("/")[1][4:])
+            p = int(g[f"{name}/cost{cost}/n_chunks"])
+            assert mps.chunk_count(len(rp) - 1, int(rp[-1]), cost)[0] == p
+            xy = mps.partition_device(d_rp, p).cpu().numpy()
+            assert np.array_equal(xy, g[key]), (name, cost)
+            six = mps.schedule_device(d_rp, p).cpu().numpy()
+            assert np.array_equal(six, g[f"{name}/cost{cost}/six"]), (name, cost)
+            checked += 1
+    assert checked >= 30
+
+
+def test_partition_bit_exact_with_oracle_on_a_mid_size_graph(mps, orc, graphs, cuda):
+    rp, _ = graphs.rmat_csr(17, 16, seed=2)
+    d_rp = _dev(rp, cuda)
+    for cost in (4, 8, 16, 32):
+        p, _ = mps.chunk_count(len(rp) - 1, int(rp[-1]), cost)
+        assert np.array_equal(mps.partition_device(d_rp, p).cpu().numpy(), orc.partition(rp, p)), cost
+        assert np.array_equal(mps.schedule_device(d_rp, p).cpu().numpy(), orc.schedule(rp, p)), cost
+
+
+# ------------------------------------------------------------------ SpMM, benchmark configurations
+
+@pytest.mark.parametrize("dim", [16, 32, 64, 128])
+@pytest.mark.parametrize("cost", [4, 8, 16, 32])
+def test_c1_rmat_fp32(mps, orc, graphs, cuda, dim, cost):
+    rp, col = cases.c1_rmat()
+    val = graphs.gcn_values(rp, col)
+    B = graphs.dense_uniform(len(rp) - 1, dim, seed=1)
+    got, info = _run(mps, cuda, rp, col, val, B, cost, tpw=32)  # tpw 32 as configuration 1 asks: clamped
+    assert info["threads_per_warp"] == (32 // dim if dim <= 32 else 1)
+    _check(orc, rp, col, val, B, got, info, cost, 1e-5)
+
+
+def test_c1_unit_values_as_the_csr_file_has_none(mps, orc, graphs, cuda):
+    rp, col = cases.c1_rmat()
+    B = graphs.dense_uniform(len(rp) - 1, 16, seed=1)
+    got, info = _run(mps, cuda, rp, col, None, B, 8)
+    _check(orc, rp, col, None, B, got, info, 8, 1e-5)
+    ones = np.ones(len(col), np.float32)
+    got2, _ = _run(mps, cuda, rp, col, ones, B, 8)
+    assert np.array_equal(_bits(got), _bits(got2))
+
+
+def test_c2_batched_structured(mps, orc, graphs, cuda):
+    rp, col = cases.c2_batched()
+    val = graphs.gcn_values(rp, col)
+    B = graphs.dense_uniform(len(rp) - 1, 16, seed=1)
+    got, info = _run(mps, cuda, rp, col, val, B, 8)
+    frac = _check(orc, rp, col, val, B, got, info, 8, 1e-5)
+    assert frac > 0.999  # short rows: the literal element-wise form holds almost everywhere
+
+
+@pytest.mark.parametrize("dim", [128, 64, 8])
+def test_c4_fp16_storage_fp32_accumulate(mps, orc, graphs, cuda, dim):
+    rp, col = cases.c1_rmat()
+    val = graphs.gcn_values(rp, col, "f16")
+    B = graphs.dense_normal_f16(len(rp) - 1, dim, seed=1)
+    got, info = _run(mps, cuda, rp, col, val, B, 8)
+    assert got.dtype == np.float16
+    _check(orc, rp, col, val, B, got, info, 8, 1e-2)
+    # against an fp32 run of the same operands: within 1e-2 relative of the result's scale
+    got32, _ = _run(mps, cuda, rp, col, val.astype(np.float32), B.astype(np.float32), 8)
+    scale = orc.spmm_abs_f64(rp, col, val, B, is_half=True)
+    assert (np.abs(got.astype(np.float64) - got32) <= 1e-6 + 1e-2 * np.maximum(scale, np.abs(got32))).all()
+
+
+# ------------------------------------------------------------------ shapes and edge cases
+
+@pytest.mark.parametrize("dim", [4, 8, 12, 24, 48, 96, 100, 160, 256, 260, 1, 5, 7, 33, 70])
+def test_generic_dims_fp32(mps, orc, graphs, cuda, dim):
+    rp, col = cases.c2_batched(120)
+    val = graphs.gcn_values(rp, col)
+    B = graphs.dense_uniform(len(rp) - 1, dim, seed=2)
+    got, info = _run(mps, cuda, rp, col, val, B, 8)
+    _check(orc, rp, col, val, B, got, info, 8, 1e-5)
+
+
+@pytest.mark.parametrize("dim", [16, 40, 256, 264, 3, 20])
+def test_generic_dims_fp16(mps, orc, graphs, cuda, dim):
+    rp, col = cases.c2_batched(120)
+    val = graphs.gcn_values(rp, col, "f16")
+    B = graphs.dense_normal_f16(len(rp) - 1, dim, seed=2)
+    got, info = _run(mps, cuda, rp, col, val, B, 8)
+    _check(orc, rp, col, val, B, got, info, 8, 1e-2)
+
+
+@pytest.mark.parametrize("name", sorted(cases.edge_cases().keys()))
+def test_edge_case_graphs(mps, orc, cuda, name):
+    rp, col = cases.edge_cases()[name]
+    n = len(rp) - 1
+    n_cols = max(int(col.max()) + 1 if len(col) else 1, n)
+    rng = np.random.default_rng(3)
+    val = rng.uniform(-1, 1, len(col)).astype(np.float32)
+    for dim in (12, 64, 5):
+        B = rng.uniform(-1, 1, (n_cols, dim)).astype(np.float32)
+        for cost, tune in ((1, None), (3, dict(chunks_per_tile=8)), (8, None), (8, dict(chunks_per_tile=1)), (32, dict(unroll=4))):
+            got, info = _run(mps, cuda, rp, col, val, B, cost, tune)
+            _check(orc, rp, col, val, B, got, info, cost, 1e-5)
+
+
+def test_long_rows_take_the_strand_fixup(mps, orc, cuda):
+    rp, col = cases.edge_cases()["one_giant_row"]
+    rng = np.random.default_rng(5)
+    B = rng.uniform(-1, 1, (6000, 64)).astype(np.float32)
+    got, info = _run(mps, cuda, rp, col, None, B, 1, dict(chunks_per_tile=2))
+    assert info["long_rows"] >= 1 and info["kernels_per_call"] == 3
+    _check(orc, rp, col, None, B, got, info, 1, 1e-5)
+
+
+@pytest.mark.parametrize("tune", [dict(chunks_per_tile=16), dict(chunks_per_tile=48), dict(chunks_per_tile=200, unroll=4),
+                                  dict(unroll=8), dict(bulk_staging=False)])
+def test_tuning_knobs_keep_parity(mps, orc, graphs, cuda, tune):
+    rp, col = cases.c1_rmat()
+    val = graphs.gcn_values(rp, col)
+    B = graphs.dense_uniform(len(rp) - 1, 64, seed=1)
+    got, info = _run(mps, cuda, rp, col, val, B, 8, tune)
+    _check(orc, rp, col, val, B, got, info, 8, 1e-5)
+
+
+def test_bulk_and_plain_staging_agree_and_unaligned_inputs_work(mps, orc, graphs, cuda):
+    rp, col = cases.c1_rmat()
+    val = graphs.gcn_values(rp, col)
+    n, nnz = len(rp) - 1, len(col)
+    B = graphs.dense_uniform(n, 32, seed=1)
+    a, info = _run(mps, cuda, rp, col, val, B, 8)
+    b, _ = _run(mps, cuda, rp, col, val, B, 8, dict(bulk_staging=False))
+    assert np.array_equal(_bits(a), _bits(b))
+    # col_idx / val / row_ptr that start 4 bytes into an allocation: 16-byte staging is not possible,
+    # the plain-load path must take over and give the same bits
+    d_B = _dev(B, cuda)
+    pad = lambda x: torch.cat([torch.zeros(1, dtype=x.dtype, device=cuda), x])[1:]
+    d_rp, d_col, d_val = pad(_dev(rp, cuda)), pad(_dev(col, cuda)), pad(_dev(val, cuda))
+    assert d_col.data_ptr() % 16 == 4
+    plan = mps.Plan(n, nnz, 32, mps.F32, 8, device=cuda)
+    plan.partition(d_rp)
+    c = plan.spmm(d_rp, d_col, d_val, d_B).cpu().numpy()
+    plan.sync_check()
+    assert np.array_equal(_bits(a), _bits(c))
+    # B that is not 16-byte aligned cannot be gathered with 128-bit loads: a clear error, no fault
+    with pytest.raises(mps.MpsError) as e:
+        plan.spmm(d_rp, d_col, d_val, pad(d_B.reshape(-1))[: (n - 1) * 32].reshape(n - 1, 32))
+    assert e.value.code == mps.capi.ERR_ALIGN
+    plan.close()
+
+
+def test_deterministic_and_repeat_safe(mps, graphs, cuda):
+    """Two launches give the same bits and a second launch into the same C does not accumulate
+    (the reference's atomics do both wrong: src/MergePathSpMM.cu:204,231-243)."""
+    rp, col = graphs.rmat_csr(16, 32, seed=5)
+    val = graphs.gcn_values(rp, col)
+    n, nnz = len(rp) - 1, len(col)
+    d_rp, d_col, d_val = _dev(rp, cuda), _dev(col, cuda), _dev(val, cuda)
+    d_B = _dev(graphs.dense_uniform(n, 64, seed=6), cuda)
+    plan = mps.Plan(n, nnz, 64, mps.F32, 8, device=cuda)
+    plan.partition(d_rp)
+    c1 = plan.spmm(d_rp, d_col, d_val, d_B)
+    first = c1.clone()
+    for _ in range(5):
+        plan.spmm(d_rp, d_col, d_val, d_B, out=c1)
+    c2 = plan.spmm(d_rp, d_col, d_val, d_B)
+    plan.sync_check()
+    assert torch.equal(first, c1) and torch.equal(first, c2)
+    plan.close()
+
+
+def test_errors_are_codes_not_faults(mps, cuda):
+    plan = mps.Plan(10, 20, 16, mps.F32, 8, device=cuda)
+    z = torch.zeros(64, dtype=torch.int32, device=cuda)
+    f = torch.zeros(10 * 16, dtype=torch.float32, device=cuda)
+    with pytest.raises(mps.MpsError) as e:
+        plan.spmm(z, z, None, f, out=f.clone())
+    assert e.value.code == mps.capi.ERR_STATE  # partition not called yet
+    with pytest.raises(mps.MpsError) as e:
+        plan.tune(unroll=5)
+    assert e.value.code == mps.capi.ERR_ARG
+    plan.close()
+    with pytest.raises(mps.MpsError) as e:
+        mps.Plan(10, 20, 0, mps.F32, 8, device=cuda)
+    assert e.value.code == mps.capi.ERR_ARG
+
+
+def test_host_buffer_call_equals_device_path(mps, orc, graphs, cuda):
+    rp, col = cases.c1_rmat()
+    val = graphs.gcn_values(rp, col)
+    B = graphs.dense_uniform(len(rp) - 1, 64, seed=1)
+    dev, info = _run(mps, cuda, rp, col, val, B, 8)
+    host = mps.spmm_host(rp, col, val, B, cost=8)
+    assert np.array_equal(_bits(dev), _bits(host))
+    host2 = mps.spmm_host(rp, col, val, B, cost=8)   # workspace reuse
+    assert np.array_equal(_bits(host), _bits(host2))
+    Bh = B.astype(np.float16)
+    vh = val.astype(np.float16)
+    devh, _ = _run(mps, cuda, rp, col, vh, Bh, 8)
+    assert np.array_equal(_bits(devh), _bits(mps.spmm_host(rp, col, vh, Bh, cost=8)))
+    mps.capi.lib().mps_host_workspace_release()
+
+
+# ------------------------------------------------------------------ slabs
+
+def test_row_slabs_are_bit_identical_to_their_own_model_and_close_to_the_whole(mps, orc, graphs, cuda):
+    rp, col = cases.c1_rmat()
+    val = graphs.gcn_values(rp, col)
+    n = len(rp) - 1
+    B = graphs.dense_uniform(n, 32, seed=1)
+    whole, _ = _run(mps, cuda, rp, col, val, B, 8)
+    for g in (2, 3, 8):
+        b = mps.slab_bounds(rp, g)
+        parts = []
+        for s in range(g):
+            r0, r1 = int(b[s]), int(b[s + 1])
+            srp = mps.slab_rebase(rp, r0, r1)
+            scol, sval = col[rp[r0]:rp[r1]], val[rp[r0]:rp[r1]]
+            got, info = _run(mps, cuda, srp, scol, sval, B, 8)
+            model = orc.tile_model(srp, scol, sval, B, 8, info["chunks_per_tile"], info["long_chain"])
+            assert np.array_equal(_bits(got), _bits(model))
+            parts.append(got)
+        cat = np.concatenate(parts)
+        scale = orc.spmm_abs_f64(rp, col, val, B)
+        assert (np.abs(cat.astype(np.float64) - whole) <= 1e-6 + 1e-5 * scale).all()
+
+
+# ------------------------------------------------------------------ full size, size-independent properties
+
+def test_full_size_rmat21_properties(mps, graphs, cuda):
+    """Benchmark configuration 3 (2^21 nodes, ~67M nnz, dim 64), graph built on the device.
+    Exact checks that need no oracle pass over 67M non-zeros:
+      - unit values and B == 1: every C element equals its row's length (exact in fp32);
+      - B = e_j columns (one-hot rows): C counts, per row, the neighbours in each residue class;
+      - linearity: A(B1 + B2) == A B1 + A B2 to rounding; two runs are bit-identical."""
+    rp, col = graphs.rmat_csr(21, 32, seed=0, device=cuda)
+    n, nnz = rp.numel() - 1, col.numel()
+    assert n == 1 << 21 and 55_000_000 < nnz <= 2 * (1 << 25) + n
+    dim = 64
+    plan = mps.Plan(n, nnz, dim, mps.F32, 8, device=cuda)
+    plan.partition(rp)
+    ones = torch.ones((n, dim), dtype=torch.float32, device=cuda)
+    c = plan.spmm(rp, col, None, ones)
+    plan.sync_check()
+    lens = (rp[1:] - rp[:-1]).to(torch.float32)
+    assert torch.equal(c, lens[:, None].expand(n, dim))
+    onehot = torch.zeros((n, dim), dtype=torch.float32, device=cuda)
+    onehot[torch.arange(n, device=cuda), torch.arange(n, device=cuda) % dim] = 1.0
+    c = plan.spmm(rp, col, None, onehot)
+    rows = torch.repeat_interleave(torch.arange(n, device=cuda), (rp[1:] - rp[:-1]).to(torch.int64))
+    want = torch.zeros(n * dim, dtype=torch.float32, device=cuda)
+    want.index_add_(0, rows * dim + (col.to(torch.int64) % dim), torch.ones(nnz, dtype=torch.float32, device=cuda))
+    assert torch.equal(c, want.reshape(n, dim))
+    del onehot, want, rows, ones
+    val = graphs.gcn_values(rp, col)
+    b1 = graphs.dense_uniform(n, dim, seed=1, device=cuda)
+    b2 = graphs.dense_uniform(n, dim, seed=2, device=cuda)
+    c1 = plan.spmm(rp, col, val, b1)
+    c2 = plan.spmm(rp, col, val, b2)
+    c12 = plan.spmm(rp, col, val, b1 + b2)
+    again = plan.spmm(rp, col, val, b1)
+    plan.sync_check()
+    assert torch.equal(c1, again)
+    # GCN values make every row an average-like sum with sum_k |a_ik| <= sqrt(deg_i); |b| < 2
+    assert (c12 - (c1 + c2)).abs().max().item() < 1e-4
+    plan.close()

@@ -1,0 +1,86 @@
+"""The new kernels against the reference's own kernels, compiled unmodified into oracle/_ref/ and
+driven the only way they compute a correct SpMM: degrees == 1 (unit-valued A; the tail partial
+hard-codes a source factor of 1, src/MergePathSpMM.cu:468,562), zeroed C, one launch (partial rows
+are added with atomics, :204,231), threads_per_warp <= 32/dim, schedule arrays padded (the grid
+formula at :230 lets the last warp read past them).  Row 0 is compared separately: the zero
+sentinel drops chunk 0's tail share of it (:365-369,467)."""
+import ctypes as C
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import cases
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _ref_lib(half):
+    path = os.path.join(ROOT, "oracle", "_ref", "libref_mergepath_f16.so" if half else "libref_mergepath_f32.so")
+    if not os.path.exists(path):
+        pytest.skip("oracle/_ref is not built (needs the reference tree at build time)")
+    lib = C.CDLL(path)
+    lib.refh_launch.argtypes = [C.c_void_p] * 5 + [C.POINTER(C.c_void_p)] + [C.c_int] * 4
+    return lib
+
+
+def _ref_spmm(lib, mps, cuda, rp, col, B, cost, tpw):
+    """Schedule from this library's device builder (bit-exact with generate_mp_sched), kernel = the reference's."""
+    n, nnz, dim = len(rp) - 1, len(col), B.shape[1]
+    p, ipt = mps.chunk_count(n, nnz, cost)
+    d_rp = torch.from_numpy(rp).to(cuda)
+    d_col = torch.from_numpy(col).to(cuda)
+    six = mps.schedule_device(d_rp, p)
+    padded = torch.zeros((6, p + 64), dtype=torch.int32, device=cuda)
+    padded[:, :p] = six
+    deg = torch.ones(n + 1, dtype=torch.int32, device=cuda)
+    d_B = torch.zeros((n + 1, dim), dtype=torch.from_numpy(B).dtype, device=cuda)
+    d_B[:n] = torch.from_numpy(B).to(cuda)
+    d_C = torch.zeros((n + 1, dim), dtype=d_B.dtype, device=cuda)
+    ptrs = (C.c_void_p * 6)(*[padded[i].data_ptr() for i in range(6)])
+    torch.cuda.synchronize()
+    rc = lib.refh_launch(d_C.data_ptr(), d_B.data_ptr(), d_rp.data_ptr(), d_col.data_ptr(), deg.data_ptr(), ptrs, n, dim, p, tpw)
+    assert rc == 0, f"reference launch failed with CUDA error {rc}"
+    return d_C[:n].cpu().numpy(), ipt
+
+
+@pytest.mark.parametrize("dim,tpw", [(16, 2), (32, 1), (64, 1), (128, 1)])
+def test_fp32_against_reference_kernel(mps, orc, graphs, cuda, dim, tpw):
+    rp, col = cases.c1_rmat()
+    n = len(rp) - 1
+    B = graphs.dense_uniform(n, dim, seed=1)
+    lib = _ref_lib(False)
+    ref, ipt = _ref_spmm(lib, mps, cuda, rp, col, B, 8, tpw)
+    got = mps.spmm(torch.from_numpy(rp).to(cuda), torch.from_numpy(col).to(cuda), None, torch.from_numpy(B).to(cuda), cost=8).cpu().numpy()
+    scale = orc.spmm_abs_f64(rp, col, None, B)
+    ok = np.abs(got.astype(np.float64) - ref) <= 1e-6 + 1e-5 * scale
+    assert ok[1:].all()
+    literal = (np.abs(got[1:] - ref[1:]) <= 1e-6 + 1e-5 * np.abs(ref[1:])).mean()
+    assert literal > 0.99
+    # row 0: the reference lacks exactly the first ipt-1 contributions
+    lost = B[col[: ipt - 1]].astype(np.float64).sum(axis=0)
+    assert np.allclose(got[0].astype(np.float64) - ref[0], lost, rtol=1e-4, atol=1e-3)
+    # and the oracle's sequential emulation of the reference kernel agrees with the real one
+    emu = orc.ref_kernel_emulate_f32(rp, col, np.ones(n + 1, np.int32), B, orc.chunk_count(n, len(col), 8))
+    assert (np.abs(emu.astype(np.float64) - ref) <= 1e-6 + 1e-5 * scale).all()
+
+
+def test_fp16_against_reference_kernel_reported_with_its_own_error(mps, orc, graphs, cuda):
+    """The reference fp16 kernel accumulates in fp16; the new one in fp32.  Both are compared with
+    the fp64 loop: the new kernel must meet 1e-2, and must not be worse than the reference."""
+    rp, col = cases.c2_batched(300)   # short rows: fp16 accumulation stays meaningful
+    n = len(rp) - 1
+    B = graphs.dense_normal_f16(n, 64, seed=1)
+    lib = _ref_lib(True)
+    ref, _ = _ref_spmm(lib, mps, cuda, rp, col, B, 8, 1)
+    got = mps.spmm(torch.from_numpy(rp).to(cuda), torch.from_numpy(col).to(cuda), None, torch.from_numpy(B).to(cuda), cost=8).cpu().numpy()
+    truth = orc.spmm_f64(rp, col, None, B, is_half=True)
+    scale = np.maximum(orc.spmm_abs_f64(rp, col, None, B, is_half=True), np.abs(truth))
+    e_new = np.abs(got.astype(np.float64) - truth)
+    e_ref = np.abs(ref.astype(np.float64) - truth)
+    rows = np.arange(n) != 0
+    assert (e_new <= 1e-6 + 1e-2 * scale).all()
+    assert (np.abs(got.astype(np.float64) - ref)[rows] <= 1e-6 + 2e-2 * scale[rows]).all()
+    assert e_new[rows].mean() <= e_ref[rows].mean() + 1e-9
