@@ -1,0 +1,461 @@
+#!/usr/bin/env python
+"""Bench of the merge-path CSR SpMM hot path: SpMM GFLOP/s = 2*nnz*dim / t.
+
+    python bench.py [--gpus N --steps K --warmup W]            this library (one rank per GPU)
+    python bench.py --impl reference ...                       host-CPU arm (see below)
+    python bench.py --impl reference-gpu ...                   the reference's CUDA kernels on the GPU
+
+Workload (seeded, synthetic; stands in for the reference's public graph suite): an R-MAT graph
+with 2^21 nodes per GPU and average degree 32 (~67M non-zeros per GPU), GCN-normalised fp32
+values, B with `dim` = 64 fp32 columns uniform in [-1,1).  With N GPUs the graph has 2^21*N nodes,
+A is cut into N row slabs of equal non-zero count, B is replicated, each rank multiplies its slab
+(weak scaling, no collective on the data path).  One step = one SpMM of the whole matrix.
+
+The reference has no CPU SpMM (its hot path is CUDA); the host arm that `--impl reference` times is
+the oracle's OpenMP CSR loop on all host cores (kind "port").  The reference's own kernels,
+compiled unmodified into oracle/_ref/, are timed on the GPU by `--impl reference-gpu`, and the
+default run embeds that number as "reference_gpu" so both baselines sit beside the result.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+import __graft_entry__ as entry  # noqa: E402
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-gpu"])
+    ap.add_argument("--scale", type=int, default=21, help="log2 of nodes per GPU")
+    ap.add_argument("--avg-degree", type=int, default=32)
+    ap.add_argument("--dim", type=int, default=64)
+    ap.add_argument("--cost", type=int, default=0, help="merge items per chunk (0 = the default of this build)")
+    ap.add_argument("--tpw", type=int, default=1, help="threads_per_warp, accepted as the reference's CLI does")
+    ap.add_argument("--dtype", default="f32", choices=["f32", "f16"])
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--chunks-per-tile", type=int, default=0)
+    ap.add_argument("--unroll", type=int, default=0)
+    ap.add_argument("--no-bulk", action="store_true")
+    ap.add_argument("--e2e-steps", type=int, default=3)
+    ap.add_argument("--skip-baselines", action="store_true", help="leave out cpu_baseline and reference_gpu (tuning runs)")
+    ap.add_argument("--gather-c", action="store_true", help="also time an NCCL all-gather of the C slabs (N > 1)")
+    return ap.parse_args()
+
+
+DEFAULT_COST = 16
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons every 200 ms while the timed region runs."""
+    Q = "clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown," \
+        "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap,power.draw"
+
+    def __init__(self, index: int):
+        self.rows, self.proc, self.index = [], None, index
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q, "--format=csv,noheader,nounits",
+                                          "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *a):
+        if self.proc:
+            time.sleep(0.25)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[0])); mx.append(float(r[1]))
+            except Exception:
+                continue
+            for i, nm in enumerate(names):
+                if len(r) > 2 + i and r[2 + i].lower().startswith("active"):
+                    reasons.add(nm)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(mx)), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def dist_setup(args):
+    import torch
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        import torch.distributed as dist
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    else:
+        torch.cuda.set_device(local)
+    return rank, world, local
+
+
+def barrier(world):
+    import torch
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+def max_over_ranks(x: float, world: int) -> float:
+    import torch
+    if world == 1:
+        return x
+    import torch.distributed as dist
+    t = torch.tensor([x], dtype=torch.float64, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def sum_over_ranks(x: float, world: int) -> float:
+    import torch
+    if world == 1:
+        return x
+    import torch.distributed as dist
+    t = torch.tensor([x], dtype=torch.float64, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.SUM)
+    return float(t.item())
+
+
+def build_workload(args, world, rank, dev):
+    """Whole graph on this rank's GPU (same bits on every rank), then this rank's row slab."""
+    import torch
+    from mergepath_spmm_b200 import graphs
+    mps = entry.load_package()
+    scale = args.scale + int(round(np.log2(world)))
+    assert 1 << (scale - args.scale) == world, "--gpus must be a power of two"
+    rp, col = graphs.rmat_csr(scale, args.avg_degree, args.seed, device=dev)
+    n, nnz = rp.numel() - 1, col.numel()
+    half = args.dtype == "f16"
+    val = graphs.gcn_values(rp, col, "f16" if half else "f32")
+    if world > 1:
+        bounds = mps.slab_bounds(rp.cpu().numpy(), world)
+        r0, r1 = int(bounds[rank]), int(bounds[rank + 1])
+        k0, k1 = int(rp[r0].item()), int(rp[r1].item())
+        s_rp = (rp[r0:r1 + 1] - k0).contiguous()
+        s_col, s_val = col[k0:k1].clone(), val[k0:k1].clone()
+        del rp, col, val
+    else:
+        r0, r1, s_rp, s_col, s_val = 0, n, rp, col, val
+    torch.cuda.empty_cache()
+    if half:
+        B = graphs.dense_normal_f16(n, args.dim, args.seed + 1, device=dev)
+    else:
+        B = graphs.dense_uniform(n, args.dim, args.seed + 1, device=dev)
+    return dict(n=n, nnz=nnz, scale=scale, r0=r0, r1=r1, rp=s_rp, col=s_col, val=s_val, B=B, half=half)
+
+
+def workload_name(args, world):
+    return f"rmat{args.scale + int(round(np.log2(world)))}_deg{args.avg_degree}_gcn_{args.dtype}_dim{args.dim}"
+
+
+def run_ours(args):
+    import torch
+    rank, world, local = dist_setup(args)
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}; launch with torch.distributed.run"
+    dev = torch.device("cuda", local)
+    mps = entry.load_package()
+    cost = args.cost or DEFAULT_COST
+    w = build_workload(args, world, rank, dev)
+    n_slab, nnz_slab = w["r1"] - w["r0"], w["col"].numel()
+    dt = mps.F16 if w["half"] else mps.F32
+    plan = mps.Plan(n_slab, nnz_slab, args.dim, dt, cost, args.tpw, device=dev)
+    if args.chunks_per_tile or args.unroll or args.no_bulk:
+        plan.tune(args.chunks_per_tile, args.unroll, not args.no_bulk)
+    t0 = time.perf_counter()
+    plan.partition(w["rp"])
+    torch.cuda.synchronize()
+    partition_ms = (time.perf_counter() - t0) * 1e3
+    info = plan.info()
+    C_out = torch.empty((n_slab, args.dim), dtype=w["B"].dtype, device=dev)
+
+    for _ in range(max(args.warmup, 3)):
+        plan.spmm(w["rp"], w["col"], w["val"], w["B"], out=C_out)
+    plan.sync_check()
+
+    # ---- timed region: K steps, CUDA events on the launching stream, barrier + sync on both sides ----
+    plan.profile(True)
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier(world)
+    with ClockSampler(local) as clocks:
+        ev0.record()
+        for _ in range(args.steps):
+            plan.spmm(w["rp"], w["col"], w["val"], w["B"], out=C_out)
+        ev1.record()
+        barrier(world)
+    ms_total = max_over_ranks(ev0.elapsed_time(ev1), world)
+    tile_ms, tile_launches = plan.profile_read()
+    plan.profile(False)
+    plan.sync_check()
+    ms_step = ms_total / args.steps
+    flops = 2.0 * w["nnz"] * args.dim
+    value = flops / (ms_step * 1e-3) / 1e9
+
+    # ---- roofline of the dominant kernel (the tile kernel), this rank's slab ----
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        pass
+    peak = float(peaks.get("hbm_gbs", 6650.0))
+    alg = mps.algorithmic_bytes(n_slab, nnz_slab, args.dim, dt, True)
+    tile_ms_avg = tile_ms / max(tile_launches, 1)
+    achieved = alg / (tile_ms_avg * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4),
+                "traffic": None, "kernel": "spmm_tile_kernel", "kernel_ms": round(tile_ms_avg, 4),
+                "algorithmic_bytes": alg, "peak_source": "measured (MEASURED_PEAKS.json)" if peaks else "fallback 6650 GB/s",
+                "step_frac": round(alg / (ms_step * 1e-3) / 1e9 / peak, 4)}
+    tpath = os.path.join(ROOT, "profiles", "traffic.json")
+    if os.path.exists(tpath):
+        try:
+            tj = json.load(open(tpath)).get(workload_name(args, 1))
+            if tj and world == 1:
+                roofline["traffic"] = tj["dram_bytes_per_launch"]
+        except Exception:
+            pass
+
+    # ---- end to end through the host-buffer C-ABI call: pinned host inputs -> C in pinned host memory ----
+    h = {k: (w[k].cpu().pin_memory() if w[k] is not None else None) for k in ("rp", "col", "val", "B")}
+    h_C = torch.empty((n_slab, args.dim), dtype=w["B"].dtype).pin_memory()
+
+    def e2e_call():
+        capi = mps.capi
+        capi.check(capi.lib().mps_spmm_host(n_slab, w["n"], nnz_slab, args.dim, dt, cost, args.tpw, C.c_void_p(h["rp"].data_ptr()),
+                                            C.c_void_p(h["col"].data_ptr()), C.c_void_p(h["val"].data_ptr()),
+                                            C.c_void_p(h["B"].data_ptr()), C.c_void_p(h_C.data_ptr())))
+    del C_out
+    e2e_call()  # warm: workspace allocation
+    barrier(world)
+    t0 = time.perf_counter()
+    for _ in range(args.e2e_steps):
+        e2e_call()
+    barrier(world)
+    e2e_s = max_over_ranks((time.perf_counter() - t0) / args.e2e_steps, world)
+    h2d = sum(h[k].numel() * h[k].element_size() for k in h if h[k] is not None)
+    d2h = h_C.numel() * h_C.element_size()
+    e2e = {"value": round(flops / e2e_s / 1e9, 2), "unit": "GFLOP/s", "h2d_bytes_per_step": int(sum_over_ranks(h2d, world)),
+           "d2h_bytes_per_step": int(sum_over_ranks(d2h, world)), "ms_per_step": round(e2e_s * 1e3, 3), "steps": args.e2e_steps}
+    mps.capi.lib().mps_host_workspace_release()
+
+    out = {
+        "metric": "SpMM GFLOP/s (2*nnz*dim/t)", "value": round(value, 2), "unit": "GFLOP/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f16 storage / f32 accumulate" if w["half"] else "f32", "data": "synthetic",
+        "config": {"workload": workload_name(args, world), "nodes": w["n"], "nnz": w["nnz"], "dim": args.dim, "cost": cost,
+                   "threads_per_warp": info["threads_per_warp"], "values": "gcn", "parallelism": f"row-slabs x{world}, B replicated",
+                   "l2": "inputs larger than L2 (B and A each > 126 MB)", "chunks_per_tile": info["chunks_per_tile"],
+                   "items_per_chunk": info["items_per_chunk"], "unroll": info["unroll"], "tiles": info["n_tiles"],
+                   "long_rows": info["long_rows"]},
+        "roofline": roofline, "e2e": e2e, "gpu_launches": args.steps * info["kernels_per_call"],
+        "clocks": clocks.summary(), "partition_ms": round(partition_ms, 3),
+        "hbm_algorithmic_gbs": round(sum_over_ranks(alg, world) / (ms_step * 1e-3) / 1e9, 1),
+    }
+
+    if args.gather_c and world > 1:
+        out["gather_c_ms"] = time_gather_c(w, args, world, rank, dev)
+
+    if rank == 0 and world == 1 and not args.skip_baselines:
+        host = {k: (h[k].numpy() if h[k] is not None else None) for k in h}
+        out["cpu_baseline"] = cpu_baseline(host, args.dim, w["nnz"], w["half"])
+        try:
+            out["reference_gpu"] = reference_gpu(w, args, dev)
+        except Exception as e:  # the checker being absent must not lose the bench line
+            out["reference_gpu"] = {"unavailable": str(e)[:200]}
+    plan.close()
+    if rank == 0:
+        print(json.dumps(out), flush=True)
+    if world > 1:
+        import torch.distributed as dist
+        dist.destroy_process_group()
+
+
+def time_gather_c(w, args, world, rank, dev):
+    """Optional replicated C: all-gather of the (unequal) slabs, padded to the tallest, over NCCL."""
+    import torch
+    import torch.distributed as dist
+    rows = torch.tensor([w["r1"] - w["r0"]], device=dev)
+    allrows = [torch.zeros_like(rows) for _ in range(world)]
+    dist.all_gather(allrows, rows)
+    tall = int(max(int(r.item()) for r in allrows))
+    mine = torch.zeros((tall, args.dim), dtype=w["B"].dtype, device=dev)
+    full = torch.empty((world * tall, args.dim), dtype=w["B"].dtype, device=dev)
+    for _ in range(2):
+        dist.all_gather_into_tensor(full, mine)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier(world)
+    e0.record()
+    for _ in range(5):
+        dist.all_gather_into_tensor(full, mine)
+    e1.record()
+    barrier(world)
+    return round(max_over_ranks(e0.elapsed_time(e1) / 5, world), 3)
+
+
+def cpu_baseline(host, dim, nnz, half):
+    """The oracle's OpenMP fp32 CSR loop on all host cores, whole workload, 1 warm-up + best of 3."""
+    orc = entry.load_oracle()
+    val = host["val"].astype(np.float32) if half else host["val"]
+    B = host["B"].astype(np.float32) if half else host["B"]
+    out = np.empty((len(host["rp"]) - 1, dim), np.float32)
+    _, cores = orc.spmm_f32_omp(host["rp"], host["col"], val, B, out=out)
+    best = float("inf")
+    t_all = time.perf_counter()
+    for _ in range(3):
+        t0 = time.perf_counter()
+        orc.spmm_f32_omp(host["rp"], host["col"], val, B, out=out)
+        best = min(best, time.perf_counter() - t0)
+        if time.perf_counter() - t_all > 25:
+            break
+    return {"value": round(2.0 * nnz * dim / best / 1e9, 3), "unit": "GFLOP/s", "cores": int(cores), "kind": "port",
+            "sample": "the whole workload (one full SpMM), best of up to 3 after 1 warm-up", "ms_per_step": round(best * 1e3, 2)}
+
+
+def _ref_lib(half):
+    path = os.path.join(ROOT, "oracle", "_ref", "libref_mergepath_f16.so" if half else "libref_mergepath_f32.so")
+    if not os.path.exists(path):
+        raise RuntimeError("oracle/_ref is not built")
+    lib = C.CDLL(path)
+    lib.refh_launch.argtypes = [C.c_void_p] * 5 + [C.POINTER(C.c_void_p)] + [C.c_int] * 4
+    return lib
+
+
+def reference_gpu(w, args, dev, steps=5, cost=8):
+    """The reference's own kernel (spmm_merge_path / _64, unmodified) on the same graph and B, driven as
+    its main() drives it: schedule for `cost`, degrees == 1 (unit values - the only setting in which it
+    is a correct SpMM), 256-thread blocks, sync after each launch.  Kernel time by CUDA events."""
+    import torch
+    mps = entry.load_package()
+    lib = _ref_lib(w["half"])
+    n, nnz, dim = w["rp"].numel() - 1, w["col"].numel(), args.dim
+    if (n + 1) * dim >= 2 ** 31:
+        raise RuntimeError("reference index arithmetic is 32-bit: (N+1)*dim overflows")
+    p, _ = mps.chunk_count(n, nnz, cost)
+    six = mps.schedule_device(w["rp"], p)
+    padded = torch.zeros((6, p + 64), dtype=torch.int32, device=dev)
+    padded[:, :p] = six
+    del six
+    deg = torch.ones(n + 1, dtype=torch.int32, device=dev)
+    B1 = torch.zeros((n + 1, dim), dtype=w["B"].dtype, device=dev)
+    B1[:n] = w["B"]
+    Cr = torch.zeros((n + 1, dim), dtype=w["B"].dtype, device=dev)
+    ptrs = (C.c_void_p * 6)(*[padded[i].data_ptr() for i in range(6)])
+    tpw = max(1, min(args.tpw, 32 // dim)) if dim <= 32 else 1
+    times = []
+    for i in range(steps + 1):
+        Cr.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        rc = lib.refh_launch(Cr.data_ptr(), B1.data_ptr(), w["rp"].data_ptr(), w["col"].data_ptr(), deg.data_ptr(), ptrs, n, dim, p, tpw)
+        e1.record()
+        torch.cuda.synchronize()
+        if rc != 0:
+            raise RuntimeError(f"reference launch returned CUDA error {rc}")
+        if i:
+            times.append(e0.elapsed_time(e1))
+    ms = float(np.median(times))
+    return {"kernel": "spmm_merge_path_64" if dim > 32 else "spmm_merge_path", "value": round(2.0 * nnz * dim / (ms * 1e-3) / 1e9, 2),
+            "unit": "GFLOP/s", "ms_per_step": round(ms, 4), "cost": cost, "threads_per_warp": tpw, "values": "unit (degrees == 1)",
+            "steps": steps}
+
+
+def run_reference_gpu(args):
+    import torch
+    rank, world, local = dist_setup(args)
+    if rank != 0:
+        return
+    dev = torch.device("cuda", local)
+    w = build_workload(args, 1, 0, dev)
+    try:
+        r = reference_gpu(w, args, dev, steps=max(args.steps, 1), cost=args.cost or 8)
+    except Exception as e:
+        print(json.dumps({"impl": "reference-gpu", "unavailable": str(e)[:200]}), flush=True)
+        return
+    print(json.dumps({"impl": "reference-gpu", "metric": "SpMM GFLOP/s (2*nnz*dim/t)", **r, "n_gpus": 1,
+                      "config": {"workload": workload_name(args, 1), "nodes": w["n"], "nnz": w["nnz"], "dim": args.dim}}), flush=True)
+
+
+def run_reference_cpu(args):
+    """Host arm: the OpenMP CSR loop of the oracle on all host cores, one step = one SpMM over a bounded
+    sample of the workload (an R-MAT graph of the same family sized for ~1-3 s per step on the host)."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    entry.load_package()
+    from mergepath_spmm_b200 import graphs
+    orc = entry.load_oracle()
+    import torch
+    scale = min(args.scale, 19)
+    if torch.cuda.is_available():
+        rp, col = graphs.rmat_csr(scale, args.avg_degree, args.seed, device=torch.device("cuda", 0))
+        val = graphs.gcn_values(rp, col).cpu().numpy()
+        rp, col = rp.cpu().numpy(), col.cpu().numpy()
+    else:
+        rp, col = graphs.rmat_csr(scale, args.avg_degree, args.seed)
+        val = graphs.gcn_values(rp, col)
+    n, nnz = len(rp) - 1, len(col)
+    B = graphs.dense_uniform(n, args.dim, args.seed + 1)
+    out = np.empty((n, args.dim), np.float32)
+    cores = 1
+    for _ in range(max(args.warmup, 1)):
+        _, cores = orc.spmm_f32_omp(rp, col, val, B, out=out)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        orc.spmm_f32_omp(rp, col, val, B, out=out)
+    s = (time.perf_counter() - t0) / args.steps
+    v = round(2.0 * nnz * args.dim / s / 1e9, 3)
+    sample = f"R-MAT scale {scale} (of {args.scale}), avg degree {args.avg_degree}, {nnz} nnz, dim {args.dim}: one full SpMM per step"
+    print(json.dumps({
+        "impl": "reference", "metric": "SpMM GFLOP/s (2*nnz*dim/t)", "value": v, "unit": "GFLOP/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": max(args.warmup, 1), "ms_per_step": round(s * 1e3, 3), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": workload_name(args, 1), "sample": sample, "dim": args.dim},
+        "cpu_baseline": {"value": v, "unit": "GFLOP/s", "cores": int(cores), "kind": "port", "sample": sample},
+        "e2e": {"value": v, "unit": "GFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "the reference has no CPU SpMM; this is the oracle's OpenMP CSR loop. Its CUDA kernels: --impl reference-gpu",
+    }), flush=True)
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference_cpu(args)
+    elif args.impl == "reference-gpu":
+        run_reference_gpu(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -143,6 +143,13 @@ MPS_API int mps_plan_sync_check(mps_plan *plan, void *stream);
  * what[10]=kernels per mps_spmm call what[11]=long_chain threshold. */
 MPS_API int mps_plan_info(const mps_plan *plan, int64_t what[12]);
 
+/* Per-kernel timing (no reference counterpart; the reference is timed from outside with nvprof,
+ * README.md:41-46): while enabled, every mps_spmm records a CUDA event pair around its tile
+ * kernel on the launching stream.  mps_plan_profile_read waits for the stream and returns the
+ * summed tile-kernel time in milliseconds and the number of launches since the last read. */
+MPS_API int mps_plan_profile(mps_plan *plan, int enable);
+MPS_API int mps_plan_profile_read(mps_plan *plan, void *stream, double *tile_ms, int32_t *launches);
+
 /* Algorithmic bytes of one SpMM: 4(N+1) + nnz(4 + s_val) + nnz*dim*s + N*dim*s, s = 4 or 2;
  * has_val = 0 drops the value term. */
 MPS_API int64_t mps_algorithmic_bytes(int32_t n_rows, int32_t nnz, int32_t dim, int dtype, int has_val);
@@ -150,9 +157,11 @@ MPS_API int64_t mps_algorithmic_bytes(int32_t n_rows, int32_t nnz, int32_t dim, 
 /* ------------------------------------------------------------------ host-buffer call ----- */
 
 /* The whole reference program body on HOST buffers (src/MergePathSpMM.cu:187-267): upload A and
- * B, partition, multiply once, download C.  Device buffers live in a per-thread workspace that
- * only grows, so repeated calls do not reallocate.  Blocking. */
-MPS_API int mps_spmm_host(int32_t n_rows, int32_t nnz, int32_t dim, int dtype, int32_t cost,
+ * B, partition, multiply once, download C.  B has n_cols rows (n_cols = n_rows for the square
+ * matrices of the file format; a row slab of a larger matrix has fewer rows than columns).
+ * Device buffers live in a per-thread workspace that only grows, so repeated calls do not
+ * reallocate.  Blocking. */
+MPS_API int mps_spmm_host(int32_t n_rows, int32_t n_cols, int32_t nnz, int32_t dim, int dtype, int32_t cost,
                   int32_t threads_per_warp, const int32_t *row_ptr, const int32_t *col_idx,
                   const void *val, const void *B, void *C);
 MPS_API void mps_host_workspace_release(void);

@@ -127,6 +127,17 @@ class Plan:
         with torch.cuda.device(self.device):
             capi.check(capi.lib().mps_plan_sync_check(self._h, _stream_ptr(stream)))
 
+    def profile(self, enable: bool = True):
+        capi.check(capi.lib().mps_plan_profile(self._h, int(enable)))
+        return self
+
+    def profile_read(self, stream=None) -> tuple[float, int]:
+        """(summed tile-kernel milliseconds, launches) since the last read."""
+        ms, n = C.c_double(), C.c_int32()
+        with torch.cuda.device(self.device):
+            capi.check(capi.lib().mps_plan_profile_read(self._h, _stream_ptr(stream), C.byref(ms), C.byref(n)))
+        return ms.value, n.value
+
     def info(self) -> dict:
         arr = (C.c_int64 * 12)()
         capi.check(capi.lib().mps_plan_info(self._h, arr))
@@ -163,7 +174,7 @@ def spmm_host(row_ptr, col_idx, val, B, out=None, cost: int = 8, threads_per_war
     is_half = str(B.dtype).endswith("float16")
     if out is None:
         out = np.empty((n_rows, dim), np.float16 if is_half else np.float32)
-    capi.check(capi.lib().mps_spmm_host(n_rows, nnz, dim, F16 if is_half else F32, cost, threads_per_warp, host_ptr(row_ptr),
+    capi.check(capi.lib().mps_spmm_host(n_rows, int(B.shape[0]), nnz, dim, F16 if is_half else F32, cost, threads_per_warp, host_ptr(row_ptr),
                                         host_ptr(col_idx), host_ptr(val), host_ptr(B), host_ptr(out)))
     return out
 

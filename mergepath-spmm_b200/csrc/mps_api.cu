@@ -52,6 +52,8 @@ static void chunking(int n_rows, int nnz, int cost, int *n_chunks, int *ipt) {
 
 using namespace mps;
 
+static const int kProfSlots = 256;  // event pairs kept between two profile reads
+
 struct mps_plan {
     int n_rows, nnz, dim, dtype, cost, tpw_requested, tpw_effective;
     int n_chunks, ipt;
@@ -65,6 +67,9 @@ struct mps_plan {
     int2 *d_tile_xy;
     float *d_tcarry, *d_thead;
     int *d_status, *d_long_list, *d_long_count;
+    bool profiling;
+    int prof_used;
+    cudaEvent_t prof_ev[2 * kProfSlots];
 };
 
 extern "C" const char *mps_last_error(void) { return g_error.c_str(); }
@@ -195,6 +200,8 @@ extern "C" int mps_plan_create(int32_t n_rows, int32_t nnz, int32_t dim, int dty
 
 extern "C" void mps_plan_destroy(mps_plan *plan) {
     if (!plan) return;
+    for (cudaEvent_t e : plan->prof_ev)
+        if (e) cudaEventDestroy(e);
     plan_free_scratch(plan);
     delete plan;
 }
@@ -269,9 +276,12 @@ static int launch_tile_gl(const mps_plan *p, const TileParams &tp, cudaStream_t 
 template <typename T, int FULLVEC>
 static int spmm_typed(mps_plan *p, const TileParams &tp, cudaStream_t st) {
     int rc;
+    const bool prof = p->profiling && p->prof_used < kProfSlots;
+    if (prof) MPS_CUDA(cudaEventRecord(p->prof_ev[2 * p->prof_used], st));
     if (p->vec == 1) rc = launch_tile<T, 1, 32, 4>(p, tp, st);
     else rc = launch_tile_gl<T, FULLVEC>(p, tp, st);
     if (rc != MPS_OK) return rc;
+    if (prof) { MPS_CUDA(cudaEventRecord(p->prof_ev[2 * p->prof_used + 1], st)); ++p->prof_used; }
     if (p->n_tiles > 1) {
         const int warps = p->n_tiles - 1;
         fixup_short_kernel<T><<<(warps + 7) / 8, 256, 0, st>>>(p->d_tile_xy, tp.rp, p->d_tcarry, p->d_thead, static_cast<T *>(tp.C),
@@ -321,6 +331,31 @@ extern "C" int mps_plan_sync_check(mps_plan *p, void *stream) {
     return MPS_OK;
 }
 
+extern "C" int mps_plan_profile(mps_plan *p, int enable) {
+    if (!p) return fail(MPS_ERR_ARG, "mps_plan_profile: plan is NULL");
+    if (enable)
+        for (cudaEvent_t &e : p->prof_ev)
+            if (!e) MPS_CUDA(cudaEventCreate(&e));
+    p->profiling = enable != 0;
+    p->prof_used = 0;
+    return MPS_OK;
+}
+
+extern "C" int mps_plan_profile_read(mps_plan *p, void *stream, double *tile_ms, int32_t *launches) {
+    if (!p || !tile_ms || !launches) return fail(MPS_ERR_ARG, "mps_plan_profile_read: NULL argument");
+    MPS_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+    double sum = 0.0;
+    for (int i = 0; i < p->prof_used; ++i) {
+        float ms = 0.0f;
+        MPS_CUDA(cudaEventElapsedTime(&ms, p->prof_ev[2 * i], p->prof_ev[2 * i + 1]));
+        sum += ms;
+    }
+    *tile_ms = sum;
+    *launches = p->prof_used;
+    p->prof_used = 0;
+    return MPS_OK;
+}
+
 extern "C" int mps_plan_info(const mps_plan *p, int64_t what[12]) {
     if (!p || !what) return fail(MPS_ERR_ARG, "mps_plan_info: NULL argument");
     what[0] = p->n_chunks; what[1] = p->ipt; what[2] = p->nch; what[3] = p->n_tiles;
@@ -361,10 +396,10 @@ static int ws_reserve(int i, size_t bytes) {
 
 extern "C" void mps_host_workspace_release(void) { g_ws.release(); }
 
-extern "C" int mps_spmm_host(int32_t n_rows, int32_t nnz, int32_t dim, int dtype, int32_t cost, int32_t threads_per_warp,
+extern "C" int mps_spmm_host(int32_t n_rows, int32_t n_cols, int32_t nnz, int32_t dim, int dtype, int32_t cost, int32_t threads_per_warp,
                              const int32_t *row_ptr, const int32_t *col_idx, const void *val, const void *B, void *C) {
     if (!row_ptr || !B || !C || (!col_idx && nnz > 0)) return fail(MPS_ERR_ARG, "mps_spmm_host: NULL argument");
-    if (dim < 1 || cost < 1) return fail(MPS_ERR_ARG, "mps_spmm_host: dim and cost must be >= 1");
+    if (dim < 1 || cost < 1 || n_cols < 0) return fail(MPS_ERR_ARG, "mps_spmm_host: dim and cost must be >= 1, n_cols >= 0");
     if (dtype != MPS_F32 && dtype != MPS_F16) return fail(MPS_ERR_ARG, "mps_spmm_host: unknown dtype %d", dtype);
     if (int rc = check_shape(n_rows, nnz)) return rc;
     int dev = 0;
@@ -372,7 +407,7 @@ extern "C" int mps_spmm_host(int32_t n_rows, int32_t nnz, int32_t dim, int dtype
     if (g_ws.device != dev) { g_ws.release(); g_ws.device = dev; }
     if (!g_ws.stream) MPS_CUDA(cudaStreamCreateWithFlags(&g_ws.stream, cudaStreamNonBlocking));
     const size_t elem = dtype == MPS_F16 ? 2 : 4;
-    const size_t n_b_rows = (size_t)n_rows;  // A is square by the file format's convention
+    const size_t n_b_rows = (size_t)n_cols;
     const size_t bytes[5] = {4 * ((size_t)n_rows + 1), 4 * (size_t)nnz, val ? elem * (size_t)nnz : 0, elem * n_b_rows * dim,
                              elem * (size_t)n_rows * dim};
     for (int i = 0; i < 5; ++i)
