@@ -1,0 +1,53 @@
+"""The MergePathSpMM command-line program: the reference's argv contract
+(src/MergePathSpMM.cu:114-124,141)."""
+import os
+import subprocess
+
+import pytest
+
+import cases
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+CLI = os.path.join(ROOT, "mergepath-spmm_b200", "lib", "MergePathSpMM")
+
+
+@pytest.fixture(scope="module")
+def cli(mps):
+    from mergepath_spmm_b200 import build
+    return build.build_cli()
+
+
+@pytest.fixture(scope="module")
+def c1_file(tmp_path_factory, mps):
+    rp, col = cases.c1_rmat()
+    p = str(tmp_path_factory.mktemp("cli") / "c1.csr")
+    mps.save_csr(p, rp, col)
+    return p, len(rp) - 1, len(col)
+
+
+def test_too_few_arguments_prints_the_reference_usage_and_exits_minus_one(cli):
+    r = subprocess.run([cli, "graph.csr", "16", "8"], capture_output=True, text=True)
+    assert r.returncode == 255  # exit(-1)
+    assert r.stdout.strip() == "Usage: ./application <input_file> <dimension> <cost> <threads_per_warp> <repeat>"
+
+
+def test_missing_file_is_an_error(cli):
+    r = subprocess.run([cli, "/nonexistent/graph.csr", "16", "8", "2", "1"], capture_output=True, text=True)
+    assert r.returncode == 1 and "cannot open" in r.stderr
+
+
+def test_first_line_matches_the_reference(cli, c1_file):
+    path, n, nnz = c1_file
+    r = subprocess.run([cli, path, "16", "8", "32", "1"], capture_output=True, text=True)
+    assert r.stdout.splitlines()[0] == f"Total number of rows: {n} and non-zeros: {nnz}"
+    assert "threads_per_warp 32 exceeds" in r.stderr  # clamped where the reference exits
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("extra", [[], ["--values=gcn"], ["--dtype=f16", "--values=gcn"]])
+def test_runs_and_checks_on_the_gpu(cli, c1_file, cuda, extra):
+    path, n, nnz = c1_file
+    for dim in ("16", "64"):
+        r = subprocess.run([cli, path, dim, "8", "2", "3", "--check"] + extra, capture_output=True, text=True)
+        assert r.returncode == 0, r.stdout + r.stderr
+        assert "check: 0 elements outside tolerance" in r.stdout and "GFLOP/s" in r.stdout
