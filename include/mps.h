@@ -166,6 +166,32 @@ MPS_API int mps_spmm_host(int32_t n_rows, int32_t n_cols, int32_t nnz, int32_t d
                   const void *val, const void *B, void *C);
 MPS_API void mps_host_workspace_release(void);
 
+/* ------------------------------------------------------------------ no-allocation call --- */
+
+/* No counterpart in the reference.  For callers that are not allowed to allocate device memory
+ * when they call (a plugin living inside a host framework's fixed arena, a process whose device
+ * memory is fully committed at start-up, a loop that cannot afford cudaMalloc's device-wide
+ * synchronisation): partition + multiply + check in one blocking call whose scratch is a fixed
+ * array inside the library image instead of a plan's cudaMalloc'ed buffers.  Inputs and output are
+ * the caller's device buffers as for mps_spmm; `cost`/`threads_per_warp` as for mps_plan_create.
+ *
+ * Limits: with T = tiles of the automatic layout (mps_plan_info what[3] of an equivalent plan),
+ * T <= MPS_NOALLOC_MAX_TILES and T * dim <= MPS_NOALLOC_MAX_CARRY_FLOATS, else MPS_ERR_UNSUPPORTED
+ * with the numbers in mps_last_error().  At dim 64, cost 16 that is about 8.9 million merge items
+ * (rows + non-zeros).  Every GPU that loads the library holds MPS_NOALLOC_SCRATCH_BYTES for this
+ * array until the process exits.
+ *
+ * The array is shared by every call on a device: calls that overlap on the GPU race on it, so
+ * issue them one after another.  The first call on each device looks up the array's address; make
+ * that call before starting any stream capture.  Calls no cudaMalloc/cudaFree and no allocating
+ * library routine. */
+#define MPS_NOALLOC_MAX_TILES 32768
+#define MPS_NOALLOC_MAX_CARRY_FLOATS (1u << 20)
+#define MPS_NOALLOC_SCRATCH_BYTES (9u << 20)
+MPS_API int mps_spmm_noalloc(int32_t n_rows, int32_t nnz, int32_t dim, int dtype, int32_t cost,
+                     int32_t threads_per_warp, const int32_t *d_row_ptr, const int32_t *d_col_idx,
+                     const void *d_val, const void *d_B, void *d_C, void *stream);
+
 /* ------------------------------------------------------------------ multi-GPU slabs ------ */
 
 /* Row slabs of equal non-zero count for n_slabs devices (no reference counterpart - the

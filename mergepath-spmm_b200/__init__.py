@@ -29,7 +29,7 @@ try:
 except Exception:  # pragma: no cover
     torch = None
 
-__all__ = ["Plan", "spmm", "spmm_host", "partition_device", "schedule_device", "chunk_count", "load_csr", "save_csr",
+__all__ = ["Plan", "spmm", "spmm_host", "spmm_noalloc", "partition_device", "schedule_device", "chunk_count", "load_csr", "save_csr",
            "save_csr_bin", "load_csr_bin", "slab_bounds", "slab_rebase", "algorithmic_bytes", "F32", "F16", "MpsError"]
 
 
@@ -155,6 +155,20 @@ def spmm(row_ptr, col_idx, val, B, cost: int = 8, threads_per_warp: int = 1):
         plan.sync_check()
     finally:
         plan.close()
+    return out
+
+
+def spmm_noalloc(row_ptr, col_idx, val, B, out, cost: int = 8, threads_per_warp: int = 1, stream=None):
+    """C = A @ B into the caller's `out` without any device allocation by the library: the scratch
+    is a fixed array inside libmps_b200.so (see mps_spmm_noalloc in include/mps.h for who needs this,
+    the size limit, and why calls must not overlap).  Blocking; raises MpsError(ERR_UNSUPPORTED)
+    when the problem's scratch does not fit."""
+    _need_cuda(row_ptr, col_idx, val, B, out)
+    dtype = F16 if B.dtype == torch.float16 else F32
+    with torch.cuda.device(B.device):
+        capi.check(capi.lib().mps_spmm_noalloc(row_ptr.numel() - 1, col_idx.numel(), B.shape[1], dtype, cost, threads_per_warp,
+                                               _dev_ptr(row_ptr), _dev_ptr(col_idx), _dev_ptr(val), _dev_ptr(B), _dev_ptr(out),
+                                               _stream_ptr(stream)))
     return out
 
 

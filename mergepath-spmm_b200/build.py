@@ -35,8 +35,8 @@ def _sources(names):
 
 
 def build_library(force: bool = False, verbose: bool = False) -> str:
-    srcs = _sources(["mps_api.cu", "csr_io.cpp"])
-    deps = srcs + _sources(["mps_kernels.cuh", "mps_internal.h"]) + [os.path.join(ROOT, "include", "mps.h")]
+    srcs = _sources(["mps_api.cu", "mps_noalloc.cu", "csr_io.cpp"])
+    deps = srcs + _sources(["mps_kernels.cuh", "mps_internal.h", "mps_plan.h"]) + [os.path.join(ROOT, "include", "mps.h")]
     if not force and _newer(LIB, deps):
         return LIB
     os.makedirs(LIBDIR, exist_ok=True)

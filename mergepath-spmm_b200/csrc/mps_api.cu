@@ -12,6 +12,7 @@
 
 #include "mps_internal.h"
 #include "mps_kernels.cuh"
+#include "mps_plan.h"
 
 namespace mps {
 
@@ -51,26 +52,6 @@ static void chunking(int n_rows, int nnz, int cost, int *n_chunks, int *ipt) {
 }  // namespace mps
 
 using namespace mps;
-
-static const int kProfSlots = 256;  // event pairs kept between two profile reads
-
-struct mps_plan {
-    int n_rows, nnz, dim, dtype, cost, tpw_requested, tpw_effective;
-    int n_chunks, ipt;
-    int vec, gl, unroll, slab_cols, n_col_slabs;
-    int nch, n_tiles, smem_bytes;
-    int bulk;
-    int long_chain, n_long, long_capacity;
-    int device;
-    bool user_nch, user_unroll;
-    bool partitioned;
-    int2 *d_tile_xy;
-    float *d_tcarry, *d_thead;
-    int *d_status, *d_long_list, *d_long_count;
-    bool profiling;
-    int prof_used;
-    cudaEvent_t prof_ev[2 * kProfSlots];
-};
 
 extern "C" const char *mps_last_error(void) { return g_error.c_str(); }
 extern "C" const char *mps_version(void) { return "mps_b200 0.1 (sm_100a)"; }
@@ -140,6 +121,32 @@ static int plan_layout(mps_plan *p) {
     return MPS_OK;
 }
 
+// Shape-dependent fields of a plan (no CUDA call, no allocation); the caller validated the arguments.
+void mps::plan_init_shape(mps_plan *p, int n_rows, int nnz, int dim, int dtype, int cost, int threads_per_warp) {
+    memset(p, 0, sizeof *p);
+    p->n_rows = n_rows; p->nnz = nnz; p->dim = dim; p->dtype = dtype; p->cost = cost;
+    p->tpw_requested = threads_per_warp;
+    // the reference exits when tpw > 32/dim (src/MergePathSpMM.cu:224-228) and ignores it for dim > 32
+    const int tpw_max = dim <= 32 ? 32 / dim : 1;
+    p->tpw_effective = threads_per_warp < 1 ? 1 : (threads_per_warp > tpw_max ? tpw_max : threads_per_warp);
+    chunking(n_rows, nnz, cost, &p->n_chunks, &p->ipt);
+    const int full_vec = dtype == MPS_F16 ? 8 : 4;
+    if (dim % full_vec == 0) {
+        p->vec = full_vec;
+        int lanes = dim / full_vec;
+        p->gl = lanes >= 32 ? 32 : pow2_at_least(lanes < 2 ? 2 : lanes);
+    } else {
+        p->vec = 1;
+        p->gl = 32;
+    }
+    p->slab_cols = p->gl * p->vec;
+    p->n_col_slabs = (dim + p->slab_cols - 1) / p->slab_cols;
+    p->bulk = 1;
+    p->long_chain = 32;
+}
+
+int mps::plan_finish_layout(mps_plan *p) { return plan_layout(p); }
+
 static void plan_free_scratch(mps_plan *p) {
     cudaFree(p->d_tile_xy); cudaFree(p->d_tcarry); cudaFree(p->d_thead);
     cudaFree(p->d_status); cudaFree(p->d_long_list); cudaFree(p->d_long_count);
@@ -170,26 +177,7 @@ extern "C" int mps_plan_create(int32_t n_rows, int32_t nnz, int32_t dim, int dty
     if (int rc = check_shape(n_rows, nnz)) return rc;
     mps_plan *p = new (std::nothrow) mps_plan();
     if (!p) return fail(MPS_ERR_NOMEM, "mps_plan_create: out of host memory");
-    memset(p, 0, sizeof *p);
-    p->n_rows = n_rows; p->nnz = nnz; p->dim = dim; p->dtype = dtype; p->cost = cost;
-    p->tpw_requested = threads_per_warp;
-    // the reference exits when tpw > 32/dim (src/MergePathSpMM.cu:224-228) and ignores it for dim > 32
-    const int tpw_max = dim <= 32 ? 32 / dim : 1;
-    p->tpw_effective = threads_per_warp < 1 ? 1 : (threads_per_warp > tpw_max ? tpw_max : threads_per_warp);
-    chunking(n_rows, nnz, cost, &p->n_chunks, &p->ipt);
-    const int full_vec = dtype == MPS_F16 ? 8 : 4;
-    if (dim % full_vec == 0) {
-        p->vec = full_vec;
-        int lanes = dim / full_vec;
-        p->gl = lanes >= 32 ? 32 : pow2_at_least(lanes < 2 ? 2 : lanes);
-    } else {
-        p->vec = 1;
-        p->gl = 32;
-    }
-    p->slab_cols = p->gl * p->vec;
-    p->n_col_slabs = (dim + p->slab_cols - 1) / p->slab_cols;
-    p->bulk = 1;
-    p->long_chain = 32;
+    plan_init_shape(p, n_rows, nnz, dim, dtype, cost, threads_per_warp);
     MPS_CUDA(cudaGetDevice(&p->device));
     int rc = plan_layout(p);
     if (rc == MPS_OK) rc = plan_alloc_scratch(p);

@@ -1,0 +1,31 @@
+// The plan object behind the opaque mps_plan of the public header.  Internal: shared by the .cu
+// translation units of libmps_b200.so only.
+#pragma once
+#include <cuda_runtime.h>
+
+static const int kProfSlots = 256;  // event pairs kept between two profile reads
+
+struct mps_plan {
+    int n_rows, nnz, dim, dtype, cost, tpw_requested, tpw_effective;
+    int n_chunks, ipt;
+    int vec, gl, unroll, slab_cols, n_col_slabs;
+    int nch, n_tiles, smem_bytes;
+    int bulk;
+    int long_chain, n_long, long_capacity;
+    int device;
+    bool user_nch, user_unroll;
+    bool partitioned;
+    int2 *d_tile_xy;
+    float *d_tcarry, *d_thead;
+    int *d_status, *d_long_list, *d_long_count;
+    bool profiling;
+    int prof_used;
+    cudaEvent_t prof_ev[2 * kProfSlots];
+};
+
+namespace mps {
+// Fills every shape-derived field (chunking, lanes, column slabs, defaults); no CUDA call.
+void plan_init_shape(mps_plan *p, int n_rows, int nnz, int dim, int dtype, int cost, int threads_per_warp);
+// Chooses chunks per tile / unroll, computes shared-memory size and the tile count.
+int plan_finish_layout(mps_plan *p);
+}  // namespace mps
