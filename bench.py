@@ -47,7 +47,7 @@ def parse_args():
     ap.add_argument("--tpw", type=int, default=1, help="threads_per_warp, accepted as the reference's CLI does")
     ap.add_argument("--dtype", default="f32", choices=["f32", "f16"])
     ap.add_argument("--seed", type=int, default=0)
-    ap.add_argument("--chunks-per-tile", type=int, default=0)
+    ap.add_argument("--chunks-per-unit", type=int, default=0)
     ap.add_argument("--unroll", type=int, default=0)
     ap.add_argument("--no-bulk", action="store_true")
     ap.add_argument("--e2e-steps", type=int, default=3)
@@ -191,8 +191,8 @@ def run_ours(args):
     n_slab, nnz_slab = w["r1"] - w["r0"], w["col"].numel()
     dt = mps.F16 if w["half"] else mps.F32
     plan = mps.Plan(n_slab, nnz_slab, args.dim, dt, cost, args.tpw, device=dev)
-    if args.chunks_per_tile or args.unroll or args.no_bulk:
-        plan.tune(args.chunks_per_tile, args.unroll, not args.no_bulk)
+    if args.chunks_per_unit or args.unroll or args.no_bulk:
+        plan.tune(args.chunks_per_unit, args.unroll, not args.no_bulk)
     t0 = time.perf_counter()
     plan.partition(w["rp"])
     torch.cuda.synchronize()
@@ -274,7 +274,7 @@ def run_ours(args):
         "vs_baseline": None, "dtype": "f16 storage / f32 accumulate" if w["half"] else "f32", "data": "synthetic",
         "config": {"workload": workload_name(args, world), "nodes": w["n"], "nnz": w["nnz"], "dim": args.dim, "cost": cost,
                    "threads_per_warp": info["threads_per_warp"], "values": "gcn", "parallelism": f"row-slabs x{world}, B replicated",
-                   "l2": "inputs larger than L2 (B and A each > 126 MB)", "chunks_per_tile": info["chunks_per_tile"],
+                   "l2": "inputs larger than L2 (B and A each > 126 MB)", "chunks_per_tile": info["chunks_per_tile"], "chunks_per_unit": info["chunks_per_unit"],
                    "items_per_chunk": info["items_per_chunk"], "unroll": info["unroll"], "tiles": info["n_tiles"],
                    "long_rows": info["long_rows"]},
         "roofline": roofline, "e2e": e2e, "gpu_launches": args.steps * info["kernels_per_call"],

@@ -101,20 +101,25 @@ static int pow2_at_least(int v) {
     return p;
 }
 
-static const int kSmemTarget = 44 * 1024;   // keeps five tile blocks resident per SM
+static const int kSmemTarget = 64 * 1024;   // three tile blocks per SM, which the registers allow anyway
+static const int kTileItems = 4352;          // merge items per tile the automatic layout aims for
 static const int kSmemLimit = 200 * 1024;
 
 static int plan_layout(mps_plan *p) {
     const int elem = p->dtype == MPS_F16 ? 2 : 4;
-    const int gpc = kBlock / p->gl;
-    if (!p->user_unroll) p->unroll = p->ipt >= 8 ? 8 : 4;
+    const int gpc = kBlock / p->gl;  // units per tile
+    if (!p->user_unroll) p->unroll = 8;
     if (p->vec == 1) p->unroll = 4;
-    if (!p->user_nch) {
-        int rounds = 8;
-        while (rounds > 1 && TileSmem(gpc * rounds, p->ipt, p->slab_cols, elem).bytes > kSmemTarget) rounds >>= 1;
-        p->nch = gpc * rounds;
+    if (!p->user_cpu) {
+        // about kTileItems merge items per tile, as long as the windows fit the shared-memory target
+        int cpu = kTileItems / (gpc * p->ipt);
+        if (cpu < 1) cpu = 1;
+        if (cpu > 64) cpu = 64;
+        while (cpu > 1 && TileSmem(gpc, gpc * cpu * p->ipt, p->slab_cols, elem).bytes > kSmemTarget) --cpu;
+        p->cpu = cpu;
     }
-    p->smem_bytes = TileSmem(p->nch, p->ipt, p->slab_cols, elem).bytes;
+    p->nch = gpc * p->cpu;
+    p->smem_bytes = TileSmem(gpc, p->nch * p->ipt, p->slab_cols, elem).bytes;
     if (p->smem_bytes > kSmemLimit)
         return fail(MPS_ERR_UNSUPPORTED, "tile of %d chunks x %d items needs %d bytes of shared memory", p->nch, p->ipt, p->smem_bytes);
     p->n_tiles = (p->n_chunks + p->nch - 1) / p->nch;
@@ -194,13 +199,13 @@ extern "C" void mps_plan_destroy(mps_plan *plan) {
     delete plan;
 }
 
-extern "C" int mps_plan_tune(mps_plan *p, int32_t chunks_per_tile, int32_t unroll, int32_t bulk_staging) {
+extern "C" int mps_plan_tune(mps_plan *p, int32_t chunks_per_unit, int32_t unroll, int32_t bulk_staging) {
     if (!p) return fail(MPS_ERR_ARG, "mps_plan_tune: plan is NULL");
     if (unroll != 0 && unroll != 4 && unroll != 8) return fail(MPS_ERR_ARG, "mps_plan_tune: unroll must be 0, 4 or 8");
-    if (chunks_per_tile < 0 || chunks_per_tile > 4096) return fail(MPS_ERR_ARG, "mps_plan_tune: chunks_per_tile out of range");
+    if (chunks_per_unit < 0 || chunks_per_unit > 4096) return fail(MPS_ERR_ARG, "mps_plan_tune: chunks_per_unit out of range");
     const int old_tiles = p->n_tiles;
-    p->user_nch = chunks_per_tile > 0;
-    if (p->user_nch) p->nch = chunks_per_tile;
+    p->user_cpu = chunks_per_unit > 0;
+    if (p->user_cpu) p->cpu = chunks_per_unit;
     p->user_unroll = unroll != 0;
     if (p->user_unroll) p->unroll = unroll;
     p->bulk = bulk_staging ? 1 : 0;
@@ -299,7 +304,7 @@ extern "C" int mps_spmm(mps_plan *p, const int32_t *d_row_ptr, const int32_t *d_
     tp.tile_xy = p->d_tile_xy; tp.tcarry = p->d_tcarry; tp.thead = p->d_thead; tp.status = p->d_status;
     tp.total = (long long)p->n_rows + 1 + p->nnz;
     tp.n_rows = p->n_rows; tp.nnz = p->nnz; tp.dim = p->dim;
-    tp.ipt = p->ipt; tp.nch = p->nch; tp.n_tiles = p->n_tiles;
+    tp.ipt = p->ipt; tp.nch = p->nch; tp.cpu = p->cpu; tp.n_tiles = p->n_tiles;
     const bool aligned16 = !((uintptr_t)d_row_ptr % 16) && !((uintptr_t)d_col_idx % 16) && !((uintptr_t)d_val % 16);
     tp.bulk = (p->bulk && aligned16) ? 1 : 0;
     cudaStream_t st = (cudaStream_t)stream;
@@ -344,13 +349,14 @@ extern "C" int mps_plan_profile_read(mps_plan *p, void *stream, double *tile_ms,
     return MPS_OK;
 }
 
-extern "C" int mps_plan_info(const mps_plan *p, int64_t what[12]) {
+extern "C" int mps_plan_info(const mps_plan *p, int64_t what[16]) {
     if (!p || !what) return fail(MPS_ERR_ARG, "mps_plan_info: NULL argument");
+    for (int i = 0; i < 16; ++i) what[i] = 0;
     what[0] = p->n_chunks; what[1] = p->ipt; what[2] = p->nch; what[3] = p->n_tiles;
     what[4] = p->gl; what[5] = p->vec; what[6] = p->unroll; what[7] = p->smem_bytes;
     what[8] = p->n_long; what[9] = p->tpw_effective;
     what[10] = 1 + (p->n_tiles > 1 ? 1 : 0) + (p->n_long > 0 ? 1 : 0);
-    what[11] = p->long_chain;
+    what[11] = p->long_chain; what[12] = p->cpu; what[13] = kBlock / p->gl;
     return MPS_OK;
 }
 

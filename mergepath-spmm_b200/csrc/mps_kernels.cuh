@@ -6,13 +6,15 @@
 //   tile   = `nch` consecutive chunks, one thread block.  Its two boundary coordinates come from
 //            the plan (searched once per row_ptr by partition_kernel); the block stages the tile's
 //            row_ptr / col_idx / val windows into shared memory with bulk async copies that
-//            complete on an mbarrier, then re-searches the nch-1 interior diagonals in shared memory.
-//   chunk  = walked by one group of GL lanes; a lane owns VEC adjacent columns and gathers its part
-//            of every B row of the chunk with one 128-bit load, U loads in flight before the first
-//            fused multiply-add.  Rows that end inside the chunk and began there are stored
-//            directly; a row that began earlier leaves its share as the chunk's "head", what is left
-//            at the chunk's end is the chunk's "carry" (both in shared memory, fp32).
-//   fix-up = inside the tile, in chunk order, by the group that ended the row; across tiles by
+//            complete on an mbarrier.
+//   unit   = `cpu` consecutive chunks of the tile, walked in order by one group of GL lanes; the
+//            unit boundaries (a subset of the chunk diagonals) are re-searched in shared memory.
+//            A lane owns VEC adjacent columns and gathers its part of every B row with one 128-bit
+//            load, U loads in flight before the first fused multiply-add; the accumulator stays in
+//            registers across the chunk boundaries inside the unit.  Rows that end inside the unit
+//            and began there are stored directly; a row that began earlier leaves its share as the
+//            unit's "head", what is left at the unit's end is its "carry" (shared memory, fp32).
+//   fix-up = inside the tile, in unit order, by the group that ended the row; across tiles by
 //            fixup kernels that add the tiles' carry rows in tile order.  No atomics touch C, every
 //            row of C is stored exactly once, sums are bitwise reproducible.
 #pragma once
@@ -42,7 +44,7 @@ struct TileParams {
     int *status;
     long long total;  // N + 1 + nnz
     int n_rows, nnz, dim;
-    int ipt, nch, n_tiles;
+    int ipt, nch, cpu, n_tiles;  // items per chunk, chunks per tile, chunks per unit
     int bulk;  // 1: bulk async staging (needs 16-byte aligned rp/col/val)
 };
 
@@ -236,16 +238,16 @@ __device__ __forceinline__ void gmem_put_f32(float *dst, const float (&v)[VEC]) 
 struct TileSmem {
     int off_fx, off_fy, off_rp, off_col, off_val, off_carry, off_head, bytes;
     __host__ __device__ static int up16(int v) { return (v + 15) & ~15; }
-    __host__ __device__ TileSmem(int nch, int ipt, int slab_cols, int elem_bytes) {
-        const int win = nch * ipt + 2 * kAlign + 8;  // window plus alignment slack on both sides
-        int o = 16;                                  // mbarrier
-        off_fx = o; o = up16(o + 4 * (nch + 1));
-        off_fy = o; o = up16(o + 4 * (nch + 1));
+    __host__ __device__ TileSmem(int n_units, int tile_items, int slab_cols, int elem_bytes) {
+        const int win = tile_items + 2 * kAlign + 8;  // window plus alignment slack on both sides
+        int o = 16;                                   // mbarrier
+        off_fx = o; o = up16(o + 4 * (n_units + 1));
+        off_fy = o; o = up16(o + 4 * (n_units + 1));
         off_rp = o; o = up16(o + 4 * win);
         off_col = o; o = up16(o + 4 * win);
         off_val = o; o = up16(o + elem_bytes * win);
-        off_carry = o; o = up16(o + 4 * nch * slab_cols);
-        off_head = o; o = up16(o + 4 * nch * slab_cols);
+        off_carry = o; o = up16(o + 4 * n_units * slab_cols);
+        off_head = o; o = up16(o + 4 * n_units * slab_cols);
         bytes = o;
     }
 };
@@ -270,12 +272,14 @@ __device__ __forceinline__ void stage_ragged(E *s_dst, const E *g_src, long long
 // ---------------------------------------------------------------------------------------------
 // the tile kernel
 // ---------------------------------------------------------------------------------------------
+// One block = one tile = GPC units; unit u = `cpu` consecutive chunks walked by one group of GL
+// lanes with the accumulator kept in registers across the chunk boundaries inside the unit.
 template <typename T, int VEC, int GL, int U>
 __global__ void __launch_bounds__(kBlock) spmm_tile_kernel(const TileParams p) {
-    constexpr int GPC = kBlock / GL;   // groups (chunks walked at once) per block
+    constexpr int GPC = kBlock / GL;   // units (lane groups) per block
     constexpr int SLAB = GL * VEC;     // columns covered by one block
     extern __shared__ __align__(128) unsigned char smem[];
-    const TileSmem L(p.nch, p.ipt, SLAB, (int)sizeof(T));
+    const TileSmem L(GPC, p.nch * p.ipt, SLAB, (int)sizeof(T));
     uint64_t *s_bar = reinterpret_cast<uint64_t *>(smem);
     int *s_fx = reinterpret_cast<int *>(smem + L.off_fx);
     int *s_fy = reinterpret_cast<int *>(smem + L.off_fy);
@@ -291,8 +295,9 @@ __global__ void __launch_bounds__(kBlock) spmm_tile_kernel(const TileParams p) {
     const int coff = blockIdx.y * SLAB + l * VEC;  // first column of this lane
     const bool active = coff < p.dim;
     const bool has_val = p.val != nullptr;
-    const T *__restrict__ Bm = static_cast<const T *>(p.B);
-    T *__restrict__ Cm = static_cast<T *>(p.C);
+    const T *__restrict__ Bl = static_cast<const T *>(p.B) + coff;  // this lane's columns of B
+    T *__restrict__ Cl = static_cast<T *>(p.C) + coff;
+    const unsigned dim = (unsigned)p.dim;
 
     const int2 c0 = __ldg(p.tile_xy + t), c1 = __ldg(p.tile_xy + t + 1);
     const int X0 = c0.x, Y0 = c0.y, X1 = c1.x, Y1 = c1.y;
@@ -320,10 +325,14 @@ __global__ void __launch_bounds__(kBlock) spmm_tile_kernel(const TileParams p) {
         stage_ragged<int>(s_rp, p.rp, rp_base, rp_be, X1, tid);
         stage_ragged<int>(s_col, p.col, y_base, y_be, Y1, tid);
         if (has_val) stage_ragged<T>(s_val, static_cast<const T *>(p.val), y_base, y_be, Y1, tid);
-        bool ok = mbar_wait_bounded(bar, 0);
-        if (!ok) {
-            atomicExch(p.status, (int)kDevStageTimeout);
-            ok = mbar_wait_bounded(bar, 0);  // give copies in flight one more bounded chance to land
+        // the first warp watches the mbarrier; the others park at the block barrier below
+        bool ok = true;
+        if (tid < 32) {
+            ok = mbar_wait_bounded(bar, 0);
+            if (!ok) {
+                if (tid == 0) atomicExch(p.status, (int)kDevStageTimeout);
+                ok = mbar_wait_bounded(bar, 0);  // give copies in flight one more bounded chance to land
+            }
         }
         if (__syncthreads_or(!ok)) return;
     } else {
@@ -333,35 +342,38 @@ __global__ void __launch_bounds__(kBlock) spmm_tile_kernel(const TileParams p) {
             for (int i = y_base + tid; i < Y1; i += kBlock) s_val[i - y_base] = static_cast<const T *>(p.val)[i];
         __syncthreads();
     }
+    const int *__restrict__ w_rp = s_rp - rp_base;   // indexable by global row_ptr index
+    const int *__restrict__ w_col = s_col - y_base;  // indexable by global non-zero index
+    const T *__restrict__ w_val = s_val - y_base;
 
-    // ---- interior diagonals, searched in the staged row_ptr window ----
-    for (int c = tid; c <= p.nch; c += kBlock) {
+    // ---- unit boundaries, searched in the staged row_ptr window ----
+    if (tid <= GPC) {
         int2 r;
-        if (c == 0) r = c0;
-        else if (c == p.nch) r = c1;
+        if (tid == 0) r = c0;
+        else if (tid == GPC) r = c1;
         else {
-            long long d = (long long)p.ipt * ((long long)t * p.nch + c);
+            long long d = (long long)p.ipt * ((long long)t * p.nch + (long long)tid * p.cpu);
             if (d > p.total) d = p.total;
             long long lo = d - Y1 > X0 ? d - Y1 : X0;
             long long hi = d - Y0 < X1 ? d - Y0 : X1;
             while (lo < hi) {
                 const long long mid = (lo + hi) >> 1;
-                if ((long long)s_rp[mid - rp_base] <= d - mid - 1) lo = mid + 1;
+                if ((long long)w_rp[mid] <= d - mid - 1) lo = mid + 1;
                 else hi = mid;
             }
             r = make_int2((int)lo, (int)(d - lo));
         }
-        s_fx[c] = r.x;
-        s_fy[c] = r.y;
+        s_fx[tid] = r.x;
+        s_fy[tid] = r.y;
     }
     __syncthreads();
 
-    // ---- walk the chunks ----
-    for (int c = g; c < p.nch; c += GPC) {
-        const int x0 = s_fx[c], y0 = s_fy[c], x1 = s_fx[c + 1], y1 = s_fy[c + 1];
-        bool head_pending = x0 >= 1 && y0 > s_rp[x0 - 1 - rp_base];  // first row began in an earlier chunk
+    // ---- walk this group's unit ----
+    {
+        const int x0 = s_fx[g], y0 = s_fy[g], x1 = s_fx[g + 1], y1 = s_fy[g + 1];
+        bool head_pending = x0 >= 1 && y0 > w_rp[x0 - 1];  // first row began before this unit
         int x = x0;
-        int next_mark = x < x1 ? s_rp[x - rp_base] : 0x7fffffff;  // non-zero index that marker x precedes
+        int next_mark = x < x1 ? w_rp[x] : 0x7fffffff;  // non-zero index that marker x precedes
         float acc[VEC];
 #pragma unroll
         for (int i = 0; i < VEC; ++i) acc[i] = 0.0f;
@@ -369,31 +381,57 @@ __global__ void __launch_bounds__(kBlock) spmm_tile_kernel(const TileParams p) {
         auto end_row = [&]() {
             if (x >= 1) {  // marker x ends row x-1 (marker 0 ends nothing)
                 if (head_pending) {
-                    smem_put<VEC>(s_head + (size_t)c * SLAB + l * VEC, acc);
+                    smem_put<VEC>(s_head + g * SLAB + l * VEC, acc);
                     head_pending = false;
                 } else if (active) {
-                    Lane<T, VEC>::store(Cm + (size_t)(x - 1) * p.dim + coff, acc);
+                    Lane<T, VEC>::store(Cl + (size_t)(x - 1) * dim, acc);
                 }
 #pragma unroll
                 for (int i = 0; i < VEC; ++i) acc[i] = 0.0f;
             }
             ++x;
-            next_mark = x < x1 ? s_rp[x - rp_base] : 0x7fffffff;
+            next_mark = x < x1 ? w_rp[x] : 0x7fffffff;
         };
 
-        for (int k = y0; k < y1; k += U) {
+        int k = y0;
+        // full batches: U gathers in flight, no bound checks
+        for (; k + U <= y1; k += U) {
             typename Lane<T, VEC>::raw b[U];
             float a[U];
 #pragma unroll
             for (int u = 0; u < U; ++u) {
+                const unsigned ci = (unsigned)w_col[k + u];
+                a[u] = has_val ? to_float(w_val[k + u]) : 1.0f;
+                if (active) b[u] = Lane<T, VEC>::load(Bl + (size_t)ci * dim);
+            }
+            while (next_mark <= k) end_row();
+            if (next_mark >= k + U) {  // no row ends inside the batch
+                if (active) {
+#pragma unroll
+                    for (int u = 0; u < U; ++u) Lane<T, VEC>::fma(acc, a[u], b[u]);
+                }
+            } else {
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    while (next_mark <= k + u) end_row();
+                    if (active) Lane<T, VEC>::fma(acc, a[u], b[u]);
+                }
+            }
+        }
+        // remainder: fewer than U non-zeros
+        if (k < y1) {
+            typename Lane<T, VEC>::raw b[U];
+            float a[U];
+#pragma unroll
+            for (int u = 0; u < U - 1; ++u) {
                 if (k + u < y1) {
-                    const int ci = s_col[k + u - y_base];
-                    a[u] = has_val ? to_float(s_val[k + u - y_base]) : 1.0f;
-                    if (active) b[u] = Lane<T, VEC>::load(Bm + (size_t)ci * p.dim + coff);
+                    const unsigned ci = (unsigned)w_col[k + u];
+                    a[u] = has_val ? to_float(w_val[k + u]) : 1.0f;
+                    if (active) b[u] = Lane<T, VEC>::load(Bl + (size_t)ci * dim);
                 }
             }
 #pragma unroll
-            for (int u = 0; u < U; ++u) {
+            for (int u = 0; u < U - 1; ++u) {
                 if (k + u < y1) {
                     while (next_mark <= k + u) end_row();
                     if (active) Lane<T, VEC>::fma(acc, a[u], b[u]);
@@ -401,37 +439,38 @@ __global__ void __launch_bounds__(kBlock) spmm_tile_kernel(const TileParams p) {
             }
         }
         while (x < x1) end_row();
-        smem_put<VEC>(s_carry + (size_t)c * SLAB + l * VEC, acc);
+        smem_put<VEC>(s_carry + g * SLAB + l * VEC, acc);
     }
     __syncthreads();
 
-    // ---- in-tile fix-up: the group that walked chunk c finishes the row chunk c ended first ----
-    for (int c = g; c < p.nch; c += GPC) {
-        const int x0 = s_fx[c], x1 = s_fx[c + 1], y0 = s_fy[c];
-        if (!(x0 >= 1 && x1 > x0 && y0 > s_rp[x0 - 1 - rp_base])) continue;
-        int s = c;
-        while (s > 0 && s_fx[s] == x0) --s;
-        const bool from_prev = s_fx[0] == x0 && Y0 > s_rp[X0 - 1 - rp_base];  // row began before this tile
-        float sum[VEC];
+    // ---- in-tile fix-up: the group finishes the row its unit ended first, if it began earlier ----
+    {
+        const int x0 = s_fx[g], x1 = s_fx[g + 1], y0 = s_fy[g];
+        if (x0 >= 1 && x1 > x0 && y0 > w_rp[x0 - 1]) {
+            int s = g;
+            while (s > 0 && s_fx[s] == x0) --s;
+            const bool from_prev = s_fx[0] == x0 && Y0 > w_rp[X0 - 1];  // row began before this tile
+            float sum[VEC];
 #pragma unroll
-        for (int i = 0; i < VEC; ++i) sum[i] = 0.0f;
-        for (int q = s; q < c; ++q) vec_add<VEC>(sum, s_carry + (size_t)q * SLAB + l * VEC);
-        vec_add<VEC>(sum, s_head + (size_t)c * SLAB + l * VEC);
-        if (active) {
-            if (from_prev) gmem_put_f32<VEC>(p.thead + (size_t)t * p.dim + coff, sum);
-            else Lane<T, VEC>::store(Cm + (size_t)(x0 - 1) * p.dim + coff, sum);
+            for (int i = 0; i < VEC; ++i) sum[i] = 0.0f;
+            for (int q = s; q < g; ++q) vec_add<VEC>(sum, s_carry + q * SLAB + l * VEC);
+            vec_add<VEC>(sum, s_head + g * SLAB + l * VEC);
+            if (active) {
+                if (from_prev) gmem_put_f32<VEC>(p.thead + (size_t)t * dim + coff, sum);
+                else Lane<T, VEC>::store(Cl + (size_t)(x0 - 1) * dim, sum);
+            }
         }
     }
     // ---- tile carry: everything after the last marker of the tile ----
     if (g == GPC - 1) {
-        const int xe = s_fx[p.nch];
-        int s = p.nch;
+        const int xe = s_fx[GPC];
+        int s = GPC;
         while (s > 0 && s_fx[s] == xe) --s;
         float sum[VEC];
 #pragma unroll
         for (int i = 0; i < VEC; ++i) sum[i] = 0.0f;
-        for (int q = s; q < p.nch; ++q) vec_add<VEC>(sum, s_carry + (size_t)q * SLAB + l * VEC);
-        if (active) gmem_put_f32<VEC>(p.tcarry + (size_t)t * p.dim + coff, sum);
+        for (int q = s; q < GPC; ++q) vec_add<VEC>(sum, s_carry + q * SLAB + l * VEC);
+        if (active) gmem_put_f32<VEC>(p.tcarry + (size_t)t * dim + coff, sum);
     }
 }
 

@@ -9,11 +9,11 @@ struct mps_plan {
     int n_rows, nnz, dim, dtype, cost, tpw_requested, tpw_effective;
     int n_chunks, ipt;
     int vec, gl, unroll, slab_cols, n_col_slabs;
-    int nch, n_tiles, smem_bytes;
+    int nch, cpu, n_tiles, smem_bytes;  // chunks per tile, chunks per unit
     int bulk;
     int long_chain, n_long, long_capacity;
     int device;
-    bool user_nch, user_unroll;
+    bool user_cpu, user_unroll;
     bool partitioned;
     int2 *d_tile_xy;
     float *d_tcarry, *d_thead;

@@ -275,18 +275,19 @@ ORC_API int orc_spmm_f32_omp(const int *row_ptr, const int *col, const float *va
 
 /* ------------------------------------------------------------------ 5 -- */
 
-/* CPU model of the tiled CUDA kernels of this repository: the same chunk
+/* CPU model of the tiled CUDA kernels of this repository: the same unit
  * boundaries, the same fused multiply-adds in the same order, the same
  * fixed-order fix-up inside a tile and across tiles, so the GPU result must
  * equal it bit for bit.
  *
  *   chunk  c : merge items [ipt*c, ipt*(c+1)), one reference chunk
- *   tile   t : chunks [nch*t, nch*(t+1))
- *   a chunk walks its non-zeros in order, acc = fmaf(a, b, acc); a row that
- *   ends inside the chunk is stored directly unless it began in an earlier
- *   chunk, in which case the chunk's share is its "head"; what is left at
- *   the chunk's end is its "carry".
- *   in-tile fix-up  : row = 0 + carry[s] + .. + carry[c-1] + head[c]
+ *   unit     : cpu consecutive chunks, walked in order by one lane group with
+ *              one running accumulator, acc = fmaf(a, b, acc)
+ *   tile   t : nch consecutive chunks = nch/cpu units
+ *   a row that ends inside a unit is stored directly unless it began in an
+ *   earlier unit, in which case the unit's share is its "head"; what is left
+ *   at the unit's end is its "carry".
+ *   in-tile fix-up  : row = 0 + carry[s] + .. + carry[u-1] + head[u]
  *   cross-tile      : row = 0 + tcarry[s] + .. + tcarry[t-1] + thead[t];
  *                     chains longer than long_chain use 16 interleaved
  *                     strands, strand g = sum of tcarry[s+g], tcarry[s+g+16]..
@@ -316,9 +317,10 @@ static inline void model_store(const model_io *io, int row, const float *v) {
 
 ORC_API int orc_tile_model(const int *row_ptr, const int *col, const void *val, const void *B,
                            void *C, int n_rows, int nnz, int dim, int is_half, int cost,
-                           int nch, int long_chain) {
-    if (cost < 1 || nch < 1 || dim < 1) return -1;
+                           int nch, int cpu, int long_chain) {
+    if (cost < 1 || nch < 1 || cpu < 1 || nch % cpu != 0 || dim < 1) return -1;
     model_io io = {row_ptr, col, val, B, C, dim, is_half};
+    const int nu = nch / cpu; /* units per tile */
     const int64_t total = (int64_t)n_rows + 1 + nnz;
     const int P = orc_chunk_count(n_rows, nnz, cost);
     const int64_t ipt = orc_items_per_chunk(n_rows, nnz, P);
@@ -326,10 +328,10 @@ ORC_API int orc_tile_model(const int *row_ptr, const int *col, const void *val, 
     int *tx = malloc(sizeof(int) * (T + 1)), *ty = malloc(sizeof(int) * (T + 1));
     float *tcarry = calloc((size_t)T * dim, sizeof(float));
     float *thead = calloc((size_t)T * dim, sizeof(float));
-    int *fx = malloc(sizeof(int) * (nch + 1)), *fy = malloc(sizeof(int) * (nch + 1));
-    float *carry = malloc(sizeof(float) * (size_t)nch * dim);
-    float *head = malloc(sizeof(float) * (size_t)nch * dim);
-    char *has_head = malloc(nch);
+    int *fx = malloc(sizeof(int) * (nu + 1)), *fy = malloc(sizeof(int) * (nu + 1));
+    float *carry = malloc(sizeof(float) * (size_t)nu * dim);
+    float *head = malloc(sizeof(float) * (size_t)nu * dim);
+    char *has_head = malloc(nu);
     float *acc = malloc(sizeof(float) * dim), *sum = malloc(sizeof(float) * dim);
     float *strand = malloc(sizeof(float) * 16 * dim);
 
@@ -337,19 +339,19 @@ ORC_API int orc_tile_model(const int *row_ptr, const int *col, const void *val, 
         orc_merge_path_search(lmin(ipt * nch * (int64_t)t, total), row_ptr, n_rows + 1, nnz, &tx[t], &ty[t]);
 
     for (int t = 0; t < T; ++t) {
-        for (int c = 0; c <= nch; ++c)
-            orc_merge_path_search(lmin(ipt * ((int64_t)t * nch + c), total), row_ptr, n_rows + 1, nnz, &fx[c], &fy[c]);
-        for (int c = 0; c < nch; ++c) {
-            const int x0 = fx[c], y0 = fy[c], x1 = fx[c + 1], y1 = fy[c + 1];
+        for (int u = 0; u <= nu; ++u)
+            orc_merge_path_search(lmin(ipt * ((int64_t)t * nch + (int64_t)u * cpu), total), row_ptr, n_rows + 1, nnz, &fx[u], &fy[u]);
+        for (int u = 0; u < nu; ++u) {
+            const int x0 = fx[u], y0 = fy[u], x1 = fx[u + 1], y1 = fy[u + 1];
             const int cont = x0 >= 1 && y0 > row_ptr[x0 - 1];
             int x = x0, first = 1;
-            has_head[c] = 0;
+            has_head[u] = 0;
             for (int j = 0; j < dim; ++j) acc[j] = 0.0f;
             for (int k = y0; k <= y1; ++k) {
                 /* consume every marker that precedes non-zero k (all that are left when k == y1) */
                 while (x < x1 && (k == y1 || row_ptr[x] <= k)) {
                     if (x >= 1) {
-                        if (first && cont) { memcpy(head + (size_t)c * dim, acc, sizeof(float) * dim); has_head[c] = 1; }
+                        if (first && cont) { memcpy(head + (size_t)u * dim, acc, sizeof(float) * dim); has_head[u] = 1; }
                         else model_store(&io, x - 1, acc);
                         first = 0;
                         for (int j = 0; j < dim; ++j) acc[j] = 0.0f;
@@ -361,25 +363,25 @@ ORC_API int orc_tile_model(const int *row_ptr, const int *col, const void *val, 
                 const int cc = col[k];
                 for (int j = 0; j < dim; ++j) acc[j] = fmaf(a, model_b(&io, cc, j), acc[j]);
             }
-            memcpy(carry + (size_t)c * dim, acc, sizeof(float) * dim);
+            memcpy(carry + (size_t)u * dim, acc, sizeof(float) * dim);
         }
         /* in-tile fix-up */
-        for (int c = 0; c < nch; ++c) {
-            if (!has_head[c]) continue;
-            int s = c;
-            while (s > 0 && fx[s] == fx[c]) --s;
-            const int from_prev = fx[0] == fx[c] && ty[t] > row_ptr[tx[t] - 1];
+        for (int u = 0; u < nu; ++u) {
+            if (!has_head[u]) continue;
+            int s = u;
+            while (s > 0 && fx[s] == fx[u]) --s;
+            const int from_prev = fx[0] == fx[u] && ty[t] > row_ptr[tx[t] - 1];
             for (int j = 0; j < dim; ++j) sum[j] = 0.0f;
-            for (int q = s; q < c; ++q) for (int j = 0; j < dim; ++j) sum[j] += carry[(size_t)q * dim + j];
-            for (int j = 0; j < dim; ++j) sum[j] += head[(size_t)c * dim + j];
+            for (int q = s; q < u; ++q) for (int j = 0; j < dim; ++j) sum[j] += carry[(size_t)q * dim + j];
+            for (int j = 0; j < dim; ++j) sum[j] += head[(size_t)u * dim + j];
             if (from_prev) memcpy(thead + (size_t)t * dim, sum, sizeof(float) * dim);
-            else model_store(&io, fx[c] - 1, sum);
+            else model_store(&io, fx[u] - 1, sum);
         }
         {
-            int s = nch;
-            while (s > 0 && fx[s] == fx[nch]) --s;
+            int s = nu;
+            while (s > 0 && fx[s] == fx[nu]) --s;
             for (int j = 0; j < dim; ++j) sum[j] = 0.0f;
-            for (int q = s; q < nch; ++q) for (int j = 0; j < dim; ++j) sum[j] += carry[(size_t)q * dim + j];
+            for (int q = s; q < nu; ++q) for (int j = 0; j < dim; ++j) sum[j] += carry[(size_t)q * dim + j];
             memcpy(tcarry + (size_t)t * dim, sum, sizeof(float) * dim);
         }
     }

@@ -47,7 +47,7 @@ def _run(mps, cuda, rp, col, val, B, cost, tune=None, tpw=1):
 
 def _check(orc, rp, col, val, B, got, info, cost, tol):
     half = B.dtype == np.float16
-    model = orc.tile_model(rp, col, val, B, cost, info["chunks_per_tile"], info["long_chain"], is_half=half)
+    model = orc.tile_model(rp, col, val, B, cost, info["chunks_per_tile"], info["chunks_per_unit"], info["long_chain"], is_half=half)
     assert not np.isnan(got.astype(np.float32)).any(), "some element of C was never written"
     same = _bits(got) == _bits(model)
     assert same.all(), f"{(~same).sum()} elements differ from the CPU model (first at {np.argwhere(~same)[0]})"
@@ -164,7 +164,7 @@ def test_edge_case_graphs(mps, orc, cuda, name):
     val = rng.uniform(-1, 1, len(col)).astype(np.float32)
     for dim in (12, 64, 5):
         B = rng.uniform(-1, 1, (n_cols, dim)).astype(np.float32)
-        for cost, tune in ((1, None), (3, dict(chunks_per_tile=8)), (8, None), (8, dict(chunks_per_tile=1)), (32, dict(unroll=4))):
+        for cost, tune in ((1, None), (3, dict(chunks_per_unit=3)), (8, None), (8, dict(chunks_per_unit=1)), (32, dict(unroll=8))):
             got, info = _run(mps, cuda, rp, col, val, B, cost, tune)
             _check(orc, rp, col, val, B, got, info, cost, 1e-5)
 
@@ -173,12 +173,12 @@ def test_long_rows_take_the_strand_fixup(mps, orc, cuda):
     rp, col = cases.edge_cases()["one_giant_row"]
     rng = np.random.default_rng(5)
     B = rng.uniform(-1, 1, (6000, 64)).astype(np.float32)
-    got, info = _run(mps, cuda, rp, col, None, B, 1, dict(chunks_per_tile=2))
+    got, info = _run(mps, cuda, rp, col, None, B, 1, dict(chunks_per_unit=1))
     assert info["long_rows"] >= 1 and info["kernels_per_call"] == 3
     _check(orc, rp, col, None, B, got, info, 1, 1e-5)
 
 
-@pytest.mark.parametrize("tune", [dict(chunks_per_tile=16), dict(chunks_per_tile=48), dict(chunks_per_tile=200, unroll=4),
+@pytest.mark.parametrize("tune", [dict(chunks_per_unit=1), dict(chunks_per_unit=3), dict(chunks_per_unit=20, unroll=4),
                                   dict(unroll=8), dict(bulk_staging=False)])
 def test_tuning_knobs_keep_parity(mps, orc, graphs, cuda, tune):
     rp, col = cases.c1_rmat()
@@ -282,7 +282,7 @@ def test_row_slabs_are_bit_identical_to_their_own_model_and_close_to_the_whole(m
             srp = mps.slab_rebase(rp, r0, r1)
             scol, sval = col[rp[r0]:rp[r1]], val[rp[r0]:rp[r1]]
             got, info = _run(mps, cuda, srp, scol, sval, B, 8)
-            model = orc.tile_model(srp, scol, sval, B, 8, info["chunks_per_tile"], info["long_chain"])
+            model = orc.tile_model(srp, scol, sval, B, 8, info["chunks_per_tile"], info["chunks_per_unit"], info["long_chain"])
             assert np.array_equal(_bits(got), _bits(model))
             parts.append(got)
         cat = np.concatenate(parts)

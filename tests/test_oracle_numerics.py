@@ -46,12 +46,12 @@ def test_c2_shape_is_the_configured_one(graphs):
     assert val.dtype == np.float32 and (val > 0).all() and (val <= 1).all()
 
 
-@pytest.mark.parametrize("dim,cost,nch", [(16, 8, 256), (64, 8, 64), (64, 4, 16), (128, 32, 32), (20, 8, 32), (5, 3, 7)])
-def test_tile_model_close_to_fp64(orc, graphs, dim, cost, nch):
+@pytest.mark.parametrize("dim,cost,nch,cpu", [(16, 8, 256, 4), (64, 8, 64, 4), (64, 4, 16, 1), (128, 32, 32, 4), (20, 8, 32, 32), (5, 3, 7, 1)])
+def test_tile_model_close_to_fp64(orc, graphs, dim, cost, nch, cpu):
     rp, col = cases.c1_rmat()
     val = graphs.gcn_values(rp, col)
     B = _rand_b(len(rp) - 1, dim)
-    got = orc.tile_model(rp, col, val, B, cost, nch, 32)
+    got = orc.tile_model(rp, col, val, B, cost, nch, cpu, 32)
     ref = orc.spmm_f64(rp, col, val, B)
     scale = orc.spmm_abs_f64(rp, col, val, B)
     assert (np.abs(got - ref) <= 1e-6 + 1e-5 * scale).all()
@@ -65,8 +65,8 @@ def test_tile_model_edge_cases(orc, name):
     rng = np.random.default_rng(3)
     val = rng.uniform(-1, 1, len(col)).astype(np.float32)
     B = rng.uniform(-1, 1, (n_cols, 12)).astype(np.float32)
-    for cost, nch, long_chain in ((1, 4, 2), (3, 8, 32), (8, 64, 32), (8, 1, 1)):
-        got = orc.tile_model(rp, col, val, B, cost, nch, long_chain)
+    for cost, nch, cpu, long_chain in ((1, 4, 1, 2), (3, 8, 2, 32), (8, 64, 4, 32), (8, 1, 1, 1), (2, 12, 12, 3)):
+        got = orc.tile_model(rp, col, val, B, cost, nch, cpu, long_chain)
         ref = orc.spmm_f64(rp, col, val, B)
         scale = orc.spmm_abs_f64(rp, col, val, B)
         assert (np.abs(got - ref) <= 1e-6 + 1e-5 * scale).all(), (name, cost, nch)
@@ -77,8 +77,8 @@ def test_tile_model_long_chain_path_is_exercised(orc):
     rp, col = cases.edge_cases()["one_giant_row"]
     rng = np.random.default_rng(5)
     B = rng.uniform(-1, 1, (6000, 8)).astype(np.float32)
-    a = orc.tile_model(rp, col, None, B, 1, 2, 32)
-    b = orc.tile_model(rp, col, None, B, 1, 2, 10**9)  # same chunks, plain order
+    a = orc.tile_model(rp, col, None, B, 1, 2, 1, 32)
+    b = orc.tile_model(rp, col, None, B, 1, 2, 1, 10**9)  # same chunks, plain order
     ref = orc.spmm_f64(rp, col, None, B)
     assert np.allclose(a, ref, rtol=1e-5, atol=1e-4) and np.allclose(b, ref, rtol=1e-5, atol=1e-4)
     assert not np.array_equal(a, b)  # different summation order => some bit differs
@@ -88,7 +88,7 @@ def test_tile_model_fp16(orc, graphs):
     rp, col = cases.c1_rmat()
     val = graphs.gcn_values(rp, col, "f16")
     B = graphs.dense_normal_f16(len(rp) - 1, 32, seed=1)
-    got = orc.tile_model(rp, col, val, B, 8, 64, 32, is_half=True).astype(np.float64)
+    got = orc.tile_model(rp, col, val, B, 8, 64, 4, 32, is_half=True).astype(np.float64)
     ref = orc.spmm_f64(rp, col, val, B, is_half=True)
     scale = orc.spmm_abs_f64(rp, col, val, B, is_half=True)
     assert (np.abs(got - ref) <= 1e-6 + 1e-2 * np.maximum(scale, np.abs(ref))).all()
