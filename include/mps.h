@@ -180,8 +180,8 @@ MPS_API void mps_host_workspace_release(void);
  *
  * Limits: with T = tiles of the automatic layout (mps_plan_info what[3] of an equivalent plan),
  * T <= MPS_NOALLOC_MAX_TILES and T * dim <= MPS_NOALLOC_MAX_CARRY_FLOATS, else MPS_ERR_UNSUPPORTED
- * with the numbers in mps_last_error().  At dim 64, cost 16 that is about 8.9 million merge items
- * (rows + non-zeros).  Every GPU that loads the library holds MPS_NOALLOC_SCRATCH_BYTES for this
+ * with the numbers in mps_last_error().  At dim 64 that is about 70 million merge items (rows +
+ * non-zeros), at dim 128 about 35 million.  Every GPU that loads the library holds MPS_NOALLOC_SCRATCH_BYTES for this
  * array until the process exits.
  *
  * The array is shared by every call on a device: calls that overlap on the GPU race on it, so

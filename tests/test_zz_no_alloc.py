@@ -75,9 +75,12 @@ def test_noalloc_unit_values_and_other_cost(mps, graphs, cuda):
 
 
 def test_noalloc_refuses_what_does_not_fit(mps, cuda):
+    """The shape is refused before any pointer is used.  It is chosen so that it cannot fit under any
+    tile layout: 2*10^9 merge items need more than 32,768 tiles even if a tile filled all of an SM's
+    shared memory (~17k items), so the small buffers passed here are never read."""
     z = torch.zeros(64, dtype=torch.int32, device=cuda)
     f = torch.zeros(64, dtype=torch.float32, device=cuda)
-    rc = mps.capi.lib().mps_spmm_noalloc(1 << 21, 65_000_000, 64, mps.F32, 16, 1, C.c_void_p(z.data_ptr()), C.c_void_p(z.data_ptr()),
+    rc = mps.capi.lib().mps_spmm_noalloc(1 << 24, 2_000_000_000, 128, mps.F32, 8, 1, C.c_void_p(z.data_ptr()), C.c_void_p(z.data_ptr()),
                                          None, C.c_void_p(f.data_ptr()), C.c_void_p(f.data_ptr()), None)
     assert rc == mps.capi.ERR_UNSUPPORTED
     msg = mps.capi.lib().mps_last_error().decode()
