@@ -52,6 +52,7 @@ def parse_args():
     ap.add_argument("--no-bulk", action="store_true")
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--skip-baselines", action="store_true", help="leave out cpu_baseline and reference_gpu (tuning runs)")
+    ap.add_argument("--balance", default="items", choices=["nnz", "items"], help="row slabs of equal non-zeros or equal rows+non-zeros")
     ap.add_argument("--gather-c", action="store_true", help="also time an NCCL all-gather of the C slabs (N > 1)")
     return ap.parse_args()
 
@@ -138,6 +139,17 @@ def max_over_ranks(x: float, world: int) -> float:
     return float(t.item())
 
 
+def all_ranks(x: float, world: int):
+    import torch
+    if world == 1:
+        return [round(x, 4)]
+    import torch.distributed as dist
+    t = torch.tensor([x], dtype=torch.float64, device="cuda")
+    out = [torch.zeros_like(t) for _ in range(world)]
+    dist.all_gather(out, t)
+    return [round(float(o.item()), 4) for o in out]
+
+
 def sum_over_ranks(x: float, world: int) -> float:
     import torch
     if world == 1:
@@ -160,7 +172,7 @@ def build_workload(args, world, rank, dev):
     half = args.dtype == "f16"
     val = graphs.gcn_values(rp, col, "f16" if half else "f32")
     if world > 1:
-        bounds = mps.slab_bounds(rp.cpu().numpy(), world)
+        bounds = mps.slab_bounds(rp.cpu().numpy(), world, args.balance)
         r0, r1 = int(bounds[rank]), int(bounds[rank + 1])
         k0, k1 = int(rp[r0].item()), int(rp[r1].item())
         s_rp = (rp[r0:r1 + 1] - k0).contiguous()
@@ -214,7 +226,9 @@ def run_ours(args):
             plan.spmm(w["rp"], w["col"], w["val"], w["B"], out=C_out)
         ev1.record()
         barrier(world)
-    ms_total = max_over_ranks(ev0.elapsed_time(ev1), world)
+    ms_mine = ev0.elapsed_time(ev1)
+    ms_total = max_over_ranks(ms_mine, world)
+    per_rank_ms = all_ranks(ms_mine / args.steps, world)
     tile_ms, tile_launches = plan.profile_read()
     plan.profile(False)
     plan.sync_check()
@@ -273,7 +287,7 @@ def run_ours(args):
         "warmup": max(args.warmup, 3), "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f16 storage / f32 accumulate" if w["half"] else "f32", "data": "synthetic",
         "config": {"workload": workload_name(args, world), "nodes": w["n"], "nnz": w["nnz"], "dim": args.dim, "cost": cost,
-                   "threads_per_warp": info["threads_per_warp"], "values": "gcn", "parallelism": f"row-slabs x{world}, B replicated",
+                   "threads_per_warp": info["threads_per_warp"], "values": "gcn", "parallelism": f"row-slabs x{world} ({args.balance}-balanced), B replicated", "per_rank_ms": per_rank_ms,
                    "l2": "inputs larger than L2 (B and A each > 126 MB)", "chunks_per_tile": info["chunks_per_tile"], "chunks_per_unit": info["chunks_per_unit"],
                    "items_per_chunk": info["items_per_chunk"], "unroll": info["unroll"], "tiles": info["n_tiles"],
                    "long_rows": info["long_rows"]},
@@ -328,12 +342,13 @@ def cpu_baseline(host, dim, nnz, half):
     val = host["val"].astype(np.float32) if half else host["val"]
     B = host["B"].astype(np.float32) if half else host["B"]
     out = np.empty((len(host["rp"]) - 1, dim), np.float32)
-    _, cores = orc.spmm_f32_omp(host["rp"], host["col"], val, B, out=out)
+    threads = len(os.sched_getaffinity(0))  # explicit: launchers such as torchrun export OMP_NUM_THREADS=1
+    _, cores = orc.spmm_f32_omp(host["rp"], host["col"], val, B, out=out, threads=threads)
     best = float("inf")
     t_all = time.perf_counter()
     for _ in range(3):
         t0 = time.perf_counter()
-        orc.spmm_f32_omp(host["rp"], host["col"], val, B, out=out)
+        orc.spmm_f32_omp(host["rp"], host["col"], val, B, out=out, threads=threads)
         best = min(best, time.perf_counter() - t0)
         if time.perf_counter() - t_all > 25:
             break
@@ -428,11 +443,12 @@ def run_reference_cpu(args):
     B = graphs.dense_uniform(n, args.dim, args.seed + 1)
     out = np.empty((n, args.dim), np.float32)
     cores = 1
+    threads = len(os.sched_getaffinity(0))  # explicit: launchers such as torchrun export OMP_NUM_THREADS=1
     for _ in range(max(args.warmup, 1)):
-        _, cores = orc.spmm_f32_omp(rp, col, val, B, out=out)
+        _, cores = orc.spmm_f32_omp(rp, col, val, B, out=out, threads=threads)
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        orc.spmm_f32_omp(rp, col, val, B, out=out)
+        orc.spmm_f32_omp(rp, col, val, B, out=out, threads=threads)
     s = (time.perf_counter() - t0) / args.steps
     v = round(2.0 * nnz * args.dim / s / 1e9, 3)
     sample = f"R-MAT scale {scale} (of {args.scale}), avg degree {args.avg_degree}, {nnz} nnz, dim {args.dim}: one full SpMM per step"

@@ -240,10 +240,13 @@ def load_csr_bin(path: str):
     return rp, col, v
 
 
-def slab_bounds(row_ptr, n_slabs: int):
+def slab_bounds(row_ptr, n_slabs: int, balance: str = "nnz"):
+    """Row slab boundaries for n_slabs devices; balance = "nnz" (equal non-zeros) or "items"
+    (equal rows + non-zeros, the merge path's own cost measure)."""
     rp = np.ascontiguousarray(row_ptr, np.int32)
     b = np.empty(n_slabs + 1, np.int32)
-    capi.check(capi.lib().mps_slab_bounds(rp.ctypes.data_as(C.c_void_p), len(rp) - 1, n_slabs, b.ctypes.data_as(C.c_void_p)))
+    fn = capi.lib().mps_slab_bounds_items if balance == "items" else capi.lib().mps_slab_bounds
+    capi.check(fn(rp.ctypes.data_as(C.c_void_p), len(rp) - 1, n_slabs, b.ctypes.data_as(C.c_void_p)))
     return b
 
 

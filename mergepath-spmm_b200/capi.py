@@ -18,7 +18,7 @@ SYMBOLS = [
     "mps_last_error", "mps_version", "mps_csr_load", "mps_csr_free", "mps_csr_save", "mps_csr_save_bin",
     "mps_csr_load_bin", "mps_chunk_count", "mps_partition_device", "mps_schedule_device", "mps_plan_create",
     "mps_plan_destroy", "mps_plan_tune", "mps_plan_partition", "mps_spmm", "mps_plan_sync_check", "mps_plan_info", "mps_plan_profile", "mps_plan_profile_read",
-    "mps_algorithmic_bytes", "mps_spmm_host", "mps_host_workspace_release", "mps_spmm_noalloc", "mps_slab_bounds", "mps_slab_rebase",
+    "mps_algorithmic_bytes", "mps_spmm_host", "mps_host_workspace_release", "mps_spmm_noalloc", "mps_slab_bounds", "mps_slab_bounds_items", "mps_slab_rebase",
 ]
 
 
@@ -73,6 +73,7 @@ def lib():
     L.mps_host_workspace_release.restype = None
     L.mps_spmm_noalloc.argtypes = [i32, i32, i32, C.c_int, i32, i32, vp, vp, vp, vp, vp, vp]
     L.mps_slab_bounds.argtypes = [vp, i32, i32, vp]
+    L.mps_slab_bounds_items.argtypes = [vp, i32, i32, vp]
     L.mps_slab_rebase.argtypes = [vp, i32, i32, vp]
     _lib = L
     return L

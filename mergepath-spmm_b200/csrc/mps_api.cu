@@ -446,6 +446,24 @@ extern "C" int mps_slab_bounds(const int32_t *row_ptr, int32_t n_rows, int32_t n
     return MPS_OK;
 }
 
+extern "C" int mps_slab_bounds_items(const int32_t *row_ptr, int32_t n_rows, int32_t n_slabs, int32_t *bounds) {
+    if (!row_ptr || !bounds || n_rows < 0 || n_slabs < 1) return fail(MPS_ERR_ARG, "mps_slab_bounds_items: bad argument");
+    const long long items = (long long)row_ptr[n_rows] + n_rows;
+    bounds[0] = 0;
+    for (int g = 1; g < n_slabs; ++g) {
+        const long long want = items * g / n_slabs;
+        int lo = 0, hi = n_rows;
+        while (lo < hi) {
+            const int mid = (lo + hi) >> 1;
+            if ((long long)row_ptr[mid] + mid < want) lo = mid + 1;
+            else hi = mid;
+        }
+        bounds[g] = lo;
+    }
+    bounds[n_slabs] = n_rows;
+    return MPS_OK;
+}
+
 extern "C" int mps_slab_rebase(const int32_t *row_ptr, int32_t row0, int32_t row1, int32_t *out_row_ptr) {
     if (!row_ptr || !out_row_ptr || row0 < 0 || row1 < row0) return fail(MPS_ERR_ARG, "mps_slab_rebase: bad argument");
     const int32_t base = row_ptr[row0];

@@ -79,5 +79,11 @@ def test_slab_bounds_match_oracle_and_balance(mps, orc):
         assert per.sum() == nnz
         biggest_row = int(np.diff(rp).max())
         assert per.max() <= nnz / g + biggest_row
+    n = len(rp) - 1
+    for g in (2, 4, 8):
+        bi = mps.slab_bounds(rp, g, "items")
+        assert bi[0] == 0 and bi[-1] == n and (np.diff(bi) >= 0).all()
+        items = np.diff(rp[bi].astype(np.int64) + bi)
+        assert items.sum() == nnz + n and items.max() <= (nnz + n) / g + biggest_row + 1
     sl = mps.slab_rebase(rp, int(b[1]), int(b[2]))
     assert sl[0] == 0 and sl[-1] == rp[b[2]] - rp[b[1]]
