@@ -4,6 +4,7 @@
     python bench.py [--gpus N --steps K --warmup W]            this library (one rank per GPU)
     python bench.py --impl reference ...                       host-CPU arm (see below)
     python bench.py --impl reference-gpu ...                   the reference's CUDA kernels on the GPU
+    python bench.py --impl baselines ...                       every reported GPU baseline on one GPU
 
 Workload (seeded, synthetic; stands in for the reference's public graph suite): an R-MAT graph
 with 2^21 nodes per GPU and average degree 32 (~67M non-zeros per GPU), GCN-normalised fp32
@@ -39,7 +40,7 @@ def parse_args():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-gpu"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-gpu", "baselines"])
     ap.add_argument("--scale", type=int, default=21, help="log2 of nodes per GPU")
     ap.add_argument("--avg-degree", type=int, default=32)
     ap.add_argument("--dim", type=int, default=64)
@@ -53,6 +54,8 @@ def parse_args():
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--skip-baselines", action="store_true", help="leave out cpu_baseline and reference_gpu (tuning runs)")
     ap.add_argument("--balance", default="items", choices=["nnz", "items"], help="row slabs of equal non-zeros or equal rows+non-zeros")
+    ap.add_argument("--row-weight", type=int, default=4, help="cost of a row in non-zeros for --balance items")
+    ap.add_argument("--strong", action="store_true", help="keep the graph fixed as N grows (strong scaling) instead of 2^scale nodes per GPU")
     ap.add_argument("--gather-c", action="store_true", help="also time an NCCL all-gather of the C slabs (N > 1)")
     return ap.parse_args()
 
@@ -165,14 +168,13 @@ def build_workload(args, world, rank, dev):
     import torch
     from mergepath_spmm_b200 import graphs
     mps = entry.load_package()
-    scale = args.scale + int(round(np.log2(world)))
-    assert 1 << (scale - args.scale) == world, "--gpus must be a power of two"
+    scale = total_scale(args, world)
     rp, col = graphs.rmat_csr(scale, args.avg_degree, args.seed, device=dev)
     n, nnz = rp.numel() - 1, col.numel()
     half = args.dtype == "f16"
     val = graphs.gcn_values(rp, col, "f16" if half else "f32")
     if world > 1:
-        bounds = mps.slab_bounds(rp.cpu().numpy(), world, args.balance)
+        bounds = mps.slab_bounds(rp.cpu().numpy(), world, args.balance, args.row_weight)
         r0, r1 = int(bounds[rank]), int(bounds[rank + 1])
         k0, k1 = int(rp[r0].item()), int(rp[r1].item())
         s_rp = (rp[r0:r1 + 1] - k0).contiguous()
@@ -185,11 +187,19 @@ def build_workload(args, world, rank, dev):
         B = graphs.dense_normal_f16(n, args.dim, args.seed + 1, device=dev)
     else:
         B = graphs.dense_uniform(n, args.dim, args.seed + 1, device=dev)
-    return dict(n=n, nnz=nnz, scale=scale, r0=r0, r1=r1, rp=s_rp, col=s_col, val=s_val, B=B, half=half)
+    return dict(n=n, nnz=nnz, scale=scale, r0=r0, r1=r1, slab_nnz=int(s_col.numel()), rp=s_rp, col=s_col, val=s_val, B=B, half=half)
+
+
+def total_scale(args, world):
+    if args.strong:
+        return args.scale
+    lg = int(round(np.log2(world)))
+    assert 1 << lg == world, "--gpus must be a power of two"
+    return args.scale + lg
 
 
 def workload_name(args, world):
-    return f"rmat{args.scale + int(round(np.log2(world)))}_deg{args.avg_degree}_gcn_{args.dtype}_dim{args.dim}"
+    return f"rmat{total_scale(args, world)}_deg{args.avg_degree}_gcn_{args.dtype}_dim{args.dim}"
 
 
 def run_ours(args):
@@ -284,10 +294,10 @@ def run_ours(args):
 
     out = {
         "metric": "SpMM GFLOP/s (2*nnz*dim/t)", "value": round(value, 2), "unit": "GFLOP/s", "n_gpus": world, "steps": args.steps,
-        "warmup": max(args.warmup, 3), "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "weak",
+        "warmup": max(args.warmup, 3), "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "strong" if args.strong else "weak",
         "vs_baseline": None, "dtype": "f16 storage / f32 accumulate" if w["half"] else "f32", "data": "synthetic",
         "config": {"workload": workload_name(args, world), "nodes": w["n"], "nnz": w["nnz"], "dim": args.dim, "cost": cost,
-                   "threads_per_warp": info["threads_per_warp"], "values": "gcn", "parallelism": f"row-slabs x{world} ({args.balance}-balanced), B replicated", "per_rank_ms": per_rank_ms,
+                   "threads_per_warp": info["threads_per_warp"], "values": "gcn", "parallelism": f"row-slabs x{world} ({args.balance}-balanced, row weight {args.row_weight}), B replicated", "per_rank_ms": per_rank_ms, "per_rank_rows": [int(v) for v in all_ranks(float(n_slab), world)], "per_rank_nnz": [int(v) for v in all_ranks(float(nnz_slab), world)],
                    "l2": "inputs larger than L2 (B and A each > 126 MB)", "chunks_per_tile": info["chunks_per_tile"], "chunks_per_unit": info["chunks_per_unit"],
                    "items_per_chunk": info["items_per_chunk"], "unroll": info["unroll"], "tiles": info["n_tiles"],
                    "long_rows": info["long_rows"]},
@@ -405,6 +415,127 @@ def reference_gpu(w, args, dev, steps=5, cost=8):
             "steps": steps}
 
 
+def _lib(name):
+    path = os.path.join(ROOT, "oracle", "_ref", name)
+    if not os.path.exists(path):
+        raise RuntimeError(f"oracle/_ref/{name} is not built")
+    return C.CDLL(path)
+
+
+def _timed(fn, steps, before=None):
+    import torch
+    times = []
+    for i in range(steps + 1):
+        if before:
+            before()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        rc = fn()
+        e1.record()
+        torch.cuda.synchronize()
+        if rc != 0:
+            raise RuntimeError(f"launch returned {rc}")
+        if i:
+            times.append(e0.elapsed_time(e1))
+    return float(np.median(times))
+
+
+def run_baselines(args):
+    """Reported baselines on one GPU, same graph and B as the default workload, unit values (the
+    reference programs have none): the reference merge-path kernels, its row_wise and nz_splitting
+    programs' kernels (unmodified, from oracle/_ref), cuSPARSE row- and column-major set up as the
+    reference's cusparse_spmm_{row,col}.cu do, and this library with unit values.  One JSON line."""
+    import torch
+    rank, world, local = dist_setup(args)
+    if rank != 0:
+        return
+    dev = torch.device("cuda", local)
+    mps = entry.load_package()
+    w = build_workload(args, 1, 0, dev)
+    n, nnz, dim = w["n"], w["nnz"], args.dim
+    vp, ci = C.c_void_p, C.c_int
+    flops = 2.0 * nnz * dim
+    res = {}
+
+    def rec(name, ms, **kw):
+        res[name] = {"ms": round(ms, 4), "gflops": round(flops / ms / 1e6, 1), **kw}
+
+    steps = max(min(args.steps, 10), 1)
+    # this library, unit values and GCN values
+    plan = mps.Plan(n, nnz, dim, mps.F32, args.cost or DEFAULT_COST, args.tpw, device=dev)
+    plan.partition(w["rp"])
+    Cm = torch.empty((n, dim), dtype=torch.float32, device=dev)
+    for name, val in (("this_library_unit_values", None), ("this_library_gcn_values", w["val"])):
+        for _ in range(3):
+            plan.spmm(w["rp"], w["col"], val, w["B"], out=Cm)
+        rec(name, _timed(lambda: (plan.spmm(w["rp"], w["col"], val, w["B"], out=Cm), 0)[1], steps), cost=args.cost or DEFAULT_COST)
+    plan.close()
+    del Cm
+    # reference merge-path kernel at each cost of the configured sweep
+    for cost in (4, 8, 16, 32):
+        try:
+            r = reference_gpu(w, args, dev, steps=3, cost=cost)
+            rec(f"reference_mergepath_cost{cost}", r["ms_per_step"], kernel=r["kernel"])
+        except Exception as e:
+            res[f"reference_mergepath_cost{cost}"] = {"unavailable": str(e)[:160]}
+    deg = torch.ones(n + 1, dtype=torch.int32, device=dev)
+    B1 = torch.zeros((n + 1, dim), dtype=torch.float32, device=dev)
+    B1[:n] = w["B"]
+    Cr = torch.zeros((n + 1, dim), dtype=torch.float32, device=dev)
+    if (n + 1) * dim < 2 ** 31:
+        # row_wise: dim <= 32 only
+        try:
+            if dim > 32:
+                raise RuntimeError("row_wise computes one column per lane: dim <= 32 only (src/row_wise.cu:222)")
+            lib = _lib("libref_row_wise.so")
+            lib.baseh_row_wise.argtypes = [vp] * 5 + [ci] * 3
+            nw = max(n // 8, 1)
+            rec("reference_row_wise", _timed(lambda: lib.baseh_row_wise(Cr.data_ptr(), B1.data_ptr(), w["rp"].data_ptr(), w["col"].data_ptr(),
+                                                                        deg.data_ptr(), n, dim, nw), 3), num_warps=nw)
+        except Exception as e:
+            res["reference_row_wise"] = {"unavailable": str(e)[:160]}
+        # nz_splitting (GNNAdvisor-opt)
+        try:
+            lib = _lib("libref_nz_splitting.so")
+            part = min(dim, 32)
+            i32p = np.ctypeslib.ndpointer(np.int32, flags="C_CONTIGUOUS")
+            lib.baseh_nz_count.argtypes = [i32p, ci, ci]
+            lib.baseh_nz_build.argtypes = [i32p, ci, ci, ci, i32p, i32p]
+            lib.baseh_nz_launch.argtypes = [vp] * 7 + [ci] * 4
+            h_rp = w["rp"].cpu().numpy()
+            num_parts = lib.baseh_nz_count(h_rp, n, part)
+            pp, p2n = np.zeros(num_parts + 1, np.int32), np.zeros(num_parts, np.int32)
+            lib.baseh_nz_build(h_rp, n, part, num_parts, pp, p2n)
+            d_pp, d_p2n = torch.from_numpy(pp).to(dev), torch.from_numpy(p2n).to(dev)
+            rec("reference_nz_splitting", _timed(lambda: lib.baseh_nz_launch(Cr.data_ptr(), B1.data_ptr(), w["rp"].data_ptr(), w["col"].data_ptr(),
+                                                                             deg.data_ptr(), d_pp.data_ptr(), d_p2n.data_ptr(), n, dim, num_parts, part),
+                                                 3, before=Cr.zero_), part_size=part, num_parts=int(num_parts))
+            del d_pp, d_p2n
+        except Exception as e:
+            res["reference_nz_splitting"] = {"unavailable": str(e)[:160]}
+    del B1, Cr, deg
+    # cuSPARSE, row- and column-major dense operands, values = 1
+    try:
+        lib = _lib("libcusparse_baseline.so")
+        lib.cush_spmm.argtypes = [ci] * 4 + [vp] * 5 + [ci, ci, C.POINTER(C.c_float)]
+        ones = torch.ones(nnz, dtype=torch.float32, device=dev)
+        Cc = torch.empty((n, dim), dtype=torch.float32, device=dev)
+        for name, colmajor, Bop in (("cusparse_row_major", 0, w["B"]), ("cusparse_col_major", 1, w["B"].t().contiguous())):
+            ms = C.c_float()
+            rc = lib.cush_spmm(n, n, nnz, dim, w["rp"].data_ptr(), w["col"].data_ptr(), ones.data_ptr(), Bop.data_ptr(), Cc.data_ptr(),
+                               colmajor, steps, C.byref(ms))
+            if rc != 0:
+                res[name] = {"unavailable": f"cusparse step {rc} failed"}
+            else:
+                rec(name, ms.value, alg="CUSPARSE_SPMM_ALG_DEFAULT")
+    except Exception as e:
+        res["cusparse"] = {"unavailable": str(e)[:160]}
+    print(json.dumps({"impl": "baselines", "metric": "SpMM GFLOP/s (2*nnz*dim/t)", "unit": "GFLOP/s", "n_gpus": 1,
+                      "config": {"workload": workload_name(args, 1), "nodes": n, "nnz": nnz, "dim": dim, "values": "unit unless named"},
+                      "results": res}), flush=True)
+
+
 def run_reference_gpu(args):
     import torch
     rank, world, local = dist_setup(args)
@@ -469,6 +600,8 @@ def main():
         run_reference_cpu(args)
     elif args.impl == "reference-gpu":
         run_reference_gpu(args)
+    elif args.impl == "baselines":
+        run_baselines(args)
     else:
         run_ours(args)
 

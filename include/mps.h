@@ -202,11 +202,13 @@ MPS_API int mps_spmm_noalloc(int32_t n_rows, int32_t nnz, int32_t dim, int dtype
  * bounds[0] = 0, bounds[n_slabs] = n_rows.  Host row_ptr. */
 MPS_API int mps_slab_bounds(const int32_t *row_ptr, int32_t n_rows, int32_t n_slabs, int32_t *bounds);
 
-/* As mps_slab_bounds, but equalising merge items (rows + non-zeros) instead of non-zeros alone:
- * bounds[g] = first row r with row_ptr[r] + r >= g*(nnz + n_rows)/n_slabs.  A slab of many short
- * rows writes far more of C than a slab of few long ones with the same non-zero count; counting a
- * row like a non-zero evens out the time per device. */
-MPS_API int mps_slab_bounds_items(const int32_t *row_ptr, int32_t n_rows, int32_t n_slabs, int32_t *bounds);
+/* As mps_slab_bounds, but equalising weighted merge items, non-zeros + row_weight * rows:
+ * bounds[g] = first row r with row_ptr[r] + row_weight*r >= g*(nnz + row_weight*n_rows)/n_slabs.
+ * A slab of many short rows writes far more of C (and ends far more rows) than a slab of few long
+ * ones with the same non-zero count; row_weight = 1 is the merge path's own cost measure,
+ * larger values charge a row end more than a gathered non-zero.  row_weight >= 0. */
+MPS_API int mps_slab_bounds_items(const int32_t *row_ptr, int32_t n_rows, int32_t n_slabs, int32_t row_weight,
+                          int32_t *bounds);
 
 /* Slab g of a host CSR with row_ptr rebased to 0: writes row1 - row0 + 1 entries. */
 MPS_API int mps_slab_rebase(const int32_t *row_ptr, int32_t row0, int32_t row1, int32_t *out_row_ptr);

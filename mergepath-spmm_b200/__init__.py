@@ -240,13 +240,16 @@ def load_csr_bin(path: str):
     return rp, col, v
 
 
-def slab_bounds(row_ptr, n_slabs: int, balance: str = "nnz"):
+def slab_bounds(row_ptr, n_slabs: int, balance: str = "nnz", row_weight: int = 1):
     """Row slab boundaries for n_slabs devices; balance = "nnz" (equal non-zeros) or "items"
-    (equal rows + non-zeros, the merge path's own cost measure)."""
+    (equal non-zeros + row_weight * rows; row_weight 1 is the merge path's own cost measure)."""
     rp = np.ascontiguousarray(row_ptr, np.int32)
     b = np.empty(n_slabs + 1, np.int32)
-    fn = capi.lib().mps_slab_bounds_items if balance == "items" else capi.lib().mps_slab_bounds
-    capi.check(fn(rp.ctypes.data_as(C.c_void_p), len(rp) - 1, n_slabs, b.ctypes.data_as(C.c_void_p)))
+    rpp, bp = rp.ctypes.data_as(C.c_void_p), b.ctypes.data_as(C.c_void_p)
+    if balance == "items":
+        capi.check(capi.lib().mps_slab_bounds_items(rpp, len(rp) - 1, n_slabs, row_weight, bp))
+    else:
+        capi.check(capi.lib().mps_slab_bounds(rpp, len(rp) - 1, n_slabs, bp))
     return b
 
 

@@ -73,7 +73,7 @@ def lib():
     L.mps_host_workspace_release.restype = None
     L.mps_spmm_noalloc.argtypes = [i32, i32, i32, C.c_int, i32, i32, vp, vp, vp, vp, vp, vp]
     L.mps_slab_bounds.argtypes = [vp, i32, i32, vp]
-    L.mps_slab_bounds_items.argtypes = [vp, i32, i32, vp]
+    L.mps_slab_bounds_items.argtypes = [vp, i32, i32, i32, vp]
     L.mps_slab_rebase.argtypes = [vp, i32, i32, vp]
     _lib = L
     return L

@@ -9,7 +9,7 @@
 //
 // Options (all optional, after the positionals):
 //   --dtype=f32|f16   --values=unit|gcn   --check   --device=K
-//   --gpus=G          row slabs of equal nnz over G devices of this node, one host thread per device
+//   --gpus=G          row slabs of equal (nnz + 4*rows) over G devices of this node, one host thread per device
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
@@ -176,7 +176,7 @@ int main(int argc, char *argv[]) {
     if (o.gpus > visible) { fprintf(stderr, "error: --gpus=%d but only %d devices are visible\n", o.gpus, visible); return 1; }
 
     std::vector<int32_t> bounds((size_t)o.gpus + 1);
-    if (mps_slab_bounds(g.row_ptr, g.n_rows, o.gpus, bounds.data()) != MPS_OK) { fprintf(stderr, "error: %s\n", mps_last_error()); return 1; }
+    if (mps_slab_bounds_items(g.row_ptr, g.n_rows, o.gpus, /*row_weight=*/4, bounds.data()) != MPS_OK) { fprintf(stderr, "error: %s\n", mps_last_error()); return 1; }
     std::vector<SlabResult> res((size_t)o.gpus);
     std::vector<std::thread> th;
     for (int s = 0; s < o.gpus; ++s)

@@ -446,16 +446,17 @@ extern "C" int mps_slab_bounds(const int32_t *row_ptr, int32_t n_rows, int32_t n
     return MPS_OK;
 }
 
-extern "C" int mps_slab_bounds_items(const int32_t *row_ptr, int32_t n_rows, int32_t n_slabs, int32_t *bounds) {
-    if (!row_ptr || !bounds || n_rows < 0 || n_slabs < 1) return fail(MPS_ERR_ARG, "mps_slab_bounds_items: bad argument");
-    const long long items = (long long)row_ptr[n_rows] + n_rows;
+extern "C" int mps_slab_bounds_items(const int32_t *row_ptr, int32_t n_rows, int32_t n_slabs, int32_t row_weight, int32_t *bounds) {
+    if (!row_ptr || !bounds || n_rows < 0 || n_slabs < 1 || row_weight < 0) return fail(MPS_ERR_ARG, "mps_slab_bounds_items: bad argument");
+    const long long w = row_weight;
+    const long long items = (long long)row_ptr[n_rows] + w * n_rows;
     bounds[0] = 0;
     for (int g = 1; g < n_slabs; ++g) {
         const long long want = items * g / n_slabs;
         int lo = 0, hi = n_rows;
         while (lo < hi) {
             const int mid = (lo + hi) >> 1;
-            if ((long long)row_ptr[mid] + mid < want) lo = mid + 1;
+            if ((long long)row_ptr[mid] + w * mid < want) lo = mid + 1;
             else hi = mid;
         }
         bounds[g] = lo;

@@ -81,9 +81,11 @@ def test_slab_bounds_match_oracle_and_balance(mps, orc):
         assert per.max() <= nnz / g + biggest_row
     n = len(rp) - 1
     for g in (2, 4, 8):
-        bi = mps.slab_bounds(rp, g, "items")
-        assert bi[0] == 0 and bi[-1] == n and (np.diff(bi) >= 0).all()
-        items = np.diff(rp[bi].astype(np.int64) + bi)
-        assert items.sum() == nnz + n and items.max() <= (nnz + n) / g + biggest_row + 1
+        for w in (1, 4):
+            bi = mps.slab_bounds(rp, g, "items", w)
+            assert bi[0] == 0 and bi[-1] == n and (np.diff(bi) >= 0).all()
+            items = np.diff(rp[bi].astype(np.int64) + w * bi.astype(np.int64))
+            assert items.sum() == nnz + w * n and items.max() <= (nnz + w * n) / g + biggest_row + w
+        assert np.array_equal(mps.slab_bounds(rp, g, "items", 0), mps.slab_bounds(rp, g))
     sl = mps.slab_rebase(rp, int(b[1]), int(b[2]))
     assert sl[0] == 0 and sl[-1] == rp[b[2]] - rp[b[1]]
