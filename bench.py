@@ -497,6 +497,13 @@ def run_baselines(args):
             res["reference_row_wise"] = {"unavailable": str(e)[:160]}
         # nz_splitting (GNNAdvisor-opt)
         try:
+            if dim <= 32:
+                # src/nz_splitting.cu:412-424: the dim <= 32 kernel guards with warpId < num_parts although each warp
+                # takes 32/dim parts, so the last block reads part_pointers/part2Node up to 8*(32/dim) entries past
+                # their end and then row data at whatever index it found there.  With the arrays sized as the
+                # reference's main() sizes them this raised an illegal memory access on a B200; not run again.
+                raise RuntimeError("reference kernel reads past its part arrays for dim <= 32 (guard at nz_splitting.cu:412); "
+                                   "faulted with an illegal memory access on B200, not run again")
             lib = _lib("libref_nz_splitting.so")
             part = min(dim, 32)
             i32p = np.ctypeslib.ndpointer(np.int32, flags="C_CONTIGUOUS")
