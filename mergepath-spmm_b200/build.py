@@ -13,7 +13,7 @@ LIB = os.path.join(LIBDIR, "libmps_b200.so")
 CLI = os.path.join(LIBDIR, "MergePathSpMM")
 
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
-COMMON = ["-O3", "-std=c++17", "-lineinfo", "-I" + os.path.join(ROOT, "include"), "-I" + CSRC]
+COMMON = ["-O3", "-std=c++17", "-lineinfo", "-I" + os.path.join(ROOT, "include"), "-I" + CSRC] + os.environ.get("MPS_EXTRA_NVCC_FLAGS", "").split()
 
 
 def _nvcc() -> str:

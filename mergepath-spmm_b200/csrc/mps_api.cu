@@ -102,6 +102,7 @@ static int pow2_at_least(int v) {
 }
 
 static const int kSmemTarget = 64 * 1024;   // three tile blocks per SM, which the registers allow anyway
+static const int kTilesPerSm = 6;            // smaller tiles rather than idle SMs on small problems
 static const int kTileItems = 4352;          // merge items per tile the automatic layout aims for
 static const int kSmemLimit = 200 * 1024;
 
@@ -111,8 +112,17 @@ static int plan_layout(mps_plan *p) {
     if (!p->user_unroll) p->unroll = 8;
     if (p->vec == 1) p->unroll = 4;
     if (!p->user_cpu) {
-        // about kTileItems merge items per tile, as long as the windows fit the shared-memory target
-        int cpu = kTileItems / (gpc * p->ipt);
+        // about kTileItems merge items per tile, fewer when the whole problem would otherwise leave SMs without
+        // a tile (at least kTilesPerSm tiles per SM), as long as the windows fit the shared-memory target
+        if (p->sm_count <= 0) {
+            int dev = 0, sms = 0;
+            if (cudaGetDevice(&dev) == cudaSuccess && cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess) p->sm_count = sms;
+            if (p->sm_count <= 0) p->sm_count = 148;
+        }
+        const long long total = (long long)p->n_rows + 1 + p->nnz;
+        long long items = total / ((long long)p->sm_count * kTilesPerSm);
+        if (items > kTileItems) items = kTileItems;
+        int cpu = (int)(items / ((long long)gpc * p->ipt));
         if (cpu < 1) cpu = 1;
         if (cpu > 64) cpu = 64;
         while (cpu > 1 && TileSmem(gpc, gpc * cpu * p->ipt, p->slab_cols, elem).bytes > kSmemTarget) --cpu;

@@ -12,7 +12,7 @@ struct mps_plan {
     int nch, cpu, n_tiles, smem_bytes;  // chunks per tile, chunks per unit
     int bulk;
     int long_chain, n_long, long_capacity;
-    int device;
+    int device, sm_count;
     bool user_cpu, user_unroll;
     bool partitioned;
     int2 *d_tile_xy;
