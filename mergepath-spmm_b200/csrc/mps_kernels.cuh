@@ -121,9 +121,16 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 __device__ __forceinline__ void mbar_arrive_expect(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
-__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-                 "l"(src), "r"(bytes), "r"(bar)
+// L2 policy for data that is read once (the CSR windows): evict first, so that the streamed arrays do
+// not displace rows of B, which are the only data with reuse.
+__device__ __forceinline__ uint64_t l2_evict_first_policy() {
+    uint64_t policy;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+    return policy;
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar, uint64_t policy) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(dst),
+                 "l"(src), "r"(bytes), "r"(bar), "l"(policy)
                  : "memory");
 }
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
@@ -320,10 +327,11 @@ __global__ void __launch_bounds__(kBlock, MPS_MIN_BLOCKS) spmm_tile_kernel(const
             const uint32_t n_rp = (uint32_t)(rp_be - rp_base) * 4u;
             const uint32_t n_col = (uint32_t)(y_be - y_base) * 4u;
             const uint32_t n_val = has_val ? (uint32_t)(y_be - y_base) * (uint32_t)sizeof(T) : 0u;
+            const uint64_t once = l2_evict_first_policy();
             mbar_arrive_expect(bar, n_rp + n_col + n_val);  // the single arrival the phase waits for
-            if (n_rp) bulk_g2s(smem_u32(s_rp), p.rp + rp_base, n_rp, bar);
-            if (n_col) bulk_g2s(smem_u32(s_col), p.col + y_base, n_col, bar);
-            if (n_val) bulk_g2s(smem_u32(s_val), static_cast<const T *>(p.val) + y_base, n_val, bar);
+            if (n_rp) bulk_g2s(smem_u32(s_rp), p.rp + rp_base, n_rp, bar, once);
+            if (n_col) bulk_g2s(smem_u32(s_col), p.col + y_base, n_col, bar, once);
+            if (n_val) bulk_g2s(smem_u32(s_val), static_cast<const T *>(p.val) + y_base, n_val, bar, once);
         }
         stage_ragged<int>(s_rp, p.rp, rp_base, rp_be, X1, tid);
         stage_ragged<int>(s_col, p.col, y_base, y_be, Y1, tid);
