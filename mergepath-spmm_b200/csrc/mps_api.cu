@@ -103,6 +103,7 @@ static int pow2_at_least(int v) {
 
 static const int kSmemTarget = 64 * 1024;   // three tile blocks per SM, which the registers allow anyway
 static const int kTilesPerSm = 6;            // smaller tiles rather than idle SMs on small problems
+static const int kUnitItems = 272;           // merge items one lane group walks per tile, at most
 static const int kTileItems = 4352;          // merge items per tile the automatic layout aims for
 static const int kSmemLimit = 200 * 1024;
 
@@ -122,6 +123,7 @@ static int plan_layout(mps_plan *p) {
         const long long total = (long long)p->n_rows + 1 + p->nnz;
         long long items = total / ((long long)p->sm_count * kTilesPerSm);
         if (items > kTileItems) items = kTileItems;
+        if (items > (long long)gpc * kUnitItems) items = (long long)gpc * kUnitItems;  // wide rows: few units, keep each walk short
         int cpu = (int)(items / ((long long)gpc * p->ipt));
         if (cpu < 1) cpu = 1;
         if (cpu > 64) cpu = 64;
