@@ -373,19 +373,41 @@ extern "C" int mps_plan_info(const mps_plan *p, int64_t what[16]) {
 }
 
 // ------------------------------------------------------------------------------------- host-buffer call
+//
+// The call is cut into row slabs (equal nnz + 4*rows) so that PCIe runs in both directions at once:
+//   copy-in stream : row_ptr, rebasing + partition of every slab, then B, then col_idx/val slab by slab;
+//   work stream    : waits for B and for slab s, multiplies slab s, copies its rows of C back
+// so the download of C overlaps the upload of the later slabs of A.  Device buffers and the
+// per-slab plans live in a per-thread workspace that only grows / is rebuilt when shapes change.
+
+// out[i] = rp[row0 + i] - rp[row0], i = 0..rows
+__global__ void rebase_kernel(const int *__restrict__ rp, int row0, int rows, int *__restrict__ out) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i <= rows) out[i] = rp[row0 + i] - rp[row0];
+}
 
 namespace {
+const int kMaxHostSlabs = 8;
+const long long kHostSlabMinItems = 4ll << 20;  // below this the call is one slab
+
 struct HostWorkspace {
-    void *buf[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};  // rp, col, val, B, C
-    size_t cap[5] = {0, 0, 0, 0, 0};
-    mps_plan *plan = nullptr;
-    cudaStream_t stream = nullptr;
+    void *buf[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};  // rp, col, val, B, C, rebased rp slabs
+    size_t cap[6] = {0, 0, 0, 0, 0, 0};
+    mps_plan *plan[kMaxHostSlabs] = {};
+    cudaStream_t s_in = nullptr, s_work = nullptr;
+    cudaEvent_t ev_b = nullptr, ev_slab[kMaxHostSlabs] = {};
     int device = -1;
     void release() {
-        for (int i = 0; i < 5; ++i) { cudaFree(buf[i]); buf[i] = nullptr; cap[i] = 0; }
-        mps_plan_destroy(plan); plan = nullptr;
-        if (stream) cudaStreamDestroy(stream);
-        stream = nullptr; device = -1;
+        for (int i = 0; i < 6; ++i) { cudaFree(buf[i]); buf[i] = nullptr; cap[i] = 0; }
+        for (int i = 0; i < kMaxHostSlabs; ++i) {
+            mps_plan_destroy(plan[i]); plan[i] = nullptr;
+            if (ev_slab[i]) cudaEventDestroy(ev_slab[i]);
+            ev_slab[i] = nullptr;
+        }
+        if (ev_b) cudaEventDestroy(ev_b);
+        if (s_in) cudaStreamDestroy(s_in);
+        if (s_work) cudaStreamDestroy(s_work);
+        ev_b = nullptr; s_in = s_work = nullptr; device = -1;
     }
 };
 thread_local HostWorkspace g_ws;
@@ -408,34 +430,83 @@ extern "C" int mps_spmm_host(int32_t n_rows, int32_t n_cols, int32_t nnz, int32_
     if (dim < 1 || cost < 1 || n_cols < 0) return fail(MPS_ERR_ARG, "mps_spmm_host: dim and cost must be >= 1, n_cols >= 0");
     if (dtype != MPS_F32 && dtype != MPS_F16) return fail(MPS_ERR_ARG, "mps_spmm_host: unknown dtype %d", dtype);
     if (int rc = check_shape(n_rows, nnz)) return rc;
+    if (row_ptr[0] != 0 || row_ptr[n_rows] != nnz) return fail(MPS_ERR_ARG, "mps_spmm_host: row_ptr[0] must be 0 and row_ptr[n_rows] == nnz");
     int dev = 0;
     MPS_CUDA(cudaGetDevice(&dev));
     if (g_ws.device != dev) { g_ws.release(); g_ws.device = dev; }
-    if (!g_ws.stream) MPS_CUDA(cudaStreamCreateWithFlags(&g_ws.stream, cudaStreamNonBlocking));
-    const size_t elem = dtype == MPS_F16 ? 2 : 4;
-    const size_t n_b_rows = (size_t)n_cols;
-    const size_t bytes[5] = {4 * ((size_t)n_rows + 1), 4 * (size_t)nnz, val ? elem * (size_t)nnz : 0, elem * n_b_rows * dim,
-                             elem * (size_t)n_rows * dim};
-    for (int i = 0; i < 5; ++i)
-        if (int rc = ws_reserve(i, bytes[i])) return rc;
-    mps_plan *p = g_ws.plan;
-    if (!p || p->n_rows != n_rows || p->nnz != nnz || p->dim != dim || p->dtype != dtype || p->cost != cost) {
-        mps_plan_destroy(p);
-        g_ws.plan = nullptr;
-        if (int rc = mps_plan_create(n_rows, nnz, dim, dtype, cost, threads_per_warp, &p)) return rc;
-        g_ws.plan = p;
+    if (!g_ws.s_in) {
+        MPS_CUDA(cudaStreamCreateWithFlags(&g_ws.s_in, cudaStreamNonBlocking));
+        MPS_CUDA(cudaStreamCreateWithFlags(&g_ws.s_work, cudaStreamNonBlocking));
+        MPS_CUDA(cudaEventCreateWithFlags(&g_ws.ev_b, cudaEventDisableTiming));
+        for (int i = 0; i < kMaxHostSlabs; ++i) MPS_CUDA(cudaEventCreateWithFlags(&g_ws.ev_slab[i], cudaEventDisableTiming));
     }
-    cudaStream_t st = g_ws.stream;
-    MPS_CUDA(cudaMemcpyAsync(g_ws.buf[0], row_ptr, bytes[0], cudaMemcpyHostToDevice, st));
-    if (int rc = mps_plan_partition(p, (const int32_t *)g_ws.buf[0], st)) return rc;  // overlaps nothing yet: needs row_ptr only
-    if (bytes[1]) MPS_CUDA(cudaMemcpyAsync(g_ws.buf[1], col_idx, bytes[1], cudaMemcpyHostToDevice, st));
-    if (bytes[2]) MPS_CUDA(cudaMemcpyAsync(g_ws.buf[2], val, bytes[2], cudaMemcpyHostToDevice, st));
-    MPS_CUDA(cudaMemcpyAsync(g_ws.buf[3], B, bytes[3], cudaMemcpyHostToDevice, st));
-    if (int rc = mps_spmm(p, (const int32_t *)g_ws.buf[0], (const int32_t *)g_ws.buf[1], val ? g_ws.buf[2] : nullptr, g_ws.buf[3],
-                          g_ws.buf[4], st))
-        return rc;
-    if (bytes[4]) MPS_CUDA(cudaMemcpyAsync(C, g_ws.buf[4], bytes[4], cudaMemcpyDeviceToHost, st));
-    return mps_plan_sync_check(p, st);
+    const size_t elem = dtype == MPS_F16 ? 2 : 4;
+    const long long items = (long long)n_rows + nnz;
+    int n_slabs = (int)(items / kHostSlabMinItems);
+    if (n_slabs < 1) n_slabs = 1;
+    if (n_slabs > kMaxHostSlabs) n_slabs = kMaxHostSlabs;
+    int32_t bounds[kMaxHostSlabs + 1];
+    if (int rc = mps_slab_bounds_items(row_ptr, n_rows, n_slabs, 4, bounds)) return rc;
+
+    // device layout: slab s of col_idx/val starts at an offset that is a multiple of 8 elements, so its
+    // base stays 16-byte aligned and the tile kernel can stage it with bulk copies
+    size_t off[kMaxHostSlabs + 1];
+    off[0] = 0;
+    for (int s = 0; s < n_slabs; ++s) {
+        const size_t len = (size_t)(row_ptr[bounds[s + 1]] - row_ptr[bounds[s]]);
+        off[s + 1] = (off[s] + len + 7) & ~(size_t)7;
+    }
+    const size_t rp_slab_cap = ((size_t)n_rows + 1 + 8 * (size_t)n_slabs + 8);
+    const size_t bytes[6] = {4 * ((size_t)n_rows + 1), 4 * (off[n_slabs] + 8), val ? elem * (off[n_slabs] + 8) : 0,
+                             elem * (size_t)n_cols * dim, elem * (size_t)n_rows * dim, 4 * rp_slab_cap};
+    for (int i = 0; i < 6; ++i)
+        if (int rc = ws_reserve(i, bytes[i])) return rc;
+    int32_t *d_rp = (int32_t *)g_ws.buf[0], *d_col = (int32_t *)g_ws.buf[1], *d_rps = (int32_t *)g_ws.buf[5];
+    char *d_val = (char *)g_ws.buf[2], *d_C = (char *)g_ws.buf[4];
+
+    cudaStream_t s_in = g_ws.s_in, s_work = g_ws.s_work;
+    MPS_CUDA(cudaMemcpyAsync(d_rp, row_ptr, bytes[0], cudaMemcpyHostToDevice, s_in));
+    size_t rps_off[kMaxHostSlabs];
+    size_t at = 0;
+    for (int s = 0; s < n_slabs; ++s) {
+        const int r0 = bounds[s], rows = bounds[s + 1] - bounds[s];
+        const int slab_nnz = row_ptr[bounds[s + 1]] - row_ptr[r0];
+        mps_plan *&p = g_ws.plan[s];
+        if (!p || p->n_rows != rows || p->nnz != slab_nnz || p->dim != dim || p->dtype != dtype || p->cost != cost) {
+            mps_plan_destroy(p);
+            p = nullptr;
+            if (int rc = mps_plan_create(rows, slab_nnz, dim, dtype, cost, threads_per_warp, &p)) return rc;
+        }
+        rps_off[s] = at;
+        rebase_kernel<<<(rows + 1 + 255) / 256, 256, 0, s_in>>>(d_rp, r0, rows, d_rps + at);
+        MPS_CUDA(cudaGetLastError());
+        if (int rc = mps_plan_partition(p, d_rps + at, s_in)) return rc;
+        at = (at + (size_t)rows + 1 + 7) & ~(size_t)7;
+    }
+    for (int s = n_slabs; s < kMaxHostSlabs; ++s) { mps_plan_destroy(g_ws.plan[s]); g_ws.plan[s] = nullptr; }
+
+    MPS_CUDA(cudaMemcpyAsync(g_ws.buf[3], B, bytes[3], cudaMemcpyHostToDevice, s_in));
+    MPS_CUDA(cudaEventRecord(g_ws.ev_b, s_in));
+    MPS_CUDA(cudaStreamWaitEvent(s_work, g_ws.ev_b, 0));
+    for (int s = 0; s < n_slabs; ++s) {
+        const int r0 = bounds[s], rows = bounds[s + 1] - bounds[s];
+        const size_t k0 = (size_t)row_ptr[r0], len = (size_t)(row_ptr[bounds[s + 1]] - row_ptr[r0]);
+        if (len) {
+            MPS_CUDA(cudaMemcpyAsync(d_col + off[s], col_idx + k0, 4 * len, cudaMemcpyHostToDevice, s_in));
+            if (val) MPS_CUDA(cudaMemcpyAsync(d_val + elem * off[s], (const char *)val + elem * k0, elem * len, cudaMemcpyHostToDevice, s_in));
+        }
+        MPS_CUDA(cudaEventRecord(g_ws.ev_slab[s], s_in));
+        MPS_CUDA(cudaStreamWaitEvent(s_work, g_ws.ev_slab[s], 0));
+        char *c_slab = d_C + elem * (size_t)r0 * dim;
+        if (int rc = mps_spmm(g_ws.plan[s], d_rps + rps_off[s], d_col + off[s], val ? (const void *)(d_val + elem * off[s]) : nullptr,
+                              g_ws.buf[3], c_slab, s_work))
+            return rc;
+        if (rows) MPS_CUDA(cudaMemcpyAsync((char *)C + elem * (size_t)r0 * dim, c_slab, elem * (size_t)rows * dim, cudaMemcpyDeviceToHost, s_work));
+    }
+    MPS_CUDA(cudaStreamSynchronize(s_in));
+    for (int s = 0; s < n_slabs; ++s)
+        if (int rc = mps_plan_sync_check(g_ws.plan[s], s_work)) return rc;
+    return MPS_OK;
 }
 
 // ------------------------------------------------------------------------------------- slabs (host)

@@ -266,6 +266,32 @@ def test_host_buffer_call_equals_device_path(mps, orc, graphs, cuda):
     mps.capi.lib().mps_host_workspace_release()
 
 
+def test_host_buffer_call_pipelines_large_inputs_over_row_slabs(mps, orc, graphs, cuda):
+    """Above 4 Mi merge items the host call cuts A into row slabs (equal nnz + 4*rows) so that C flows back
+    while later slabs of A still upload; each slab must equal the device path run on that slab alone."""
+    rp, col = graphs.rmat_csr(18, 32, seed=3)
+    val = graphs.gcn_values(rp, col)
+    n, nnz = len(rp) - 1, len(col)
+    n_slabs = min(8, (n + nnz) // (4 << 20))
+    assert n_slabs >= 2
+    B = graphs.dense_uniform(n, 32, seed=4)
+    pinned = [torch.from_numpy(a).pin_memory() for a in (rp, col, val, B)]
+    out = torch.empty((n, 32), dtype=torch.float32).pin_memory()
+    for _ in range(2):   # second call reuses the workspace and the per-slab plans
+        out.fill_(float("nan"))
+        mps.spmm_host(*pinned, out=out, cost=16)
+        host = out.numpy()
+        b = mps.slab_bounds(rp, n_slabs, "items", 4)
+        for s in range(n_slabs):
+            r0, r1 = int(b[s]), int(b[s + 1])
+            srp = mps.slab_rebase(rp, r0, r1)
+            got, _ = _run(mps, cuda, srp, col[rp[r0]:rp[r1]], val[rp[r0]:rp[r1]], B, 16)
+            assert np.array_equal(_bits(got), _bits(host[r0:r1])), s
+    scale = orc.spmm_abs_f64(rp, col, val, B)
+    assert (np.abs(host.astype(np.float64) - orc.spmm_f64(rp, col, val, B)) <= 1e-6 + 1e-5 * scale).all()
+    mps.capi.lib().mps_host_workspace_release()
+
+
 # ------------------------------------------------------------------ slabs
 
 def test_row_slabs_are_bit_identical_to_their_own_model_and_close_to_the_whole(mps, orc, graphs, cuda):
