@@ -375,7 +375,8 @@ extern "C" int mps_plan_info(const mps_plan *p, int64_t what[16]) {
 // ------------------------------------------------------------------------------------- host-buffer call
 //
 // The call is cut into row slabs (equal nnz + 4*rows) so that PCIe runs in both directions at once:
-//   copy-in stream : row_ptr, rebasing + partition of every slab, then B, then col_idx/val slab by slab;
+//   B stream       : all of B, from the start;
+//   copy-in stream : row_ptr, rebasing + partition of every slab, then col_idx/val slab by slab;
 //   work stream    : waits for B and for slab s, multiplies slab s, copies its rows of C back
 // so the download of C overlaps the upload of the later slabs of A.  Device buffers and the
 // per-slab plans live in a per-thread workspace that only grows / is rebuilt when shapes change.
@@ -394,7 +395,7 @@ struct HostWorkspace {
     void *buf[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};  // rp, col, val, B, C, rebased rp slabs
     size_t cap[6] = {0, 0, 0, 0, 0, 0};
     mps_plan *plan[kMaxHostSlabs] = {};
-    cudaStream_t s_in = nullptr, s_work = nullptr;
+    cudaStream_t s_in = nullptr, s_b = nullptr, s_work = nullptr;
     cudaEvent_t ev_b = nullptr, ev_slab[kMaxHostSlabs] = {};
     int device = -1;
     void release() {
@@ -406,8 +407,9 @@ struct HostWorkspace {
         }
         if (ev_b) cudaEventDestroy(ev_b);
         if (s_in) cudaStreamDestroy(s_in);
+        if (s_b) cudaStreamDestroy(s_b);
         if (s_work) cudaStreamDestroy(s_work);
-        ev_b = nullptr; s_in = s_work = nullptr; device = -1;
+        ev_b = nullptr; s_in = s_b = s_work = nullptr; device = -1;
     }
 };
 thread_local HostWorkspace g_ws;
@@ -436,6 +438,7 @@ extern "C" int mps_spmm_host(int32_t n_rows, int32_t n_cols, int32_t nnz, int32_
     if (g_ws.device != dev) { g_ws.release(); g_ws.device = dev; }
     if (!g_ws.s_in) {
         MPS_CUDA(cudaStreamCreateWithFlags(&g_ws.s_in, cudaStreamNonBlocking));
+        MPS_CUDA(cudaStreamCreateWithFlags(&g_ws.s_b, cudaStreamNonBlocking));
         MPS_CUDA(cudaStreamCreateWithFlags(&g_ws.s_work, cudaStreamNonBlocking));
         MPS_CUDA(cudaEventCreateWithFlags(&g_ws.ev_b, cudaEventDisableTiming));
         for (int i = 0; i < kMaxHostSlabs; ++i) MPS_CUDA(cudaEventCreateWithFlags(&g_ws.ev_slab[i], cudaEventDisableTiming));
@@ -465,6 +468,9 @@ extern "C" int mps_spmm_host(int32_t n_rows, int32_t n_cols, int32_t nnz, int32_
     char *d_val = (char *)g_ws.buf[2], *d_C = (char *)g_ws.buf[4];
 
     cudaStream_t s_in = g_ws.s_in, s_work = g_ws.s_work;
+    // B starts uploading at once on its own stream; row_ptr, rebasing and the partitions run beside it
+    MPS_CUDA(cudaMemcpyAsync(g_ws.buf[3], B, bytes[3], cudaMemcpyHostToDevice, g_ws.s_b));
+    MPS_CUDA(cudaEventRecord(g_ws.ev_b, g_ws.s_b));
     MPS_CUDA(cudaMemcpyAsync(d_rp, row_ptr, bytes[0], cudaMemcpyHostToDevice, s_in));
     size_t rps_off[kMaxHostSlabs];
     size_t at = 0;
@@ -485,10 +491,16 @@ extern "C" int mps_spmm_host(int32_t n_rows, int32_t n_cols, int32_t nnz, int32_
     }
     for (int s = n_slabs; s < kMaxHostSlabs; ++s) { mps_plan_destroy(g_ws.plan[s]); g_ws.plan[s] = nullptr; }
 
-    MPS_CUDA(cudaMemcpyAsync(g_ws.buf[3], B, bytes[3], cudaMemcpyHostToDevice, s_in));
-    MPS_CUDA(cudaEventRecord(g_ws.ev_b, s_in));
     MPS_CUDA(cudaStreamWaitEvent(s_work, g_ws.ev_b, 0));
-    for (int s = 0; s < n_slabs; ++s) {
+    // slabs with many rows first: their share of C is the largest download and should overlap the most uploads
+    int order[kMaxHostSlabs];
+    for (int s = 0; s < n_slabs; ++s) order[s] = s;
+    for (int i = 1; i < n_slabs; ++i)
+        for (int j = i; j > 0 && bounds[order[j] + 1] - bounds[order[j]] > bounds[order[j - 1] + 1] - bounds[order[j - 1]]; --j) {
+            const int t = order[j]; order[j] = order[j - 1]; order[j - 1] = t;
+        }
+    for (int i = 0; i < n_slabs; ++i) {
+        const int s = order[i];
         const int r0 = bounds[s], rows = bounds[s + 1] - bounds[s];
         const size_t k0 = (size_t)row_ptr[r0], len = (size_t)(row_ptr[bounds[s + 1]] - row_ptr[r0]);
         if (len) {
@@ -504,6 +516,7 @@ extern "C" int mps_spmm_host(int32_t n_rows, int32_t n_cols, int32_t nnz, int32_
         if (rows) MPS_CUDA(cudaMemcpyAsync((char *)C + elem * (size_t)r0 * dim, c_slab, elem * (size_t)rows * dim, cudaMemcpyDeviceToHost, s_work));
     }
     MPS_CUDA(cudaStreamSynchronize(s_in));
+    MPS_CUDA(cudaStreamSynchronize(g_ws.s_b));
     for (int s = 0; s < n_slabs; ++s)
         if (int rc = mps_plan_sync_check(g_ws.plan[s], s_work)) return rc;
     return MPS_OK;

@@ -269,7 +269,7 @@ def test_host_buffer_call_equals_device_path(mps, orc, graphs, cuda):
 def test_host_buffer_call_pipelines_large_inputs_over_row_slabs(mps, orc, graphs, cuda):
     """Above 4 Mi merge items the host call cuts A into row slabs (equal nnz + 4*rows) so that C flows back
     while later slabs of A still upload; each slab must equal the device path run on that slab alone."""
-    rp, col = graphs.rmat_csr(18, 32, seed=3)
+    rp, col = graphs.rmat_csr(19, 32, seed=3)
     val = graphs.gcn_values(rp, col)
     n, nnz = len(rp) - 1, len(col)
     n_slabs = min(8, (n + nnz) // (4 << 20))
