@@ -213,6 +213,28 @@ MPS_API int mps_slab_bounds_items(const int32_t *row_ptr, int32_t n_rows, int32_
 /* Slab g of a host CSR with row_ptr rebased to 0: writes row1 - row0 + 1 entries. */
 MPS_API int mps_slab_rebase(const int32_t *row_ptr, int32_t row0, int32_t row1, int32_t *out_row_ptr);
 
+/* ------------------------------------------------------------------ multi-GPU driver ----- */
+
+/* Single-process driver over n_gpus devices of one node (no reference counterpart).  create: cuts
+ * the HOST CSR into row slabs of equal (nnz + 4*rows), uploads slab g to devices[g] (NULL = 0..n-1),
+ * plans and partitions it there, and allocates on every device a full copy of B and a full-height C.
+ * set_b: replicates a host B (n_cols x dim).  spmm: `repeat` multiplies on all devices at once, each
+ * into its own rows of its C; *ms_spmm = time per multiply, the maximum over devices (CUDA events).
+ * gather_c != 0 then makes every device's C complete with one grouped NCCL broadcast per slab over
+ * NVLink (*ms_gather); NCCL is loaded on first use, and only this option needs it.  get_c: from_gpu
+ * < 0 collects every slab from the device that computed it, otherwise copies the whole C that
+ * device `from_gpu` holds.  One host thread drives all devices; the calls wait for completion. */
+typedef struct mps_multi mps_multi;
+MPS_API int mps_multi_create(int32_t n_gpus, const int32_t *devices, int32_t n_rows, int32_t n_cols, int32_t dim,
+                     int dtype, int32_t cost, int32_t threads_per_warp, const int32_t *row_ptr,
+                     const int32_t *col_idx, const void *val, mps_multi **out);
+MPS_API void mps_multi_destroy(mps_multi *m);
+MPS_API int mps_multi_slab(const mps_multi *m, int32_t g, int32_t *device, int32_t *row0, int32_t *row1, int32_t *nnz,
+                   void **d_C);
+MPS_API int mps_multi_set_b(mps_multi *m, const void *host_B);
+MPS_API int mps_multi_spmm(mps_multi *m, int32_t repeat, int32_t gather_c, float *ms_spmm, float *ms_gather);
+MPS_API int mps_multi_get_c(mps_multi *m, void *host_C, int32_t from_gpu);
+
 #ifdef __cplusplus
 }
 #endif

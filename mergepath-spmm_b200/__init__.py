@@ -29,7 +29,7 @@ try:
 except Exception:  # pragma: no cover
     torch = None
 
-__all__ = ["Plan", "spmm", "spmm_host", "spmm_noalloc", "partition_device", "schedule_device", "chunk_count", "load_csr", "save_csr",
+__all__ = ["Plan", "MultiGpu", "spmm", "spmm_host", "spmm_noalloc", "partition_device", "schedule_device", "chunk_count", "load_csr", "save_csr",
            "save_csr_bin", "load_csr_bin", "slab_bounds", "slab_rebase", "algorithmic_bytes", "F32", "F16", "MpsError"]
 
 
@@ -191,6 +191,52 @@ def spmm_host(row_ptr, col_idx, val, B, out=None, cost: int = 8, threads_per_war
     capi.check(capi.lib().mps_spmm_host(n_rows, int(B.shape[0]), nnz, dim, F16 if is_half else F32, cost, threads_per_warp, host_ptr(row_ptr),
                                         host_ptr(col_idx), host_ptr(val), host_ptr(B), host_ptr(out)))
     return out
+
+
+class MultiGpu:
+    """Single-process driver over several GPUs of one node (mps_multi_*): A in row slabs of equal
+    nnz + 4*rows, B replicated, each device writes its own rows of C; gather_c makes C complete on
+    every device with NCCL.  Host (numpy) arrays in, host arrays out."""
+
+    def __init__(self, row_ptr, col_idx, val, n_cols: int, dim: int, dtype=F32, cost: int = 16, threads_per_warp: int = 1,
+                 n_gpus: int = 1, devices=None):
+        self._keep = [np.ascontiguousarray(row_ptr, np.int32), np.ascontiguousarray(col_idx, np.int32),
+                      None if val is None else np.ascontiguousarray(val, np.float16 if dtype == F16 else np.float32)]
+        self.n_rows, self.n_cols, self.dim, self.dtype, self.n_gpus = len(self._keep[0]) - 1, n_cols, dim, dtype, n_gpus
+        dev = None if devices is None else np.ascontiguousarray(devices, np.int32)
+        ptr = lambda a: None if a is None else a.ctypes.data_as(C.c_void_p)
+        self._h = C.c_void_p()
+        capi.check(capi.lib().mps_multi_create(n_gpus, ptr(dev), self.n_rows, n_cols, dim, dtype, cost, threads_per_warp,
+                                               ptr(self._keep[0]), ptr(self._keep[1]), ptr(self._keep[2]), C.byref(self._h)))
+
+    def close(self):
+        if getattr(self, "_h", None) is not None and self._h:
+            capi.lib().mps_multi_destroy(self._h)
+            self._h = C.c_void_p()
+
+    __del__ = close
+
+    def slab(self, g: int) -> dict:
+        dev, r0, r1, nz = C.c_int32(), C.c_int32(), C.c_int32(), C.c_int32()
+        capi.check(capi.lib().mps_multi_slab(self._h, g, C.byref(dev), C.byref(r0), C.byref(r1), C.byref(nz), None))
+        return {"device": dev.value, "row0": r0.value, "row1": r1.value, "nnz": nz.value}
+
+    def set_b(self, B):
+        B = np.ascontiguousarray(B, np.float16 if self.dtype == F16 else np.float32)
+        assert B.shape == (self.n_cols, self.dim)
+        capi.check(capi.lib().mps_multi_set_b(self._h, B.ctypes.data_as(C.c_void_p)))
+        return self
+
+    def spmm(self, repeat: int = 1, gather_c: bool = False) -> tuple[float, float]:
+        """(ms per multiply, ms of the gather), each the maximum over devices."""
+        a, b = C.c_float(), C.c_float()
+        capi.check(capi.lib().mps_multi_spmm(self._h, repeat, int(gather_c), C.byref(a), C.byref(b)))
+        return a.value, b.value
+
+    def get_c(self, from_gpu: int = -1):
+        out = np.empty((self.n_rows, self.dim), np.float16 if self.dtype == F16 else np.float32)
+        capi.check(capi.lib().mps_multi_get_c(self._h, out.ctypes.data_as(C.c_void_p), from_gpu))
+        return out
 
 
 def load_csr(path: str, threads: int = 0):

@@ -35,13 +35,13 @@ def _sources(names):
 
 
 def build_library(force: bool = False, verbose: bool = False) -> str:
-    srcs = _sources(["mps_api.cu", "mps_noalloc.cu", "csr_io.cpp"])
+    srcs = _sources(["mps_api.cu", "mps_noalloc.cu", "mps_multi.cu", "csr_io.cpp"])
     deps = srcs + _sources(["mps_kernels.cuh", "mps_internal.h", "mps_plan.h"]) + [os.path.join(ROOT, "include", "mps.h")]
     if not force and _newer(LIB, deps):
         return LIB
     os.makedirs(LIBDIR, exist_ok=True)
     cmd = [_nvcc()] + ARCH + COMMON + ["-shared", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
-                                      "-Xcompiler", "-pthread", "-o", LIB] + srcs
+                                      "-Xcompiler", "-pthread", "-o", LIB] + srcs + ["-ldl"]
     if verbose:
         cmd.insert(1, "-Xptxas=-v")
     subprocess.run(cmd, check=True)

@@ -18,7 +18,8 @@ SYMBOLS = [
     "mps_last_error", "mps_version", "mps_csr_load", "mps_csr_free", "mps_csr_save", "mps_csr_save_bin",
     "mps_csr_load_bin", "mps_chunk_count", "mps_partition_device", "mps_schedule_device", "mps_plan_create",
     "mps_plan_destroy", "mps_plan_tune", "mps_plan_partition", "mps_spmm", "mps_plan_sync_check", "mps_plan_info", "mps_plan_profile", "mps_plan_profile_read",
-    "mps_algorithmic_bytes", "mps_spmm_host", "mps_host_workspace_release", "mps_spmm_noalloc", "mps_slab_bounds", "mps_slab_bounds_items", "mps_slab_rebase",
+    "mps_algorithmic_bytes", "mps_spmm_host", "mps_host_workspace_release", "mps_spmm_noalloc", "mps_slab_bounds", "mps_slab_bounds_items", "mps_slab_rebase", "mps_multi_create", "mps_multi_destroy", "mps_multi_slab",
+    "mps_multi_set_b", "mps_multi_spmm", "mps_multi_get_c",
 ]
 
 
@@ -75,6 +76,13 @@ def lib():
     L.mps_slab_bounds.argtypes = [vp, i32, i32, vp]
     L.mps_slab_bounds_items.argtypes = [vp, i32, i32, i32, vp]
     L.mps_slab_rebase.argtypes = [vp, i32, i32, vp]
+    L.mps_multi_create.argtypes = [i32, vp, i32, i32, i32, C.c_int, i32, i32, vp, vp, vp, C.POINTER(vp)]
+    L.mps_multi_destroy.argtypes = [vp]
+    L.mps_multi_destroy.restype = None
+    L.mps_multi_slab.argtypes = [vp, i32, C.POINTER(i32), C.POINTER(i32), C.POINTER(i32), C.POINTER(i32), C.POINTER(vp)]
+    L.mps_multi_set_b.argtypes = [vp, vp]
+    L.mps_multi_spmm.argtypes = [vp, i32, i32, C.POINTER(C.c_float), C.POINTER(C.c_float)]
+    L.mps_multi_get_c.argtypes = [vp, vp, i32]
     _lib = L
     return L
 

@@ -9,7 +9,8 @@
 //
 // Options (all optional, after the positionals):
 //   --dtype=f32|f16   --values=unit|gcn   --check   --device=K
-//   --gpus=G          row slabs of equal (nnz + 4*rows) over G devices of this node, one host thread per device
+//   --gpus=G          row slabs of equal (nnz + 4*rows) over G devices of this node (mps_multi_*)
+//   --gather-c        after the timed multiplies, replicate C on every device with NCCL and time it
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
@@ -20,7 +21,6 @@
 #include <cstring>
 #include <iostream>
 #include <string>
-#include <thread>
 #include <vector>
 
 #include "mps.h"
@@ -29,7 +29,7 @@ namespace {
 
 struct Options {
     std::string dtype = "f32", values = "unit";
-    bool check = false;
+    bool check = false, gather_c = false;
     int device = 0, gpus = 1;
 };
 
@@ -44,17 +44,10 @@ bool parse_option(const char *arg, Options &o) {
     if (const char *v = val("--device=")) { o.device = atoi(v); return true; }
     if (const char *v = val("--gpus=")) { o.gpus = atoi(v); return o.gpus >= 1; }
     if (a == "--check") { o.check = true; return true; }
+    if (a == "--gather-c") { o.gather_c = true; return true; }
     return false;
 }
 
-#define CUDA_OK(call)                                                                      \
-    do {                                                                                   \
-        cudaError_t e_ = (call);                                                           \
-        if (e_ != cudaSuccess) {                                                           \
-            fprintf(stderr, "CUDA error: %s (%s)\n", cudaGetErrorString(e_), #call);       \
-            return 1;                                                                      \
-        }                                                                                  \
-    } while (0)
 #define MPS_OK_OR_DIE(call)                                              \
     do {                                                                 \
         if ((call) != MPS_OK) {                                          \
@@ -63,82 +56,7 @@ bool parse_option(const char *arg, Options &o) {
         }                                                                \
     } while (0)
 
-struct SlabResult {
-    double ms_per_spmm = 0, partition_ms = 0;
-    int rc = 0;
-    long long bad = 0;
-};
-
-// One device: upload the slab [row0,row1) and all of B, partition, warm up, time `repeat` launches.
-int run_slab(const mps_csr &g, const std::vector<float> &val, int row0, int row1, int dim, int cost, int tpw, int repeat,
-             const Options &o, int device, SlabResult *out) {
-    CUDA_OK(cudaSetDevice(device));
-    const bool half = o.dtype == "f16";
-    const int n = row1 - row0;
-    const int k0 = g.row_ptr[row0], nnz = g.row_ptr[row1] - k0;
-    const size_t es = half ? 2 : 4;
-    std::vector<int32_t> rp((size_t)n + 1);
-    MPS_OK_OR_DIE(mps_slab_rebase(g.row_ptr, row0, row1, rp.data()));
-
-    int32_t *d_rp = nullptr, *d_col = nullptr;
-    void *d_val = nullptr, *d_B = nullptr, *d_C = nullptr;
-    CUDA_OK(cudaMalloc(&d_rp, 4 * ((size_t)n + 1)));
-    CUDA_OK(cudaMalloc(&d_col, 4 * (size_t)(nnz ? nnz : 1)));
-    CUDA_OK(cudaMalloc(&d_B, es * (size_t)g.n_rows * dim + 16));
-    CUDA_OK(cudaMalloc(&d_C, es * (size_t)n * dim + 16));
-    CUDA_OK(cudaMemcpy(d_rp, rp.data(), 4 * ((size_t)n + 1), cudaMemcpyHostToDevice));
-    CUDA_OK(cudaMemcpy(d_col, g.col_idx + k0, 4 * (size_t)nnz, cudaMemcpyHostToDevice));
-    if (!val.empty()) {
-        CUDA_OK(cudaMalloc(&d_val, es * (size_t)(nnz ? nnz : 1)));
-        if (half) {
-            std::vector<__half> hv((size_t)nnz);
-            for (int k = 0; k < nnz; ++k) hv[(size_t)k] = __float2half(val[(size_t)k0 + k]);
-            CUDA_OK(cudaMemcpy(d_val, hv.data(), 2 * (size_t)nnz, cudaMemcpyHostToDevice));
-        } else {
-            CUDA_OK(cudaMemcpy(d_val, val.data() + k0, 4 * (size_t)nnz, cudaMemcpyHostToDevice));
-        }
-    }
-    {   // B = 1 everywhere, as the reference fills it
-        const size_t cells = (size_t)g.n_rows * dim;
-        if (half) { std::vector<__half> b(cells, __float2half(1.0f)); CUDA_OK(cudaMemcpy(d_B, b.data(), 2 * cells, cudaMemcpyHostToDevice)); }
-        else { std::vector<float> b(cells, 1.0f); CUDA_OK(cudaMemcpy(d_B, b.data(), 4 * cells, cudaMemcpyHostToDevice)); }
-    }
-    mps_plan *plan = nullptr;
-    MPS_OK_OR_DIE(mps_plan_create(n, nnz, dim, half ? MPS_F16 : MPS_F32, cost, tpw, &plan));
-    auto t0 = std::chrono::steady_clock::now();
-    MPS_OK_OR_DIE(mps_plan_partition(plan, d_rp, nullptr));
-    out->partition_ms = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
-    for (int i = 0; i < 3; ++i) MPS_OK_OR_DIE(mps_spmm(plan, d_rp, d_col, d_val, d_B, d_C, nullptr));
-    cudaEvent_t e0, e1;
-    CUDA_OK(cudaEventCreate(&e0));
-    CUDA_OK(cudaEventCreate(&e1));
-    CUDA_OK(cudaDeviceSynchronize());
-    CUDA_OK(cudaEventRecord(e0));
-    for (int i = 0; i < repeat; ++i) MPS_OK_OR_DIE(mps_spmm(plan, d_rp, d_col, d_val, d_B, d_C, nullptr));
-    CUDA_OK(cudaEventRecord(e1));
-    MPS_OK_OR_DIE(mps_plan_sync_check(plan, nullptr));
-    float ms = 0;
-    CUDA_OK(cudaEventElapsedTime(&ms, e0, e1));
-    out->ms_per_spmm = repeat > 0 ? ms / repeat : 0.0;
-
-    if (o.check) {  // with B == 1 every element of row i is the sum of the row's values
-        std::vector<unsigned char> hc(es * (size_t)n * dim);
-        CUDA_OK(cudaMemcpy(hc.data(), d_C, hc.size(), cudaMemcpyDeviceToHost));
-        for (int i = 0; i < n; ++i) {
-            double want = 0;
-            for (int k = rp[(size_t)i]; k < rp[(size_t)i + 1]; ++k) want += val.empty() ? 1.0 : (half ? (double)__half2float(__float2half(val[(size_t)k0 + k])) : (double)val[(size_t)k0 + k]);
-            const double tol = (half ? 1e-2 : 1e-5) * std::fabs(want) + 1e-6;
-            for (int j = 0; j < dim; ++j) {
-                const double got = half ? (double)__half2float(((const __half *)hc.data())[(size_t)i * dim + j]) : (double)((const float *)hc.data())[(size_t)i * dim + j];
-                if (std::fabs(got - want) > tol) ++out->bad;
-            }
-        }
-    }
-    mps_plan_destroy(plan);
-    cudaEventDestroy(e0); cudaEventDestroy(e1);
-    cudaFree(d_rp); cudaFree(d_col); cudaFree(d_val); cudaFree(d_B); cudaFree(d_C);
-    return 0;
-}
+float half_to_float(uint16_t h) { return __half2float(*reinterpret_cast<const __half *>(&h)); }
 
 }  // namespace
 
@@ -158,8 +76,11 @@ int main(int argc, char *argv[]) {
     if (dim < 1 || cost < 1) { fprintf(stderr, "error: dimension and cost must be >= 1\n"); return 2; }
     if (dim <= 32 && tpw > 32 / dim)
         fprintf(stderr, "note: threads_per_warp %d exceeds 32/dim = %d; using %d (the reference exits here)\n", tpw, 32 / dim, 32 / dim);
+    const bool half = o.dtype == "f16";
 
+    // values: none in the file; --values=gcn derives D^-1/2 (A) D^-1/2 from the row lengths
     std::vector<float> val;
+    std::vector<__half> val_h;
     if (o.values == "gcn") {
         val.resize((size_t)g.nnz);
         for (int i = 0; i < g.n_rows; ++i) {
@@ -170,36 +91,64 @@ int main(int argc, char *argv[]) {
                 val[(size_t)k] = (float)(1.0 / std::sqrt(di * dj));
             }
         }
+        if (half) {
+            val_h.resize(val.size());
+            for (size_t k = 0; k < val.size(); ++k) val_h[k] = __float2half(val[k]);
+        }
     }
+    const void *val_ptr = val.empty() ? nullptr : (half ? (const void *)val_h.data() : (const void *)val.data());
+
     int visible = 0;
     if (cudaGetDeviceCount(&visible) != cudaSuccess || visible < 1) { fprintf(stderr, "error: no CUDA device\n"); return 1; }
     if (o.gpus > visible) { fprintf(stderr, "error: --gpus=%d but only %d devices are visible\n", o.gpus, visible); return 1; }
+    std::vector<int32_t> devices((size_t)o.gpus);
+    for (int d = 0; d < o.gpus; ++d) devices[(size_t)d] = o.gpus == 1 ? o.device : d;
 
-    std::vector<int32_t> bounds((size_t)o.gpus + 1);
-    if (mps_slab_bounds_items(g.row_ptr, g.n_rows, o.gpus, /*row_weight=*/4, bounds.data()) != MPS_OK) { fprintf(stderr, "error: %s\n", mps_last_error()); return 1; }
-    std::vector<SlabResult> res((size_t)o.gpus);
-    std::vector<std::thread> th;
-    for (int s = 0; s < o.gpus; ++s)
-        th.emplace_back([&, s] {
-            res[(size_t)s].rc = run_slab(g, val, bounds[(size_t)s], bounds[(size_t)s + 1], dim, cost, tpw, repeat, o,
-                                         o.gpus == 1 ? o.device : s, &res[(size_t)s]);
-        });
-    for (auto &t : th) t.join();
-    double ms = 0, part = 0;
+    // B = 1 everywhere, as the reference fills it (src/MergePathSpMM.cu:180-182)
+    const size_t cells = (size_t)g.n_rows * dim, es = half ? 2 : 4;
+    std::vector<unsigned char> hB(cells * es), hC(cells * es);
+    if (half) { const __half one = __float2half(1.0f); for (size_t i = 0; i < cells; ++i) ((__half *)hB.data())[i] = one; }
+    else for (size_t i = 0; i < cells; ++i) ((float *)hB.data())[i] = 1.0f;
+
+    mps_multi *m = nullptr;
+    auto t0 = std::chrono::steady_clock::now();
+    MPS_OK_OR_DIE(mps_multi_create(o.gpus, devices.data(), g.n_rows, g.n_rows, dim, half ? MPS_F16 : MPS_F32, cost, tpw, g.row_ptr, g.col_idx,
+                                   val_ptr, &m));
+    const double setup_ms = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
+    MPS_OK_OR_DIE(mps_multi_set_b(m, hB.data()));
+    float ms = 0, ms_gather = 0;
+    MPS_OK_OR_DIE(mps_multi_spmm(m, 3, 0, &ms, nullptr));  // warm-up
+    if (repeat > 0) MPS_OK_OR_DIE(mps_multi_spmm(m, repeat, o.gather_c ? 1 : 0, &ms, &ms_gather));
+
     long long bad = 0;
-    for (const SlabResult &r : res) {
-        if (r.rc) return r.rc;
-        if (r.ms_per_spmm > ms) ms = r.ms_per_spmm;
-        if (r.partition_ms > part) part = r.partition_ms;
-        bad += r.bad;
+    if (o.check) {  // with B == 1 every element of row i is the sum of the row's values
+        MPS_OK_OR_DIE(mps_multi_get_c(m, hC.data(), o.gather_c ? o.gpus - 1 : -1));
+        for (int i = 0; i < g.n_rows; ++i) {
+            double want = 0;
+            for (int k = g.row_ptr[i]; k < g.row_ptr[i + 1]; ++k)
+                want += val.empty() ? 1.0 : (half ? (double)__half2float(val_h[(size_t)k]) : (double)val[(size_t)k]);
+            const double tol = (half ? 1e-2 : 1e-5) * std::fabs(want) + 1e-6;
+            for (int j = 0; j < dim; ++j) {
+                const size_t at = (size_t)i * dim + j;
+                const double got = half ? (double)half_to_float(((const uint16_t *)hC.data())[at]) : (double)((const float *)hC.data())[at];
+                if (std::fabs(got - want) > tol) ++bad;
+            }
+        }
     }
     const double flops = 2.0 * g.nnz * dim;
-    const double bytes = (double)mps_algorithmic_bytes(g.n_rows, g.nnz, dim, o.dtype == "f16" ? MPS_F16 : MPS_F32, o.values == "gcn");
+    const double bytes = (double)mps_algorithmic_bytes(g.n_rows, g.nnz, dim, half ? MPS_F16 : MPS_F32, o.values == "gcn");
     printf("gpus: %d  dtype: %s  values: %s  dim: %d  cost: %d  repeat: %d\n", o.gpus, o.dtype.c_str(), o.values.c_str(), dim, cost, repeat);
-    printf("partition: %.3f ms (once)\n", part);
+    for (int d = 0; d < o.gpus; ++d) {
+        int32_t dev, r0, r1, nz;
+        mps_multi_slab(m, d, &dev, &r0, &r1, &nz, nullptr);
+        printf("  device %d: rows [%d, %d)  nnz %d\n", dev, r0, r1, nz);
+    }
+    printf("upload + partition: %.3f ms (once)\n", setup_ms);
     if (repeat > 0)
         printf("time per SpMM: %.4f ms  %.1f GFLOP/s  %.1f GB/s algorithmic (max over devices)\n", ms, flops / ms / 1e6, bytes / ms / 1e6);
+    if (o.gather_c) printf("all-gather of C over NCCL: %.4f ms\n", ms_gather);
     if (o.check) printf("check: %lld elements outside tolerance\n", bad);
+    mps_multi_destroy(m);
     mps_csr_free(&g);
     return bad ? 3 : 0;
 }

@@ -1,0 +1,40 @@
+"""bench.py prints one JSON line with the keys its contract names (small scales so that it is quick)."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _run(*args):
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), *args], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    lines = [l for l in r.stdout.splitlines() if l.startswith("{")]
+    assert len(lines) == 1, r.stdout
+    return json.loads(lines[0])
+
+
+def test_host_arm_line():
+    out = _run("--impl", "reference", "--steps", "1", "--warmup", "1", "--scale", "12")
+    assert out["impl"] == "reference" and out["unit"] == "GFLOP/s" and out["higher_is_better"] is True
+    assert out["cpu_baseline"]["kind"] == "port" and out["cpu_baseline"]["cores"] >= 1
+    assert out["cpu_baseline"]["value"] == out["value"] == out["e2e"]["value"]
+    assert out["e2e"]["h2d_bytes_per_step"] == 0 and out["e2e"]["d2h_bytes_per_step"] == 0
+    assert "sample" in out["cpu_baseline"]
+
+
+@pytest.mark.gpu
+def test_default_arm_line_on_a_small_graph(cuda):
+    out = _run("--steps", "5", "--warmup", "3", "--scale", "15", "--e2e-steps", "1")
+    for key in ("metric", "value", "unit", "n_gpus", "steps", "warmup", "ms_per_step", "higher_is_better", "scaling", "vs_baseline",
+                "dtype", "data", "config", "roofline", "e2e", "gpu_launches", "clocks", "cpu_baseline"):
+        assert key in out, key
+    assert out["n_gpus"] == 1 and out["steps"] == 5 and out["vs_baseline"] is None and out["data"] == "synthetic"
+    assert out["roofline"]["bound"] == "hbm" and out["roofline"]["achieved"] > 0 and out["roofline"]["peak"] > 0
+    assert abs(out["roofline"]["frac"] - out["roofline"]["achieved"] / out["roofline"]["peak"]) < 1e-3
+    assert out["e2e"]["h2d_bytes_per_step"] > 0 and out["e2e"]["d2h_bytes_per_step"] > 0 and out["e2e"]["value"] < out["value"]
+    assert out["gpu_launches"] >= 5 and "workload" in out["config"]
+    assert out["cpu_baseline"]["kind"] == "port" and out["cpu_baseline"]["value"] > 0
