@@ -174,9 +174,9 @@ extern "C" int mps_multi_set_b(mps_multi *m, const void *host_B) {
     return MPS_OK;
 }
 
-static int multi_gather(mps_multi *m) {
-    if (m->n_gpus == 1) return MPS_OK;
-    if (m->comm.empty()) {
+// Communicators are created once, outside any timed region.
+static int multi_init_comm(mps_multi *m) {
+    if (m->n_gpus > 1 && m->comm.empty()) {
         if (!g_nccl.load()) return fail(MPS_ERR_UNSUPPORTED, "mps_multi_spmm: a replicated C needs NCCL (libnccl.so.2 not found: %s)", dlerror());
         std::vector<int> devs;
         for (const Slab &s : m->slab) devs.push_back(s.device);
@@ -184,6 +184,11 @@ static int multi_gather(mps_multi *m) {
         ncclResult_t r = g_nccl.CommInitAll(m->comm.data(), m->n_gpus, devs.data());
         if (r != ncclSuccess) { m->comm.clear(); return fail(MPS_ERR_CUDA, "ncclCommInitAll: %s", g_nccl.GetErrorString(r)); }
     }
+    return MPS_OK;
+}
+
+static int multi_gather(mps_multi *m) {
+    if (m->n_gpus == 1) return MPS_OK;
     const size_t es = elem_bytes(m->dtype);
     const ncclDataType_t dt = m->dtype == MPS_F16 ? ncclFloat16 : ncclFloat32;
     ncclResult_t r = g_nccl.GroupStart();
@@ -230,6 +235,7 @@ extern "C" int mps_multi_spmm(mps_multi *m, int32_t repeat, int32_t gather_c, fl
         if (rc == MPS_OK && cudaEventElapsedTime(&ms, s.ev0, s.ev1) == cudaSuccess && ms > worst) worst = ms;
     }
     if (ms_spmm) *ms_spmm = worst / repeat;
+    if (rc == MPS_OK && gather_c) rc = multi_init_comm(m);
     if (rc == MPS_OK && gather_c) {
         for (Slab &s : m->slab) { cudaSetDevice(s.device); cudaEventRecord(s.ev0, s.stream); }
         rc = multi_gather(m);
