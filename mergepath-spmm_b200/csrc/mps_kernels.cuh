@@ -156,12 +156,28 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity)
 // ---------------------------------------------------------------------------------------------
 // per-lane column vectors
 // ---------------------------------------------------------------------------------------------
+// Lane<T, VEC>: one lane's VEC adjacent columns.  `scalar` is how the non-zero's value is held while a
+// batch is in flight: float for fp32 storage, the fp16 bit pattern for fp16 storage (the sm_100
+// mixed-precision fma takes fp16 factors and an fp32 addend, which equals converting both factors to
+// fp32 first - an fp16 x fp16 product is exact in fp32 - without spending instructions on conversion).
 template <typename T, int VEC>
 struct Lane;
+
+__device__ __forceinline__ void fma_f32_f16x2(float &acc0, float &acc1, unsigned short a, uint32_t b_pair) {
+    asm("{\n\t.reg .b16 lo, hi;\n\t"
+        "mov.b32 {lo, hi}, %2;\n\t"
+        "fma.rn.f32.f16 %0, %3, lo, %0;\n\t"
+        "fma.rn.f32.f16 %1, %3, hi, %1;\n\t}"
+        : "+f"(acc0), "+f"(acc1)
+        : "r"(b_pair), "h"(a));
+}
 
 template <>
 struct Lane<float, 4> {
     typedef float4 raw;
+    typedef float scalar;
+    static __device__ __forceinline__ scalar value(float v) { return v; }
+    static __device__ __forceinline__ scalar one() { return 1.0f; }
     static __device__ __forceinline__ raw load(const float *p) { return __ldg(reinterpret_cast<const float4 *>(p)); }
     static __device__ __forceinline__ void fma(float (&acc)[4], float a, const raw &b) {
         acc[0] = fmaf(a, b.x, acc[0]); acc[1] = fmaf(a, b.y, acc[1]);
@@ -174,6 +190,9 @@ struct Lane<float, 4> {
 template <>
 struct Lane<float, 1> {
     typedef float raw;
+    typedef float scalar;
+    static __device__ __forceinline__ scalar value(float v) { return v; }
+    static __device__ __forceinline__ scalar one() { return 1.0f; }
     static __device__ __forceinline__ raw load(const float *p) { return __ldg(p); }
     static __device__ __forceinline__ void fma(float (&acc)[1], float a, const raw &b) { acc[0] = fmaf(a, b, acc[0]); }
     static __device__ __forceinline__ void store(float *p, const float (&v)[1]) { __stcs(p, v[0]); }
@@ -181,15 +200,15 @@ struct Lane<float, 1> {
 template <>
 struct Lane<__half, 8> {
     typedef uint4 raw;
+    typedef unsigned short scalar;
+    static __device__ __forceinline__ scalar value(__half v) { return __half_as_ushort(v); }
+    static __device__ __forceinline__ scalar one() { return (unsigned short)0x3C00; }
     static __device__ __forceinline__ raw load(const __half *p) { return __ldg(reinterpret_cast<const uint4 *>(p)); }
-    static __device__ __forceinline__ void fma(float (&acc)[8], float a, const raw &b) {
-        const __half2 *h = reinterpret_cast<const __half2 *>(&b);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const float2 f = __half22float2(h[i]);
-            acc[2 * i] = fmaf(a, f.x, acc[2 * i]);
-            acc[2 * i + 1] = fmaf(a, f.y, acc[2 * i + 1]);
-        }
+    static __device__ __forceinline__ void fma(float (&acc)[8], scalar a, const raw &b) {
+        fma_f32_f16x2(acc[0], acc[1], a, b.x);
+        fma_f32_f16x2(acc[2], acc[3], a, b.y);
+        fma_f32_f16x2(acc[4], acc[5], a, b.z);
+        fma_f32_f16x2(acc[6], acc[7], a, b.w);
     }
     static __device__ __forceinline__ void store(__half *p, const float (&v)[8]) {
         uint4 o;
@@ -202,6 +221,9 @@ struct Lane<__half, 8> {
 template <>
 struct Lane<__half, 1> {
     typedef __half raw;
+    typedef float scalar;
+    static __device__ __forceinline__ scalar value(__half v) { return __half2float(v); }
+    static __device__ __forceinline__ scalar one() { return 1.0f; }
     static __device__ __forceinline__ raw load(const __half *p) { return __ldg(p); }
     static __device__ __forceinline__ void fma(float (&acc)[1], float a, const raw &b) { acc[0] = fmaf(a, __half2float(b), acc[0]); }
     static __device__ __forceinline__ void store(__half *p, const float (&v)[1]) { *p = __float2half_rn(v[0]); }
@@ -408,11 +430,11 @@ __global__ void __launch_bounds__(kBlock, MPS_MIN_BLOCKS) spmm_tile_kernel(const
         // full batches: U gathers in flight, no bound checks
         for (; k + U <= y1; k += U) {
             typename Lane<T, VEC>::raw b[U];
-            float a[U];
+            typename Lane<T, VEC>::scalar a[U];
 #pragma unroll
             for (int u = 0; u < U; ++u) {
                 const unsigned ci = (unsigned)w_col[k + u];
-                a[u] = has_val ? to_float(w_val[k + u]) : 1.0f;
+                a[u] = has_val ? Lane<T, VEC>::value(w_val[k + u]) : Lane<T, VEC>::one();
                 if (active) b[u] = Lane<T, VEC>::load(Bl + (size_t)ci * dim);
             }
             while (next_mark <= k) end_row();
@@ -432,12 +454,12 @@ __global__ void __launch_bounds__(kBlock, MPS_MIN_BLOCKS) spmm_tile_kernel(const
         // remainder: fewer than U non-zeros
         if (k < y1) {
             typename Lane<T, VEC>::raw b[U];
-            float a[U];
+            typename Lane<T, VEC>::scalar a[U];
 #pragma unroll
             for (int u = 0; u < U - 1; ++u) {
                 if (k + u < y1) {
                     const unsigned ci = (unsigned)w_col[k + u];
-                    a[u] = has_val ? to_float(w_val[k + u]) : 1.0f;
+                    a[u] = has_val ? Lane<T, VEC>::value(w_val[k + u]) : Lane<T, VEC>::one();
                     if (active) b[u] = Lane<T, VEC>::load(Bl + (size_t)ci * dim);
                 }
             }
