@@ -51,6 +51,7 @@ def parse_args():
     ap.add_argument("--chunks-per-unit", type=int, default=0)
     ap.add_argument("--unroll", type=int, default=0)
     ap.add_argument("--no-bulk", action="store_true")
+    ap.add_argument("--block", type=int, default=0, help="threads per tile block (0 = automatic)")
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--skip-baselines", action="store_true", help="leave out cpu_baseline and reference_gpu (tuning runs)")
     ap.add_argument("--balance", default="items", choices=["nnz", "items"], help="row slabs of equal non-zeros or equal rows+non-zeros")
@@ -213,8 +214,8 @@ def run_ours(args):
     n_slab, nnz_slab = w["r1"] - w["r0"], w["col"].numel()
     dt = mps.F16 if w["half"] else mps.F32
     plan = mps.Plan(n_slab, nnz_slab, args.dim, dt, cost, args.tpw, device=dev)
-    if args.chunks_per_unit or args.unroll or args.no_bulk:
-        plan.tune(args.chunks_per_unit, args.unroll, not args.no_bulk)
+    if args.chunks_per_unit or args.unroll or args.no_bulk or args.block:
+        plan.tune(args.chunks_per_unit, args.unroll, not args.no_bulk, args.block)
     t0 = time.perf_counter()
     plan.partition(w["rp"])
     torch.cuda.synchronize()
@@ -299,7 +300,7 @@ def run_ours(args):
         "config": {"workload": workload_name(args, world), "nodes": w["n"], "nnz": w["nnz"], "dim": args.dim, "cost": cost,
                    "threads_per_warp": info["threads_per_warp"], "values": "gcn", "parallelism": f"row-slabs x{world} ({args.balance}-balanced, row weight {args.row_weight}), B replicated", "per_rank_ms": per_rank_ms, "per_rank_rows": [int(v) for v in all_ranks(float(n_slab), world)], "per_rank_nnz": [int(v) for v in all_ranks(float(nnz_slab), world)],
                    "l2": "inputs larger than L2 (B and A each > 126 MB)", "chunks_per_tile": info["chunks_per_tile"], "chunks_per_unit": info["chunks_per_unit"],
-                   "items_per_chunk": info["items_per_chunk"], "unroll": info["unroll"], "tiles": info["n_tiles"],
+                   "items_per_chunk": info["items_per_chunk"], "unroll": info["unroll"], "block_threads": info["block_threads"], "tiles": info["n_tiles"],
                    "long_rows": info["long_rows"]},
         "roofline": roofline, "e2e": e2e, "gpu_launches": args.steps * info["kernels_per_call"],
         "clocks": clocks.summary(), "partition_ms": round(partition_ms, 3),

@@ -116,9 +116,11 @@ MPS_API void mps_plan_destroy(mps_plan *plan);
 
 /* Optional tuning before mps_plan_partition: chunks per unit (0 = automatic; a unit is the run of
  * consecutive chunks one lane group walks with its accumulator kept in registers, a tile holds
- * 256/lanes_per_chunk units), gather unroll (4 or 8, 0 = automatic), staging through bulk async
- * copies (1, default) or plain loads (0). */
-MPS_API int mps_plan_tune(mps_plan *plan, int32_t chunks_per_unit, int32_t unroll, int32_t bulk_staging);
+ * block_threads/lanes_per_chunk units), gather unroll (4 or 8, 0 = automatic), staging through
+ * bulk async copies (1, default) or plain loads (0), threads per tile block (64, 128, 256; 0 =
+ * automatic: 64). */
+MPS_API int mps_plan_tune(mps_plan *plan, int32_t chunks_per_unit, int32_t unroll, int32_t bulk_staging,
+                  int32_t block_threads);
 
 /* Replaces the call of generate_mp_sched and the eleven uploads that follow it
  * (src/MergePathSpMM.cu:192-220): searches the tile boundaries on the device and lists the rows
@@ -143,7 +145,7 @@ MPS_API int mps_plan_sync_check(mps_plan *plan, void *stream);
  * what[3]=n_tiles what[4]=lanes_per_chunk what[5]=elements_per_lane what[6]=unroll
  * what[7]=shared_bytes_per_block what[8]=long_rows what[9]=effective threads_per_warp
  * what[10]=kernels per mps_spmm call what[11]=long_chain threshold what[12]=chunks_per_unit
- * what[13]=units_per_tile; what[14..15] reserved (0). */
+ * what[13]=units_per_tile what[14]=threads per tile block; what[15] reserved (0). */
 MPS_API int mps_plan_info(const mps_plan *plan, int64_t what[16]);
 
 /* Per-kernel timing (no reference counterpart; the reference is timed from outside with nvprof,

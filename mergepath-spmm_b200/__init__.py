@@ -87,7 +87,7 @@ class Plan:
     """Shape-bound plan: create -> (tune) -> partition(row_ptr) -> spmm(...) any number of times."""
 
     INFO = ("n_chunks", "items_per_chunk", "chunks_per_tile", "n_tiles", "lanes_per_chunk", "elements_per_lane", "unroll",
-            "shared_bytes", "long_rows", "threads_per_warp", "kernels_per_call", "long_chain", "chunks_per_unit", "units_per_tile")
+            "shared_bytes", "long_rows", "threads_per_warp", "kernels_per_call", "long_chain", "chunks_per_unit", "units_per_tile", "block_threads")
 
     def __init__(self, n_rows: int, nnz: int, dim: int, dtype=F32, cost: int = 8, threads_per_warp: int = 1, device=None):
         self._h = C.c_void_p()
@@ -103,9 +103,9 @@ class Plan:
 
     __del__ = close
 
-    def tune(self, chunks_per_unit: int = 0, unroll: int = 0, bulk_staging: bool = True):
+    def tune(self, chunks_per_unit: int = 0, unroll: int = 0, bulk_staging: bool = True, block_threads: int = 0):
         with torch.cuda.device(self.device):
-            capi.check(capi.lib().mps_plan_tune(self._h, chunks_per_unit, unroll, int(bulk_staging)))
+            capi.check(capi.lib().mps_plan_tune(self._h, chunks_per_unit, unroll, int(bulk_staging), block_threads))
         return self
 
     def partition(self, row_ptr, stream=None):

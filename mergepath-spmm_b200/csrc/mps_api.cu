@@ -101,15 +101,18 @@ static int pow2_at_least(int v) {
     return p;
 }
 
-static const int kSmemTarget = 64 * 1024;   // three tile blocks per SM, which the registers allow anyway
+static const int kSmemTargetPer256 = 64 * 1024;   // three tile blocks per SM, which the registers allow anyway
 static const int kTilesPerSm = 6;            // smaller tiles rather than idle SMs on small problems
 static const int kUnitItems = 272;           // merge items one lane group walks per tile, at most
-static const int kTileItems = 4352;          // merge items per tile the automatic layout aims for
+static const int kTileItemsPerThread = 17;          // merge items per tile the automatic layout aims for
 static const int kSmemLimit = 200 * 1024;
 
 static int plan_layout(mps_plan *p) {
     const int elem = p->dtype == MPS_F16 ? 2 : 4;
-    const int gpc = kBlock / p->gl;  // units per tile
+    if (!p->user_block) p->block = 64;  // small blocks wait least at the three block barriers of a tile; 12 of them fit an SM
+    if (p->block < p->gl) p->block = p->gl;
+    const int gpc = p->block / p->gl;  // units per tile
+    const int kSmemTarget = kSmemTargetPer256 * p->block / 256, kTileItems = kTileItemsPerThread * p->block;
     if (!p->user_unroll) p->unroll = 8;
     if (p->vec == 1) p->unroll = 4;
     if (!p->user_cpu) {
@@ -211,10 +214,15 @@ extern "C" void mps_plan_destroy(mps_plan *plan) {
     delete plan;
 }
 
-extern "C" int mps_plan_tune(mps_plan *p, int32_t chunks_per_unit, int32_t unroll, int32_t bulk_staging) {
+extern "C" int mps_plan_tune(mps_plan *p, int32_t chunks_per_unit, int32_t unroll, int32_t bulk_staging, int32_t block_threads) {
     if (!p) return fail(MPS_ERR_ARG, "mps_plan_tune: plan is NULL");
     if (unroll != 0 && unroll != 4 && unroll != 8) return fail(MPS_ERR_ARG, "mps_plan_tune: unroll must be 0, 4 or 8");
     if (chunks_per_unit < 0 || chunks_per_unit > 4096) return fail(MPS_ERR_ARG, "mps_plan_tune: chunks_per_unit out of range");
+    if (block_threads != 0 && block_threads != 64 && block_threads != 128 && block_threads != 256)
+        return fail(MPS_ERR_ARG, "mps_plan_tune: block_threads must be 0, 64, 128 or 256");
+    if (block_threads != 0 && block_threads < p->gl) return fail(MPS_ERR_ARG, "mps_plan_tune: a block must hold at least one group of %d lanes", p->gl);
+    p->user_block = block_threads != 0;
+    if (p->user_block) p->block = block_threads;
     const int old_tiles = p->n_tiles;
     p->user_cpu = chunks_per_unit > 0;
     if (p->user_cpu) p->cpu = chunks_per_unit;
@@ -250,20 +258,34 @@ extern "C" int mps_plan_partition(mps_plan *p, const int32_t *d_row_ptr, void *s
     return MPS_OK;
 }
 
-template <typename T, int VEC, int GL, int U>
+template <typename T, int VEC, int GL, int U, int BLOCK>
 static int launch_tile(const mps_plan *p, const TileParams &tp, cudaStream_t st) {
-    auto kern = spmm_tile_kernel<T, VEC, GL, U>;
-    if (p->smem_bytes > 48 * 1024) MPS_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, p->smem_bytes));
-    dim3 grid((unsigned)p->n_tiles, (unsigned)p->n_col_slabs);
-    kern<<<grid, kBlock, p->smem_bytes, st>>>(tp);
-    MPS_CUDA(cudaGetLastError());
-    return MPS_OK;
+    if constexpr (BLOCK < GL) {
+        return fail(MPS_ERR_STATE, "block of %d threads cannot hold a group of %d lanes", BLOCK, GL);
+    } else {
+        auto kern = spmm_tile_kernel<T, VEC, GL, U, BLOCK>;
+        if (p->smem_bytes > 48 * 1024) MPS_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, p->smem_bytes));
+        dim3 grid((unsigned)p->n_tiles, (unsigned)p->n_col_slabs);
+        kern<<<grid, BLOCK, p->smem_bytes, st>>>(tp);
+        MPS_CUDA(cudaGetLastError());
+        return MPS_OK;
+    }
+}
+
+template <typename T, int VEC, int GL, int U>
+static int launch_tile_b(const mps_plan *p, const TileParams &tp, cudaStream_t st) {
+    switch (p->block) {
+        case 64: return launch_tile<T, VEC, GL, U, 64>(p, tp, st);
+        case 128: return launch_tile<T, VEC, GL, U, 128>(p, tp, st);
+        case 256: return launch_tile<T, VEC, GL, U, 256>(p, tp, st);
+    }
+    return fail(MPS_ERR_STATE, "no kernel for blocks of %d threads", p->block);
 }
 
 template <typename T, int VEC, int GL>
 static int launch_tile_u(const mps_plan *p, const TileParams &tp, cudaStream_t st) {
-    if (p->unroll == 8) return launch_tile<T, VEC, GL, 8>(p, tp, st);
-    return launch_tile<T, VEC, GL, 4>(p, tp, st);
+    if (p->unroll == 8) return launch_tile_b<T, VEC, GL, 8>(p, tp, st);
+    return launch_tile_b<T, VEC, GL, 4>(p, tp, st);
 }
 
 template <typename T, int VEC>
@@ -283,7 +305,7 @@ static int spmm_typed(mps_plan *p, const TileParams &tp, cudaStream_t st) {
     int rc;
     const bool prof = p->profiling && p->prof_used < kProfSlots;
     if (prof) MPS_CUDA(cudaEventRecord(p->prof_ev[2 * p->prof_used], st));
-    if (p->vec == 1) rc = launch_tile<T, 1, 32, 4>(p, tp, st);
+    if (p->vec == 1) rc = launch_tile_b<T, 1, 32, 4>(p, tp, st);
     else rc = launch_tile_gl<T, FULLVEC>(p, tp, st);
     if (rc != MPS_OK) return rc;
     if (prof) { MPS_CUDA(cudaEventRecord(p->prof_ev[2 * p->prof_used + 1], st)); ++p->prof_used; }
@@ -368,7 +390,7 @@ extern "C" int mps_plan_info(const mps_plan *p, int64_t what[16]) {
     what[4] = p->gl; what[5] = p->vec; what[6] = p->unroll; what[7] = p->smem_bytes;
     what[8] = p->n_long; what[9] = p->tpw_effective;
     what[10] = 1 + (p->n_tiles > 1 ? 1 : 0) + (p->n_long > 0 ? 1 : 0);
-    what[11] = p->long_chain; what[12] = p->cpu; what[13] = kBlock / p->gl;
+    what[11] = p->long_chain; what[12] = p->cpu; what[13] = p->block / p->gl; what[14] = p->block;
     return MPS_OK;
 }
 

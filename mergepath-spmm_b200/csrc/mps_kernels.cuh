@@ -25,10 +25,8 @@
 
 namespace mps {
 
-#ifndef MPS_MIN_BLOCKS
-#define MPS_MIN_BLOCKS 3  // tile blocks per SM the register allocation is held to
-#endif
-constexpr int kBlock = 256;          // threads per tile block
+constexpr int kWarpsPerSm = 24;      // resident warps per SM the register allocation is held to (768 threads)
+constexpr int kMaxBlock = 256;       // largest tile block (threads); 64 and 128 are the other sizes
 constexpr int kStrands = 16;         // interleaved partial sums of the long-row fix-up
 constexpr int kAlign = 8;            // staging windows start on multiples of 8 elements (>= 16 bytes)
 constexpr int kWaitPolls = 1 << 22;  // bounded mbarrier wait
@@ -306,8 +304,9 @@ __device__ __forceinline__ void stage_ragged(E *s_dst, const E *g_src, long long
 // ---------------------------------------------------------------------------------------------
 // One block = one tile = GPC units; unit u = `cpu` consecutive chunks walked by one group of GL
 // lanes with the accumulator kept in registers across the chunk boundaries inside the unit.
-template <typename T, int VEC, int GL, int U>
-__global__ void __launch_bounds__(kBlock, MPS_MIN_BLOCKS) spmm_tile_kernel(const TileParams p) {
+template <typename T, int VEC, int GL, int U, int BLOCK>
+__global__ void __launch_bounds__(BLOCK, kWarpsPerSm * 32 / BLOCK) spmm_tile_kernel(const TileParams p) {
+    constexpr int kBlock = BLOCK;
     constexpr int GPC = kBlock / GL;   // units (lane groups) per block
     constexpr int SLAB = GL * VEC;     // columns covered by one block
     extern __shared__ __align__(128) unsigned char smem[];

@@ -9,11 +9,12 @@ struct mps_plan {
     int n_rows, nnz, dim, dtype, cost, tpw_requested, tpw_effective;
     int n_chunks, ipt;
     int vec, gl, unroll, slab_cols, n_col_slabs;
+    int block;                          // threads per tile block (64, 128 or 256)
     int nch, cpu, n_tiles, smem_bytes;  // chunks per tile, chunks per unit
     int bulk;
     int long_chain, n_long, long_capacity;
     int device, sm_count;
-    bool user_cpu, user_unroll;
+    bool user_cpu, user_unroll, user_block;
     bool partitioned;
     int2 *d_tile_xy;
     float *d_tcarry, *d_thead;
