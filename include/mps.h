@@ -123,8 +123,8 @@ MPS_API int mps_plan_tune(mps_plan *plan, int32_t chunks_per_unit, int32_t unrol
                   int32_t block_threads);
 
 /* Replaces the call of generate_mp_sched and the eleven uploads that follow it
- * (src/MergePathSpMM.cu:192-220): searches the tile boundaries on the device and lists the rows
- * whose carries span many tiles.  Must be called once per row_ptr before mps_spmm; synchronises
+ * (src/MergePathSpMM.cu:192-220): searches the tile boundaries on the device, records for every tile
+ * which tile ends the row its carry belongs to, and lists the rows whose carries span thousands of tiles.  Must be called once per row_ptr before mps_spmm; synchronises
  * the stream once (it reads back one counter). */
 MPS_API int mps_plan_partition(mps_plan *plan, const int32_t *d_row_ptr, void *stream);
 
@@ -145,7 +145,7 @@ MPS_API int mps_plan_sync_check(mps_plan *plan, void *stream);
  * what[3]=n_tiles what[4]=lanes_per_chunk what[5]=elements_per_lane what[6]=unroll
  * what[7]=shared_bytes_per_block what[8]=long_rows what[9]=effective threads_per_warp
  * what[10]=kernels per mps_spmm call what[11]=long_chain threshold what[12]=chunks_per_unit
- * what[13]=units_per_tile what[14]=threads per tile block; what[15] reserved (0). */
+ * what[13]=units_per_tile what[14]=threads per tile block what[15]=very_long chain threshold. */
 MPS_API int mps_plan_info(const mps_plan *plan, int64_t what[16]);
 
 /* Per-kernel timing (no reference counterpart; the reference is timed from outside with nvprof,

@@ -87,7 +87,7 @@ class Plan:
     """Shape-bound plan: create -> (tune) -> partition(row_ptr) -> spmm(...) any number of times."""
 
     INFO = ("n_chunks", "items_per_chunk", "chunks_per_tile", "n_tiles", "lanes_per_chunk", "elements_per_lane", "unroll",
-            "shared_bytes", "long_rows", "threads_per_warp", "kernels_per_call", "long_chain", "chunks_per_unit", "units_per_tile", "block_threads")
+            "shared_bytes", "long_rows", "threads_per_warp", "kernels_per_call", "long_chain", "chunks_per_unit", "units_per_tile", "block_threads", "very_long")
 
     def __init__(self, n_rows: int, nnz: int, dim: int, dtype=F32, cost: int = 8, threads_per_warp: int = 1, device=None):
         self._h = C.c_void_p()

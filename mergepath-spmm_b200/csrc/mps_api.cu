@@ -163,6 +163,7 @@ void mps::plan_init_shape(mps_plan *p, int n_rows, int nnz, int dim, int dtype, 
     p->n_col_slabs = (dim + p->slab_cols - 1) / p->slab_cols;
     p->bulk = 1;
     p->long_chain = 32;
+    p->very_long = 8192;
 }
 
 int mps::plan_finish_layout(mps_plan *p) { return plan_layout(p); }
@@ -170,13 +171,15 @@ int mps::plan_finish_layout(mps_plan *p) { return plan_layout(p); }
 static void plan_free_scratch(mps_plan *p) {
     cudaFree(p->d_tile_xy); cudaFree(p->d_tcarry); cudaFree(p->d_thead);
     cudaFree(p->d_status); cudaFree(p->d_long_list); cudaFree(p->d_long_count);
+    cudaFree(p->d_consumer); cudaFree(p->d_need); cudaFree(p->d_cnt);
     p->d_tile_xy = nullptr; p->d_tcarry = p->d_thead = nullptr;
     p->d_status = p->d_long_list = p->d_long_count = nullptr;
+    p->d_consumer = p->d_need = p->d_cnt = nullptr;
 }
 
 static int plan_alloc_scratch(mps_plan *p) {
     plan_free_scratch(p);
-    p->long_capacity = p->n_tiles / p->long_chain + 2;
+    p->long_capacity = p->n_tiles / p->very_long + 2;
     const size_t rows = (size_t)p->n_tiles * p->dim * sizeof(float);
     MPS_CUDA(cudaMalloc(&p->d_tile_xy, sizeof(int2) * ((size_t)p->n_tiles + 1)));
     MPS_CUDA(cudaMalloc(&p->d_tcarry, rows ? rows : 4));
@@ -184,6 +187,9 @@ static int plan_alloc_scratch(mps_plan *p) {
     MPS_CUDA(cudaMalloc(&p->d_status, sizeof(int)));
     MPS_CUDA(cudaMalloc(&p->d_long_list, sizeof(int) * (size_t)p->long_capacity));
     MPS_CUDA(cudaMalloc(&p->d_long_count, sizeof(int)));
+    MPS_CUDA(cudaMalloc(&p->d_consumer, sizeof(int) * (size_t)p->n_tiles));
+    MPS_CUDA(cudaMalloc(&p->d_need, sizeof(int) * (size_t)p->n_tiles));
+    MPS_CUDA(cudaMalloc(&p->d_cnt, sizeof(int) * (size_t)p->n_tiles * p->n_col_slabs));
     MPS_CUDA(cudaMemset(p->d_status, 0, sizeof(int)));
     return MPS_OK;
 }
@@ -244,11 +250,10 @@ extern "C" int mps_plan_partition(mps_plan *p, const int32_t *d_row_ptr, void *s
                                                          p->d_tile_xy);
     MPS_CUDA(cudaGetLastError());
     MPS_CUDA(cudaMemsetAsync(p->d_long_count, 0, sizeof(int), st));
-    if (p->n_tiles > 1) {
-        fixup_list_long_kernel<<<(p->n_tiles - 1 + 255) / 256, 256, 0, st>>>(p->d_tile_xy, d_row_ptr, p->n_tiles, p->long_chain,
-                                                                            p->d_long_list, p->d_long_count, p->long_capacity);
-        MPS_CUDA(cudaGetLastError());
-    }
+    MPS_CUDA(cudaMemsetAsync(p->d_cnt, 0, sizeof(int) * (size_t)p->n_tiles * p->n_col_slabs, st));
+    fixup_plan_kernel<<<(p->n_tiles + 255) / 256, 256, 0, st>>>(p->d_tile_xy, d_row_ptr, p->n_tiles, p->very_long, p->d_consumer, p->d_need,
+                                                                p->d_long_list, p->d_long_count, p->long_capacity);
+    MPS_CUDA(cudaGetLastError());
     int n_long = 0;
     MPS_CUDA(cudaMemcpyAsync(&n_long, p->d_long_count, sizeof(int), cudaMemcpyDeviceToHost, st));
     MPS_CUDA(cudaStreamSynchronize(st));
@@ -309,12 +314,6 @@ static int spmm_typed(mps_plan *p, const TileParams &tp, cudaStream_t st) {
     else rc = launch_tile_gl<T, FULLVEC>(p, tp, st);
     if (rc != MPS_OK) return rc;
     if (prof) { MPS_CUDA(cudaEventRecord(p->prof_ev[2 * p->prof_used + 1], st)); ++p->prof_used; }
-    if (p->n_tiles > 1) {
-        const int warps = p->n_tiles - 1;
-        fixup_short_kernel<T><<<(warps + 7) / 8, 256, 0, st>>>(p->d_tile_xy, tp.rp, p->d_tcarry, p->d_thead, static_cast<T *>(tp.C),
-                                                              p->n_tiles, p->dim, p->long_chain);
-        MPS_CUDA(cudaGetLastError());
-    }
     if (p->n_long > 0) {
         fixup_long_kernel<T><<<p->n_long, kStrands * 32, 0, st>>>(p->d_tile_xy, tp.rp, p->d_tcarry, p->d_thead, static_cast<T *>(tp.C),
                                                                  p->d_long_list, p->dim);
@@ -336,6 +335,7 @@ extern "C" int mps_spmm(mps_plan *p, const int32_t *d_row_ptr, const int32_t *d_
     TileParams tp;
     tp.rp = d_row_ptr; tp.col = d_col_idx; tp.val = d_val; tp.B = d_B; tp.C = d_C;
     tp.tile_xy = p->d_tile_xy; tp.tcarry = p->d_tcarry; tp.thead = p->d_thead; tp.status = p->d_status;
+    tp.consumer = p->d_consumer; tp.need = p->d_need; tp.cnt = p->d_cnt; tp.long_chain = p->long_chain; tp.very_long = p->very_long;
     tp.total = (long long)p->n_rows + 1 + p->nnz;
     tp.n_rows = p->n_rows; tp.nnz = p->nnz; tp.dim = p->dim;
     tp.ipt = p->ipt; tp.nch = p->nch; tp.cpu = p->cpu; tp.n_tiles = p->n_tiles;
@@ -353,6 +353,7 @@ extern "C" int mps_plan_sync_check(mps_plan *p, void *stream) {
     MPS_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
     if (status != kDevOk) {
         cudaMemsetAsync(p->d_status, 0, sizeof(int), (cudaStream_t)stream);
+        cudaMemsetAsync(p->d_cnt, 0, sizeof(int) * (size_t)p->n_tiles * p->n_col_slabs, (cudaStream_t)stream);  // a block that gave up left its count short
         return fail(MPS_ERR_DEVICE, "a tile block gave up waiting for its staged window (status %d)", status);
     }
     return MPS_OK;
@@ -389,8 +390,8 @@ extern "C" int mps_plan_info(const mps_plan *p, int64_t what[16]) {
     what[0] = p->n_chunks; what[1] = p->ipt; what[2] = p->nch; what[3] = p->n_tiles;
     what[4] = p->gl; what[5] = p->vec; what[6] = p->unroll; what[7] = p->smem_bytes;
     what[8] = p->n_long; what[9] = p->tpw_effective;
-    what[10] = 1 + (p->n_tiles > 1 ? 1 : 0) + (p->n_long > 0 ? 1 : 0);
-    what[11] = p->long_chain; what[12] = p->cpu; what[13] = p->block / p->gl; what[14] = p->block;
+    what[10] = 1 + (p->n_long > 0 ? 1 : 0);
+    what[11] = p->long_chain; what[12] = p->cpu; what[13] = p->block / p->gl; what[14] = p->block; what[15] = p->very_long;
     return MPS_OK;
 }
 

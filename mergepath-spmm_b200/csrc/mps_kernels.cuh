@@ -14,9 +14,10 @@
 //            registers across the chunk boundaries inside the unit.  Rows that end inside the unit
 //            and began there are stored directly; a row that began earlier leaves its share as the
 //            unit's "head", what is left at the unit's end is its "carry" (shared memory, fp32).
-//   fix-up = inside the tile, in unit order, by the group that ended the row; across tiles by
-//            fixup kernels that add the tiles' carry rows in tile order.  No atomics touch C, every
-//            row of C is stored exactly once, sums are bitwise reproducible.
+//   fix-up = inside the tile, in unit order, by the group that ended the row; across tiles by the
+//            tile block whose contribution to the row arrives last (a counter per ending tile; nobody
+//            waits), which adds the tiles' carry rows in tile order.  No atomics touch C, every row
+//            of C is stored exactly once, sums are bitwise reproducible.
 #pragma once
 
 #include <cuda_fp16.h>
@@ -43,6 +44,10 @@ struct TileParams {
     float *tcarry;        // n_tiles x dim
     float *thead;         // n_tiles x dim
     int *status;
+    const int *consumer;  // per tile: the tile that ends the row this tile's carry belongs to, or -1
+    const int *need;      // per tile: contributions its cross-tile fix-up waits for (0 = none)
+    int *cnt;             // per (column slab, tile): contributions that have arrived; zero between launches
+    int long_chain, very_long;
     long long total;  // N + 1 + nnz
     int n_rows, nnz, dim;
     int ipt, nch, cpu, n_tiles;  // items per chunk, chunks per tile, chunks per unit
@@ -300,6 +305,62 @@ __device__ __forceinline__ void stage_ragged(E *s_dst, const E *g_src, long long
 }
 
 // ---------------------------------------------------------------------------------------------
+// cross-tile fix-up helpers
+// ---------------------------------------------------------------------------------------------
+// Tile t needs a cross-tile fix-up when it ends (consumes a marker of) a row that began in an
+// earlier tile.  Returns that row, and in `s` the first tile whose carry belongs to it.
+__device__ __forceinline__ int fixup_candidate(const int2 *__restrict__ xy, const int *__restrict__ rp, int t, int &s) {
+    const int2 a = __ldg(xy + t), b = __ldg(xy + t + 1);
+    if (!(a.x >= 1 && b.x > a.x && a.y > __ldg(rp + a.x - 1))) return -1;
+    // f = first tile that starts with x == a.x (tiles f..t start inside the row); f >= 1
+    int lo = 0, hi = t;
+    if (__ldg(xy + t - 1).x != a.x) lo = t;
+    while (lo < hi) {
+        const int mid = (lo + hi) >> 1;
+        if (__ldg(xy + mid).x < a.x) lo = mid + 1;
+        else hi = mid;
+    }
+    s = lo - 1;
+    return a.x - 1;
+}
+
+__device__ __forceinline__ void store_c(float *p, float v) { *p = v; }
+__device__ __forceinline__ void store_c(__half *p, float v) { *p = __float2half_rn(v); }
+
+// Cross-tile fix-up of tile e, run by the tile block whose contribution arrived last: columns
+// [col0, col1) of row x_e - 1 = 0 + tcarry[s] + .. + tcarry[e-1] + thead[e] in that order, or, for
+// chains longer than long_chain, 16 interleaved strands (strand g = tcarry[s+g] + tcarry[s+g+16] + ..)
+// added in strand order, then thead[e].  The operands were written by other blocks: read through L2.
+template <typename T, int BLOCK>
+__device__ __forceinline__ void block_fixup(const TileParams &p, int e, int chain, int col0, int col1, int tid) {
+    const int row = __ldg(p.tile_xy + e).x - 1;
+    const int s = e - chain;
+    const size_t dim = (size_t)p.dim;
+    for (int j = col0 + tid; j < col1; j += BLOCK) {
+        float sum = 0.0f;
+        if (chain <= p.long_chain) {
+            for (int q = s; q < e; ++q) sum += __ldcg(p.tcarry + (size_t)q * dim + j);
+        } else {
+            float sg[kStrands];
+#pragma unroll
+            for (int g = 0; g < kStrands; ++g) sg[g] = 0.0f;
+            int q = s;
+            for (; q + kStrands <= e; q += kStrands) {
+#pragma unroll
+                for (int g = 0; g < kStrands; ++g) sg[g] += __ldcg(p.tcarry + (size_t)(q + g) * dim + j);
+            }
+#pragma unroll
+            for (int g = 0; g < kStrands; ++g)
+                if (q + g < e) sg[g] += __ldcg(p.tcarry + (size_t)(q + g) * dim + j);
+#pragma unroll
+            for (int g = 0; g < kStrands; ++g) sum += sg[g];
+        }
+        sum += __ldcg(p.thead + (size_t)e * dim + j);
+        store_c(static_cast<T *>(p.C) + (size_t)row * dim + j, sum);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
 // the tile kernel
 // ---------------------------------------------------------------------------------------------
 // One block = one tile = GPC units; unit u = `cpu` consecutive chunks walked by one group of GL
@@ -504,63 +565,79 @@ __global__ void __launch_bounds__(BLOCK, kWarpsPerSm * 32 / BLOCK) spmm_tile_ker
         for (int q = s; q < GPC; ++q) vec_add<VEC>(sum, s_carry + q * SLAB + l * VEC);
         if (active) gmem_put_f32<VEC>(p.tcarry + (size_t)t * dim + coff, sum);
     }
+
+    // ---- cross-tile fix-up without a second kernel: every contribution (a tile's carry, the ending tile's
+    // head) bumps the counter of the tile that ends the row; the block that brings the count to `need`
+    // finds everything in place and sums it, in the fixed order.  No block ever waits for another.
+    __threadfence();  // this thread's tcarry / thead stores are visible device-wide before the count moves
+    __syncthreads();
+    int *s_todo = s_fx;  // the unit boundaries are no longer needed
+    if (tid == 0) {
+        __threadfence();
+        int *cnt = p.cnt + (size_t)blockIdx.y * p.n_tiles;
+        int todo0 = -1, todo1 = -1;
+        const int e = __ldg(p.consumer + t);
+        if (e >= 0 && atomicAdd(cnt + e, 1) + 1 == __ldg(p.need + e)) todo0 = e;
+        const int mine = __ldg(p.need + t);
+        if (mine > 0 && atomicAdd(cnt + t, 1) + 1 == mine) todo1 = t;
+        if (todo0 >= 0) cnt[todo0] = 0;  // ready for the next launch
+        if (todo1 >= 0) cnt[todo1] = 0;
+        __threadfence();
+        s_todo[0] = todo0;
+        s_todo[1] = todo1;
+    }
+    __syncthreads();
+    const int col0 = blockIdx.y * SLAB, col1 = col0 + SLAB < p.dim ? col0 + SLAB : p.dim;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int e = s_todo[i];
+        if (e < 0) continue;
+        const int chain = __ldg(p.need + e) - 1;
+        if (chain <= p.very_long) block_fixup<T, kBlock>(p, e, chain, col0, col1, tid);  // longer chains: fixup_long_kernel
+    }
 }
 
 // ---------------------------------------------------------------------------------------------
 // cross-tile fix-up
 // ---------------------------------------------------------------------------------------------
-// Tile t needs a cross-tile fix-up when it ends (consumes a marker of) a row that began in an
-// earlier tile.  Returns that row, and in `s` the first tile whose carry belongs to it.
-__device__ __forceinline__ int fixup_candidate(const int2 *__restrict__ xy, const int *__restrict__ rp, int t, int &s) {
-    const int2 a = __ldg(xy + t), b = __ldg(xy + t + 1);
-    if (!(a.x >= 1 && b.x > a.x && a.y > __ldg(rp + a.x - 1))) return -1;
-    // f = first tile that starts with x == a.x (tiles f..t start inside the row); f >= 1
-    int lo = 0, hi = t;
-    if (__ldg(xy + t - 1).x != a.x) lo = t;
+// Plan time, one thread per tile: how many contributions the tile's cross-tile fix-up waits for
+// (its own head plus one carry per tile of the chain), which tile consumes this tile's carry, and the
+// list of tiles whose chain is too long to be summed by one tile block (very_long).
+__global__ void fixup_plan_kernel(const int2 *__restrict__ xy, const int *__restrict__ rp, int n_tiles, int very_long,
+                                  int *__restrict__ consumer, int *__restrict__ need, int *__restrict__ list, int *__restrict__ count,
+                                  int capacity) {
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= n_tiles) return;
+    int s = 0, n = 0;
+    if (t >= 1 && fixup_candidate(xy, rp, t, s) >= 0) {
+        n = t - s + 1;
+        if (t - s > very_long) {
+            const int at = atomicAdd(count, 1);
+            if (at < capacity) list[at] = t;
+        }
+    }
+    need[t] = n;
+    // the row in progress when tile t ends is row xe-1; it is ended by the tile e that consumes marker xe:
+    // j = first boundary with x > xe, e = j - 1 (>= t + 1)
+    const int xe = __ldg(xy + t + 1).x;
+    int lo = t + 2, hi = n_tiles + 1;
     while (lo < hi) {
         const int mid = (lo + hi) >> 1;
-        if (__ldg(xy + mid).x < a.x) lo = mid + 1;
-        else hi = mid;
+        if (__ldg(xy + mid).x > xe) hi = mid;
+        else lo = mid + 1;
     }
-    s = lo - 1;
-    return a.x - 1;
-}
-
-__device__ __forceinline__ void store_c(float *p, float v) { *p = v; }
-__device__ __forceinline__ void store_c(__half *p, float v) { *p = __float2half_rn(v); }
-
-// one warp per tile; chains of up to long_chain tiles
-template <typename T>
-__global__ void fixup_short_kernel(const int2 *__restrict__ xy, const int *__restrict__ rp, const float *__restrict__ tcarry,
-                                   const float *__restrict__ thead, T *__restrict__ C, int n_tiles, int dim, int long_chain) {
-    const int t = 1 + (blockIdx.x * blockDim.x + threadIdx.x) / 32;
-    const int lane = threadIdx.x % 32;
-    if (t >= n_tiles) return;
-    int s;
-    const int row = fixup_candidate(xy, rp, t, s);
-    if (row < 0 || t - s > long_chain) return;
-    for (int j = lane; j < dim; j += 32) {
-        float sum = 0.0f;
-        for (int q = s; q < t; ++q) sum += tcarry[(size_t)q * dim + j];
-        sum += thead[(size_t)t * dim + j];
-        store_c(C + (size_t)row * dim + j, sum);
+    int e = -1;
+    if (lo <= n_tiles) {
+        e = lo - 1;
+        const int2 a = __ldg(xy + e);
+        if (!(a.x >= 1 && a.y > __ldg(rp + a.x - 1))) e = -1;  // the row starts exactly where tile e starts: nothing carried in
     }
+    consumer[t] = e;
 }
 
-// lists the tiles whose chain is longer than long_chain (plan time)
-__global__ void fixup_list_long_kernel(const int2 *__restrict__ xy, const int *__restrict__ rp, int n_tiles, int long_chain,
-                                       int *__restrict__ list, int *__restrict__ count, int capacity) {
-    const int t = 1 + blockIdx.x * blockDim.x + threadIdx.x;
-    if (t >= n_tiles) return;
-    int s;
-    const int row = fixup_candidate(xy, rp, t, s);
-    if (row < 0 || t - s <= long_chain) return;
-    const int at = atomicAdd(count, 1);
-    if (at < capacity) list[at] = t;
-}
-
-// one block of kStrands warps per listed tile: strand g adds carries s+g, s+g+16, ... in order,
-// then strand 0 adds the strands in order and the tile's head last
+// Chains longer than very_long (a row spanning thousands of tiles): one block of kStrands warps per
+// listed tile, after the tile kernel.  Strand g adds carries s+g, s+g+16, ... in order, then strand 0
+// adds the strands in order and the tile's head last - the same order block_fixup uses.
 template <typename T>
 __global__ void __launch_bounds__(kStrands * 32) fixup_long_kernel(const int2 *__restrict__ xy, const int *__restrict__ rp,
                                                                     const float *__restrict__ tcarry, const float *__restrict__ thead,

@@ -13,8 +13,9 @@
 //   - problems whose scratch does not fit are rejected with MPS_ERR_UNSUPPORTED (limits below);
 //   - all calls on a device share the array, so two calls that overlap on the GPU (different
 //     streams or host threads) race on it - serialise them;
-//   - the array keeps the previous call's contents; the two words that must start at zero (status,
-//     long-row counter) are cleared by every call, everything else is written before it is read;
+//   - the array keeps the previous call's contents; what must start at zero (status word, long-row
+//     counter, the per-tile arrival counters) is cleared by every call, everything else is written
+//     before it is read;
 //   - the first call on each device looks up the array's device address (cudaGetSymbolAddress) -
 //     make that first call outside any stream capture.
 // Nothing in this path calls cudaMalloc, cudaFree or a library routine that allocates.
@@ -34,8 +35,7 @@ namespace {
 
 constexpr int kMaxTiles = MPS_NOALLOC_MAX_TILES;
 constexpr size_t kMaxCarryFloats = MPS_NOALLOC_MAX_CARRY_FLOATS;
-constexpr int kLongChain = 32;                        // plan_init_shape's threshold
-constexpr int kMaxLong = kMaxTiles / kLongChain + 2;  // long-row list entries
+constexpr int kMaxLong = kMaxTiles / 32 + 2;  // very-long-row list entries (more than the plan ever asks for)
 
 // byte offsets inside the scratch array, each a multiple of 256
 constexpr size_t up256(size_t v) { return (v + 255) & ~(size_t)255; }
@@ -43,7 +43,10 @@ constexpr size_t kOffStatus = 0;
 constexpr size_t kOffCount = 256;
 constexpr size_t kOffTileXy = 512;
 constexpr size_t kOffLongList = kOffTileXy + up256(sizeof(int2) * ((size_t)kMaxTiles + 1));
-constexpr size_t kOffCarry = kOffLongList + up256(sizeof(int) * (size_t)kMaxLong);
+constexpr size_t kOffConsumer = kOffLongList + up256(sizeof(int) * (size_t)kMaxLong);
+constexpr size_t kOffNeed = kOffConsumer + up256(sizeof(int) * (size_t)kMaxTiles);
+constexpr size_t kOffCnt = kOffNeed + up256(sizeof(int) * (size_t)kMaxTiles);
+constexpr size_t kOffCarry = kOffCnt + up256(sizeof(int) * (size_t)kMaxTiles);
 constexpr size_t kOffHead = kOffCarry + up256(sizeof(float) * kMaxCarryFloats);
 constexpr size_t kScratchBytes = kOffHead + up256(sizeof(float) * kMaxCarryFloats);
 static_assert(kScratchBytes <= MPS_NOALLOC_SCRATCH_BYTES, "the header states the size of the scratch array");
@@ -88,7 +91,7 @@ extern "C" int mps_spmm_noalloc(int32_t n_rows, int32_t nnz, int32_t dim, int dt
     mps::plan_init_shape(&plan, n_rows, nnz, dim, dtype, cost, threads_per_warp);
     if (int rc = mps::plan_finish_layout(&plan)) return rc;
     const size_t carry_floats = (size_t)plan.n_tiles * (size_t)dim;
-    if (plan.n_tiles > kMaxTiles || carry_floats > kMaxCarryFloats)
+    if ((long long)plan.n_tiles * plan.n_col_slabs > kMaxTiles || carry_floats > kMaxCarryFloats)
         return fail(MPS_ERR_UNSUPPORTED,
                     "mps_spmm_noalloc: this problem needs %d tiles and %zu carry floats; the built-in scratch holds at most %d tiles and "
                     "%zu floats (tiles x dim) - use mps_plan_create/mps_spmm, which allocate what they need",
@@ -100,14 +103,17 @@ extern "C" int mps_spmm_noalloc(int32_t n_rows, int32_t nnz, int32_t dim, int dt
     plan.d_long_count = reinterpret_cast<int *>(base + kOffCount);
     plan.d_tile_xy = reinterpret_cast<int2 *>(base + kOffTileXy);
     plan.d_long_list = reinterpret_cast<int *>(base + kOffLongList);
+    plan.d_consumer = reinterpret_cast<int *>(base + kOffConsumer);
+    plan.d_need = reinterpret_cast<int *>(base + kOffNeed);
+    plan.d_cnt = reinterpret_cast<int *>(base + kOffCnt);
     plan.d_tcarry = reinterpret_cast<float *>(base + kOffCarry);
     plan.d_thead = reinterpret_cast<float *>(base + kOffHead);
-    plan.long_capacity = plan.n_tiles / plan.long_chain + 2;  // <= kMaxLong because n_tiles <= kMaxTiles
+    plan.long_capacity = plan.n_tiles / plan.very_long + 2;  // <= kMaxLong because n_tiles <= kMaxTiles
 
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     cudaError_t e = cudaMemsetAsync(plan.d_status, 0, sizeof(int), st);  // left over from the previous call otherwise
     if (e != cudaSuccess) return fail(MPS_ERR_CUDA, "cudaMemsetAsync(status): %s", cudaGetErrorString(e));
-    if (int rc = mps_plan_partition(&plan, d_row_ptr, stream)) return rc;  // clears the long-row counter itself
+    if (int rc = mps_plan_partition(&plan, d_row_ptr, stream)) return rc;  // clears the long-row counter and the arrival counters itself
     if (int rc = mps_spmm(&plan, d_row_ptr, d_col_idx, d_val, d_B, d_C, stream)) return rc;
     return mps_plan_sync_check(&plan, stream);
 }

@@ -12,13 +12,14 @@ struct mps_plan {
     int block;                          // threads per tile block (64, 128 or 256)
     int nch, cpu, n_tiles, smem_bytes;  // chunks per tile, chunks per unit
     int bulk;
-    int long_chain, n_long, long_capacity;
+    int long_chain, very_long, n_long, long_capacity;  // chain lengths (tiles): strand order above long_chain, own kernel above very_long
     int device, sm_count;
     bool user_cpu, user_unroll, user_block;
     bool partitioned;
     int2 *d_tile_xy;
     float *d_tcarry, *d_thead;
     int *d_status, *d_long_list, *d_long_count;
+    int *d_consumer, *d_need, *d_cnt;  // per tile: who ends my carry's row, contributions awaited, arrivals (x column slabs)
     bool profiling;
     int prof_used;
     cudaEvent_t prof_ev[2 * kProfSlots];

@@ -169,13 +169,27 @@ def test_edge_case_graphs(mps, orc, cuda, name):
             _check(orc, rp, col, val, B, got, info, cost, 1e-5)
 
 
-def test_long_rows_take_the_strand_fixup(mps, orc, cuda):
+def test_long_rows_take_the_strand_order(mps, orc, cuda):
+    """A row spanning more than long_chain tiles is summed in 16 interleaved strands, still by the tile
+    block whose contribution arrives last: one kernel per SpMM."""
     rp, col = cases.edge_cases()["one_giant_row"]
     rng = np.random.default_rng(5)
     B = rng.uniform(-1, 1, (6000, 64)).astype(np.float32)
     got, info = _run(mps, cuda, rp, col, None, B, 1, dict(chunks_per_unit=1))
-    assert info["long_rows"] >= 1 and info["kernels_per_call"] == 3
+    assert info["kernels_per_call"] == 1 and info["long_rows"] == 0
+    assert 5000 // (info["chunks_per_tile"] * info["items_per_chunk"]) > info["long_chain"]
     _check(orc, rp, col, None, B, got, info, 1, 1e-5)
+
+
+def test_rows_spanning_thousands_of_tiles_take_the_second_kernel(mps, orc, cuda):
+    rp, col = cases.from_lengths([3, 80000, 2, 0, 5], 90000, 21)
+    rng = np.random.default_rng(6)
+    val = rng.uniform(-1, 1, len(col)).astype(np.float32)
+    B = rng.uniform(-1, 1, (90000, 64)).astype(np.float32)
+    got, info = _run(mps, cuda, rp, col, val, B, 1, dict(chunks_per_unit=1))
+    assert info["long_rows"] == 1 and info["kernels_per_call"] == 2
+    assert 80000 // (info["chunks_per_tile"] * info["items_per_chunk"]) > info["very_long"]
+    _check(orc, rp, col, val, B, got, info, 1, 1e-5)
 
 
 @pytest.mark.parametrize("tune", [dict(chunks_per_unit=1), dict(chunks_per_unit=3), dict(chunks_per_unit=20, unroll=4),
