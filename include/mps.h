@@ -181,9 +181,10 @@ MPS_API void mps_host_workspace_release(void);
  * the caller's device buffers as for mps_spmm; `cost`/`threads_per_warp` as for mps_plan_create.
  *
  * Limits: with T = tiles of the automatic layout (mps_plan_info what[3] of an equivalent plan),
- * T <= MPS_NOALLOC_MAX_TILES and T * dim <= MPS_NOALLOC_MAX_CARRY_FLOATS, else MPS_ERR_UNSUPPORTED
- * with the numbers in mps_last_error().  At dim 64 that is about 70 million merge items (rows +
- * non-zeros), at dim 128 about 35 million.  Every GPU that loads the library holds MPS_NOALLOC_SCRATCH_BYTES for this
+ * T * column_slabs <= MPS_NOALLOC_MAX_TILES and T * dim <= MPS_NOALLOC_MAX_CARRY_FLOATS, else MPS_ERR_UNSUPPORTED
+ * with the numbers in mps_last_error().  A tile holds about 1,088 merge items (rows + non-zeros),
+ * so at dim 64 that is about 17 million merge items, at dim 128 about 9 million, at dim <= 32 about 35
+ * million.  Every GPU that loads the library holds MPS_NOALLOC_SCRATCH_BYTES for this
  * array until the process exits.
  *
  * The array is shared by every call on a device: calls that overlap on the GPU race on it, so
