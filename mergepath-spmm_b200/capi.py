@@ -42,7 +42,7 @@ def lib():
     global _lib
     if _lib is not None:
         return _lib
-    path = _build.LIB
+    path = os.environ.get("MPS_B200_LIB") or _build.LIB  # MPS_B200_LIB: use a library built elsewhere
     if not os.path.exists(path):
         path = _build.build_library()
     L = C.CDLL(path)
@@ -61,7 +61,7 @@ def lib():
     L.mps_plan_create.argtypes = [i32, i32, i32, C.c_int, i32, i32, C.POINTER(vp)]
     L.mps_plan_destroy.argtypes = [vp]
     L.mps_plan_destroy.restype = None
-    L.mps_plan_tune.argtypes = [vp, i32, i32, i32, i32]
+    L.mps_plan_tune.argtypes = [vp, i32, i32, i32, i32, i32]
     L.mps_plan_partition.argtypes = [vp, vp, vp]
     L.mps_spmm.argtypes = [vp, vp, vp, vp, vp, vp, vp]
     L.mps_plan_sync_check.argtypes = [vp, vp]

@@ -102,6 +102,7 @@ static int pow2_at_least(int v) {
 }
 
 static const int kSmemTargetPer256 = 64 * 1024;   // three tile blocks per SM, which the registers allow anyway
+static const int kFuseMaxTiles = 2048;       // up to here a second launch costs more than the fence the fused fix-up needs
 static const int kTilesPerSm = 6;            // smaller tiles rather than idle SMs on small problems
 static const int kUnitItems = 272;           // merge items one lane group walks per tile, at most
 static const int kTileItemsPerThread = 17;          // merge items per tile the automatic layout aims for
@@ -138,6 +139,7 @@ static int plan_layout(mps_plan *p) {
     if (p->smem_bytes > kSmemLimit)
         return fail(MPS_ERR_UNSUPPORTED, "tile of %d chunks x %d items needs %d bytes of shared memory", p->nch, p->ipt, p->smem_bytes);
     p->n_tiles = (p->n_chunks + p->nch - 1) / p->nch;
+    if (!p->user_fused) p->fused = (long long)p->n_tiles * p->n_col_slabs <= kFuseMaxTiles ? 1 : 0;
     return MPS_OK;
 }
 
@@ -220,13 +222,17 @@ extern "C" void mps_plan_destroy(mps_plan *plan) {
     delete plan;
 }
 
-extern "C" int mps_plan_tune(mps_plan *p, int32_t chunks_per_unit, int32_t unroll, int32_t bulk_staging, int32_t block_threads) {
+extern "C" int mps_plan_tune(mps_plan *p, int32_t chunks_per_unit, int32_t unroll, int32_t bulk_staging, int32_t block_threads,
+                             int32_t fused_fixup) {
     if (!p) return fail(MPS_ERR_ARG, "mps_plan_tune: plan is NULL");
     if (unroll != 0 && unroll != 4 && unroll != 8) return fail(MPS_ERR_ARG, "mps_plan_tune: unroll must be 0, 4 or 8");
     if (chunks_per_unit < 0 || chunks_per_unit > 4096) return fail(MPS_ERR_ARG, "mps_plan_tune: chunks_per_unit out of range");
     if (block_threads != 0 && block_threads != 64 && block_threads != 128 && block_threads != 256)
         return fail(MPS_ERR_ARG, "mps_plan_tune: block_threads must be 0, 64, 128 or 256");
     if (block_threads != 0 && block_threads < p->gl) return fail(MPS_ERR_ARG, "mps_plan_tune: a block must hold at least one group of %d lanes", p->gl);
+    if (fused_fixup < -1 || fused_fixup > 1) return fail(MPS_ERR_ARG, "mps_plan_tune: fused_fixup must be -1 (automatic), 0 or 1");
+    p->user_fused = fused_fixup >= 0;
+    if (p->user_fused) p->fused = fused_fixup;
     p->user_block = block_threads != 0;
     if (p->user_block) p->block = block_threads;
     const int old_tiles = p->n_tiles;
@@ -314,6 +320,11 @@ static int spmm_typed(mps_plan *p, const TileParams &tp, cudaStream_t st) {
     else rc = launch_tile_gl<T, FULLVEC>(p, tp, st);
     if (rc != MPS_OK) return rc;
     if (prof) { MPS_CUDA(cudaEventRecord(p->prof_ev[2 * p->prof_used + 1], st)); ++p->prof_used; }
+    if (!p->fused && p->n_tiles > 1) {
+        const int warps = p->n_tiles - 1;
+        fixup_warp_kernel<T><<<(warps + 7) / 8, 256, 0, st>>>(tp);
+        MPS_CUDA(cudaGetLastError());
+    }
     if (p->n_long > 0) {
         fixup_long_kernel<T><<<p->n_long, kStrands * 32, 0, st>>>(p->d_tile_xy, tp.rp, p->d_tcarry, p->d_thead, static_cast<T *>(tp.C),
                                                                  p->d_long_list, p->dim);
@@ -335,7 +346,7 @@ extern "C" int mps_spmm(mps_plan *p, const int32_t *d_row_ptr, const int32_t *d_
     TileParams tp;
     tp.rp = d_row_ptr; tp.col = d_col_idx; tp.val = d_val; tp.B = d_B; tp.C = d_C;
     tp.tile_xy = p->d_tile_xy; tp.tcarry = p->d_tcarry; tp.thead = p->d_thead; tp.status = p->d_status;
-    tp.consumer = p->d_consumer; tp.need = p->d_need; tp.cnt = p->d_cnt; tp.long_chain = p->long_chain; tp.very_long = p->very_long;
+    tp.consumer = p->d_consumer; tp.need = p->d_need; tp.cnt = p->d_cnt; tp.long_chain = p->long_chain; tp.very_long = p->very_long; tp.fused = p->fused;
     tp.total = (long long)p->n_rows + 1 + p->nnz;
     tp.n_rows = p->n_rows; tp.nnz = p->nnz; tp.dim = p->dim;
     tp.ipt = p->ipt; tp.nch = p->nch; tp.cpu = p->cpu; tp.n_tiles = p->n_tiles;
@@ -390,7 +401,7 @@ extern "C" int mps_plan_info(const mps_plan *p, int64_t what[16]) {
     what[0] = p->n_chunks; what[1] = p->ipt; what[2] = p->nch; what[3] = p->n_tiles;
     what[4] = p->gl; what[5] = p->vec; what[6] = p->unroll; what[7] = p->smem_bytes;
     what[8] = p->n_long; what[9] = p->tpw_effective;
-    what[10] = 1 + (p->n_long > 0 ? 1 : 0);
+    what[10] = 1 + ((!p->fused && p->n_tiles > 1) ? 1 : 0) + (p->n_long > 0 ? 1 : 0);
     what[11] = p->long_chain; what[12] = p->cpu; what[13] = p->block / p->gl; what[14] = p->block; what[15] = p->very_long;
     return MPS_OK;
 }

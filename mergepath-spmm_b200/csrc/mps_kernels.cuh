@@ -48,6 +48,7 @@ struct TileParams {
     const int *need;      // per tile: contributions its cross-tile fix-up waits for (0 = none)
     int *cnt;             // per (column slab, tile): contributions that have arrived; zero between launches
     int long_chain, very_long;
+    int fused;  // 1: the tile kernel signals and performs the cross-tile fix-up itself; 0: fixup_warp_kernel follows
     long long total;  // N + 1 + nnz
     int n_rows, nnz, dim;
     int ipt, nch, cpu, n_tiles;  // items per chunk, chunks per tile, chunks per unit
@@ -566,9 +567,12 @@ __global__ void __launch_bounds__(BLOCK, kWarpsPerSm * 32 / BLOCK) spmm_tile_ker
         if (active) gmem_put_f32<VEC>(p.tcarry + (size_t)t * dim + coff, sum);
     }
 
-    // ---- cross-tile fix-up without a second kernel: every contribution (a tile's carry, the ending tile's
-    // head) bumps the counter of the tile that ends the row; the block that brings the count to `need`
-    // finds everything in place and sums it, in the fixed order.  No block ever waits for another.
+    // ---- cross-tile fix-up without a second kernel (small problems, where a launch costs more than this):
+    // every contribution (a tile's carry, the ending tile's head) bumps the counter of the tile that ends
+    // the row; the block that brings the count to `need` finds everything in place and sums it, in the
+    // fixed order.  No block ever waits for another.  The fence below has to wait for this thread's
+    // stores to C as well, which is why large problems run fixup_warp_kernel after the tile kernel instead.
+    if (!p.fused) return;
     __threadfence();  // this thread's tcarry / thead stores are visible device-wide before the count moves
     __syncthreads();
     int *s_todo = s_fx;  // the unit boundaries are no longer needed
@@ -633,6 +637,17 @@ __global__ void fixup_plan_kernel(const int2 *__restrict__ xy, const int *__rest
         if (!(a.x >= 1 && a.y > __ldg(rp + a.x - 1))) e = -1;  // the row starts exactly where tile e starts: nothing carried in
     }
     consumer[t] = e;
+}
+
+// Cross-tile fix-up as a kernel of its own (large problems): one warp per tile that ends a carried-in
+// row, same sums in the same order as block_fixup in the tile kernel.
+template <typename T>
+__global__ void fixup_warp_kernel(const TileParams p) {
+    const int t = 1 + (blockIdx.x * blockDim.x + threadIdx.x) / 32;
+    if (t >= p.n_tiles) return;
+    const int n = __ldg(p.need + t);
+    if (n <= 0 || n - 1 > p.very_long) return;
+    block_fixup<T, 32>(p, t, n - 1, 0, p.dim, (int)(threadIdx.x % 32));
 }
 
 // Chains longer than very_long (a row spanning thousands of tiles): one block of kStrands warps per

@@ -14,7 +14,8 @@ struct mps_plan {
     int bulk;
     int long_chain, very_long, n_long, long_capacity;  // chain lengths (tiles): strand order above long_chain, own kernel above very_long
     int device, sm_count;
-    bool user_cpu, user_unroll, user_block;
+    bool user_cpu, user_unroll, user_block, user_fused;
+    int fused;  // cross-tile fix-up inside the tile kernel (small problems) or as a kernel of its own
     bool partitioned;
     int2 *d_tile_xy;
     float *d_tcarry, *d_thead;

@@ -164,7 +164,7 @@ def test_edge_case_graphs(mps, orc, cuda, name):
     val = rng.uniform(-1, 1, len(col)).astype(np.float32)
     for dim in (12, 64, 5):
         B = rng.uniform(-1, 1, (n_cols, dim)).astype(np.float32)
-        for cost, tune in ((1, None), (3, dict(chunks_per_unit=3)), (8, None), (8, dict(chunks_per_unit=1)), (32, dict(unroll=8))):
+        for cost, tune in ((1, None), (3, dict(chunks_per_unit=3)), (8, dict(fused_fixup=0)), (8, dict(chunks_per_unit=1)), (32, dict(unroll=8))):
             got, info = _run(mps, cuda, rp, col, val, B, cost, tune)
             _check(orc, rp, col, val, B, got, info, cost, 1e-5)
 
@@ -175,10 +175,11 @@ def test_long_rows_take_the_strand_order(mps, orc, cuda):
     rp, col = cases.edge_cases()["one_giant_row"]
     rng = np.random.default_rng(5)
     B = rng.uniform(-1, 1, (6000, 64)).astype(np.float32)
-    got, info = _run(mps, cuda, rp, col, None, B, 1, dict(chunks_per_unit=1))
-    assert info["kernels_per_call"] == 1 and info["long_rows"] == 0
-    assert 5000 // (info["chunks_per_tile"] * info["items_per_chunk"]) > info["long_chain"]
-    _check(orc, rp, col, None, B, got, info, 1, 1e-5)
+    for fused in (1, 0):
+        got, info = _run(mps, cuda, rp, col, None, B, 1, dict(chunks_per_unit=1, fused_fixup=fused))
+        assert info["kernels_per_call"] == 2 - fused and info["long_rows"] == 0
+        assert 5000 // (info["chunks_per_tile"] * info["items_per_chunk"]) > info["long_chain"]
+        _check(orc, rp, col, None, B, got, info, 1, 1e-5)
 
 
 def test_rows_spanning_thousands_of_tiles_take_the_second_kernel(mps, orc, cuda):
@@ -187,13 +188,14 @@ def test_rows_spanning_thousands_of_tiles_take_the_second_kernel(mps, orc, cuda)
     val = rng.uniform(-1, 1, len(col)).astype(np.float32)
     B = rng.uniform(-1, 1, (90000, 64)).astype(np.float32)
     got, info = _run(mps, cuda, rp, col, val, B, 1, dict(chunks_per_unit=1))
-    assert info["long_rows"] == 1 and info["kernels_per_call"] == 2
+    assert info["long_rows"] == 1 and info["kernels_per_call"] == 3  # 10,000+ tiles: fix-up kernel of its own, plus the long-row kernel
     assert 80000 // (info["chunks_per_tile"] * info["items_per_chunk"]) > info["very_long"]
     _check(orc, rp, col, val, B, got, info, 1, 1e-5)
 
 
 @pytest.mark.parametrize("tune", [dict(chunks_per_unit=1), dict(chunks_per_unit=3), dict(chunks_per_unit=20, unroll=4),
-                                  dict(unroll=8), dict(bulk_staging=False)])
+                                  dict(unroll=8), dict(bulk_staging=False), dict(block_threads=128), dict(block_threads=256, unroll=4),
+                                  dict(fused_fixup=0), dict(fused_fixup=1), dict(fused_fixup=0, chunks_per_unit=1)])
 def test_tuning_knobs_keep_parity(mps, orc, graphs, cuda, tune):
     rp, col = cases.c1_rmat()
     val = graphs.gcn_values(rp, col)
