@@ -135,7 +135,8 @@ MPS_API int mps_plan_partition(mps_plan *plan, const int32_t *d_row_ptr, void *s
  * val, B and C hold IEEE fp16 and all sums are kept in fp32 until the single rounding of C.
  * Every row of C is written exactly once per call - nothing has to be zeroed and repeated calls
  * do not accumulate (the reference's atomics do, :204,231).  Rows split across chunks are
- * combined in a fixed order, so results are bitwise reproducible. */
+ * combined in a fixed order, so results are bitwise reproducible.  A plan's scratch serves one
+ * multiply at a time: launches that use the same plan must be ordered (same stream, or events). */
 MPS_API int mps_spmm(mps_plan *plan, const int32_t *d_row_ptr, const int32_t *d_col_idx, const void *d_val,
              const void *d_B, void *d_C, void *stream);
 
