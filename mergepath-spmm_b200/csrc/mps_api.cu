@@ -102,6 +102,7 @@ static int pow2_at_least(int v) {
 }
 
 static const int kSmemTargetPer256 = 64 * 1024;   // three tile blocks per SM, which the registers allow anyway
+static const int kVeryLongFused = 8192;       // chain length (tiles) above which even the fused form hands a row to fixup_long_kernel
 static const int kFuseMaxTiles = 2048;       // up to here a second launch costs more than the fence the fused fix-up needs
 static const int kTilesPerSm = 6;            // smaller tiles rather than idle SMs on small problems
 static const int kUnitItems = 272;           // merge items one lane group walks per tile, at most
@@ -140,6 +141,9 @@ static int plan_layout(mps_plan *p) {
         return fail(MPS_ERR_UNSUPPORTED, "tile of %d chunks x %d items needs %d bytes of shared memory", p->nch, p->ipt, p->smem_bytes);
     p->n_tiles = (p->n_chunks + p->nch - 1) / p->nch;
     if (!p->user_fused) p->fused = (long long)p->n_tiles * p->n_col_slabs <= kFuseMaxTiles ? 1 : 0;
+    // a tile block sums chains of any realistic length itself; a lone warp of fixup_warp_kernel should not:
+    // there every strand-order chain goes to fixup_long_kernel (512 threads per row)
+    p->very_long = p->fused ? kVeryLongFused : p->long_chain;
     return MPS_OK;
 }
 
@@ -165,7 +169,7 @@ void mps::plan_init_shape(mps_plan *p, int n_rows, int nnz, int dim, int dtype, 
     p->n_col_slabs = (dim + p->slab_cols - 1) / p->slab_cols;
     p->bulk = 1;
     p->long_chain = 32;
-    p->very_long = 8192;
+    p->very_long = kVeryLongFused;
 }
 
 int mps::plan_finish_layout(mps_plan *p) { return plan_layout(p); }
@@ -181,7 +185,7 @@ static void plan_free_scratch(mps_plan *p) {
 
 static int plan_alloc_scratch(mps_plan *p) {
     plan_free_scratch(p);
-    p->long_capacity = p->n_tiles / p->very_long + 2;
+    p->long_capacity = p->n_tiles / p->long_chain + 2;
     const size_t rows = (size_t)p->n_tiles * p->dim * sizeof(float);
     MPS_CUDA(cudaMalloc(&p->d_tile_xy, sizeof(int2) * ((size_t)p->n_tiles + 1)));
     MPS_CUDA(cudaMalloc(&p->d_tcarry, rows ? rows : 4));

@@ -108,7 +108,7 @@ extern "C" int mps_spmm_noalloc(int32_t n_rows, int32_t nnz, int32_t dim, int dt
     plan.d_cnt = reinterpret_cast<int *>(base + kOffCnt);
     plan.d_tcarry = reinterpret_cast<float *>(base + kOffCarry);
     plan.d_thead = reinterpret_cast<float *>(base + kOffHead);
-    plan.long_capacity = plan.n_tiles / plan.very_long + 2;  // <= kMaxLong because n_tiles <= kMaxTiles
+    plan.long_capacity = plan.n_tiles / plan.long_chain + 2;  // <= kMaxLong because n_tiles <= kMaxTiles
 
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     cudaError_t e = cudaMemsetAsync(plan.d_status, 0, sizeof(int), st);  // left over from the previous call otherwise
