@@ -233,9 +233,6 @@ struct Lane<__half, 1> {
     static __device__ __forceinline__ void store(__half *p, const float (&v)[1]) { *p = __float2half_rn(v[0]); }
 };
 
-__device__ __forceinline__ float to_float(float v) { return v; }
-__device__ __forceinline__ float to_float(__half v) { return __half2float(v); }
-
 template <int VEC>
 __device__ __forceinline__ void smem_put(float *dst, const float (&v)[VEC]) {
     if constexpr (VEC % 4 == 0) {

@@ -1,7 +1,7 @@
 """Generates tests/golden/reference_partition.npz from the REFERENCE's own host functions.
 
 Run in a container that has the reference tree and the harness built from it
-(`make -C oracle REF=/root/reference` -> oracle/_ref/libref_mergepath_f32.so):
+(`make -C oracle REF=<reference tree>` -> oracle/_ref/libref_mergepath_f32.so):
 
     python tests/golden/make_golden.py
 
