@@ -527,17 +527,22 @@ def run_baselines(args):
     # cuSPARSE, row- and column-major dense operands, values = 1
     try:
         lib = _lib("libcusparse_baseline.so")
-        lib.cush_spmm.argtypes = [ci] * 4 + [vp] * 5 + [ci, ci, C.POINTER(C.c_float)]
+        lib.cush_spmm.argtypes = [ci] * 4 + [vp] * 5 + [ci, ci, ci, C.POINTER(C.c_float)]
         ones = torch.ones(nnz, dtype=torch.float32, device=dev)
         Cc = torch.empty((n, dim), dtype=torch.float32, device=dev)
-        for name, colmajor, Bop in (("cusparse_row_major", 0, w["B"]), ("cusparse_col_major", 1, w["B"].t().contiguous())):
+        Bt = w["B"].t().contiguous()
+        runs = [("cusparse_row_major", 0, 0, w["B"], "CUSPARSE_SPMM_ALG_DEFAULT"), ("cusparse_col_major", 1, 0, Bt, "CUSPARSE_SPMM_ALG_DEFAULT"),
+                ("cusparse_row_major_csr_alg2_preprocessed", 0, 2, w["B"], "CUSPARSE_SPMM_CSR_ALG2 + preprocess"),
+                ("cusparse_row_major_csr_alg3_preprocessed", 0, 3, w["B"], "CUSPARSE_SPMM_CSR_ALG3 + preprocess"),
+                ("cusparse_col_major_csr_alg1_preprocessed", 1, 1, Bt, "CUSPARSE_SPMM_CSR_ALG1 + preprocess")]
+        for name, colmajor, alg, Bop, label in runs:
             ms = C.c_float()
             rc = lib.cush_spmm(n, n, nnz, dim, w["rp"].data_ptr(), w["col"].data_ptr(), ones.data_ptr(), Bop.data_ptr(), Cc.data_ptr(),
-                               colmajor, steps, C.byref(ms))
+                               colmajor, alg, steps, C.byref(ms))
             if rc != 0:
                 res[name] = {"unavailable": f"cusparse step {rc} failed"}
             else:
-                rec(name, ms.value, alg="CUSPARSE_SPMM_ALG_DEFAULT")
+                rec(name, ms.value, alg=label)
     except Exception as e:
         res["cusparse"] = {"unavailable": str(e)[:160]}
     print(json.dumps({"impl": "baselines", "metric": "SpMM GFLOP/s (2*nnz*dim/t)", "unit": "GFLOP/s", "n_gpus": 1,
