@@ -79,6 +79,18 @@ MPS_API int mps_csr_save_bin(const char *path, int32_t n_rows, const int32_t *ro
                      const void *val, int val_bytes);
 MPS_API int mps_csr_load_bin(const char *path, mps_csr *out, void **val, int *val_bytes);
 
+/* Replaces the COO -> CSR step of the reference's converters (scripts/npz_to_csr.py:13-19,
+ * scripts/fetch_dataset.py:11-13: scipy coo_matrix(...).tocsr()): duplicate (src, dst) pairs collapse
+ * into one entry and every row's columns come out sorted.  The matrix is square with n_nodes rows
+ * (0 = largest index + 1).  Host arrays in, malloc'ed CSR out (mps_csr_free). */
+MPS_API int mps_coo_to_csr(int32_t n_nodes, int64_t n_edges, const int64_t *src, const int64_t *dst, int n_threads,
+                   mps_csr *out);
+
+/* Replaces scripts/npz_to_csr.py as a whole up to the text writer: reads the members `src_li` and
+ * `dst_li` (one-dimensional little-endian integer arrays) of a `.npz` archive, stored or deflated,
+ * and converts them with mps_coo_to_csr; follow with mps_csr_save for the `.csr` text. */
+MPS_API int mps_npz_to_csr(const char *path, int n_threads, mps_csr *out);
+
 /* ------------------------------------------------------------------ partition ------------ */
 
 /* Chunk count and items per chunk for a cost, exactly the reference's integer arithmetic:

@@ -29,7 +29,7 @@ try:
 except Exception:  # pragma: no cover
     torch = None
 
-__all__ = ["Plan", "MultiGpu", "spmm", "spmm_host", "spmm_noalloc", "partition_device", "schedule_device", "chunk_count", "load_csr", "save_csr",
+__all__ = ["Plan", "MultiGpu", "coo_to_csr", "npz_to_csr", "spmm", "spmm_host", "spmm_noalloc", "partition_device", "schedule_device", "chunk_count", "load_csr", "save_csr",
            "save_csr_bin", "load_csr_bin", "slab_bounds", "slab_rebase", "algorithmic_bytes", "F32", "F16", "MpsError"]
 
 
@@ -249,6 +249,32 @@ def load_csr(path: str, threads: int = 0):
     finally:
         capi.lib().mps_csr_free(C.byref(csr))
     return rp, col
+
+
+def _take_csr(csr):
+    try:
+        rp = np.ctypeslib.as_array(csr.row_ptr, shape=(csr.n_rows + 1,)).copy()
+        col = np.ctypeslib.as_array(csr.col_idx, shape=(csr.nnz,)).copy() if csr.nnz else np.empty(0, np.int32)
+    finally:
+        capi.lib().mps_csr_free(C.byref(csr))
+    return rp, col
+
+
+def coo_to_csr(src, dst, n_nodes: int = 0, threads: int = 0):
+    """Edge list -> (row_ptr, col_idx): duplicates collapsed, columns sorted per row, as scipy's
+    coo_matrix(...).tocsr() leaves them in the reference's converters."""
+    s = np.ascontiguousarray(src, np.int64)
+    d = np.ascontiguousarray(dst, np.int64)
+    csr = capi.Csr()
+    capi.check(capi.lib().mps_coo_to_csr(n_nodes, len(s), s.ctypes.data_as(C.c_void_p), d.ctypes.data_as(C.c_void_p), threads, C.byref(csr)))
+    return _take_csr(csr)
+
+
+def npz_to_csr(path: str, threads: int = 0):
+    """(row_ptr, col_idx) from a `.npz` with members src_li / dst_li (scripts/npz_to_csr.py's input)."""
+    csr = capi.Csr()
+    capi.check(capi.lib().mps_npz_to_csr(path.encode(), threads, C.byref(csr)))
+    return _take_csr(csr)
 
 
 def save_csr(path: str, row_ptr, col_idx) -> None:

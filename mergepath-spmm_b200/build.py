@@ -35,13 +35,13 @@ def _sources(names):
 
 
 def build_library(force: bool = False, verbose: bool = False) -> str:
-    srcs = _sources(["mps_api.cu", "mps_noalloc.cu", "mps_multi.cu", "csr_io.cpp"])
+    srcs = _sources(["mps_api.cu", "mps_noalloc.cu", "mps_multi.cu", "csr_io.cpp", "convert.cpp"])
     deps = srcs + _sources(["mps_kernels.cuh", "mps_internal.h", "mps_plan.h"]) + [os.path.join(ROOT, "include", "mps.h")]
     if not force and _newer(LIB, deps):
         return LIB
     os.makedirs(LIBDIR, exist_ok=True)
     cmd = [_nvcc()] + ARCH + COMMON + ["-shared", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
-                                      "-Xcompiler", "-pthread", "-o", LIB] + srcs + ["-ldl"]
+                                      "-Xcompiler", "-pthread", "-o", LIB] + srcs + ["-ldl", "-lz"]
     if verbose:
         cmd.insert(1, "-Xptxas=-v")
     subprocess.run(cmd, check=True)
@@ -49,15 +49,15 @@ def build_library(force: bool = False, verbose: bool = False) -> str:
 
 
 def build_cli(force: bool = False) -> str:
-    src = os.path.join(CSRC, "bench_main.cpp")
-    if not os.path.exists(src):
-        return ""
+    """MergePathSpMM (the reference's entry point) and npz_to_csr (its converter script), linked to the library."""
     build_library(force)
-    if not force and _newer(CLI, [src, LIB]):
-        return CLI
-    cmd = [_nvcc()] + ARCH + COMMON + ["-Xcompiler", "-pthread", "-o", CLI, src, "-L" + LIBDIR, "-lmps_b200",
-                                      "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN"]
-    subprocess.run(cmd, check=True)
+    for exe, name in ((CLI, "bench_main.cpp"), (os.path.join(LIBDIR, "npz_to_csr"), "npz_to_csr_main.cpp")):
+        src = os.path.join(CSRC, name)
+        if not force and _newer(exe, [src, LIB]):
+            continue
+        cmd = [_nvcc()] + ARCH + COMMON + ["-Xcompiler", "-pthread", "-o", exe, src, "-L" + LIBDIR, "-lmps_b200",
+                                          "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN"]
+        subprocess.run(cmd, check=True)
     return CLI
 
 

@@ -1,0 +1,70 @@
+"""Edge list / .npz -> CSR against scipy's coo_matrix(...).tocsr(), which is what the reference's
+converters run (scripts/npz_to_csr.py:13-19)."""
+import os
+import subprocess
+
+import numpy as np
+import pytest
+import scipy.sparse as sp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _scipy_csr(src, dst, n):
+    m = sp.coo_matrix((np.ones(len(src)), (src, dst)), shape=(n, n)).tocsr()
+    m.sort_indices()
+    return m.indptr.astype(np.int32), m.indices.astype(np.int32)
+
+
+@pytest.mark.parametrize("n,e,seed", [(300, 4000, 0), (5000, 200000, 1), (50, 0, 2), (1, 5, 3), (70000, 300000, 4)])
+def test_coo_to_csr_equals_scipy(mps, n, e, seed):
+    rng = np.random.default_rng(seed)
+    src, dst = rng.integers(0, n, e), rng.integers(0, n, e)
+    for threads in (1, 0):
+        rp, col = mps.coo_to_csr(src, dst, n, threads)
+        want_rp, want_col = _scipy_csr(src, dst, n)
+        assert np.array_equal(rp, want_rp) and np.array_equal(col, want_col)
+
+
+def test_size_is_inferred_and_bad_indices_are_errors(mps):
+    rp, col = mps.coo_to_csr([0, 5, 5, 2], [1, 0, 0, 9])
+    assert len(rp) - 1 == 10 and rp[-1] == 3  # the duplicate (5, 0) collapsed
+    with pytest.raises(mps.MpsError):
+        mps.coo_to_csr([0, -1], [1, 0])
+    with pytest.raises(mps.MpsError):
+        mps.coo_to_csr([0, 7], [1, 0], n_nodes=4)
+
+
+@pytest.mark.parametrize("compressed,dtype", [(False, np.int64), (True, np.int64), (False, np.int32)])
+def test_npz_reader_and_cli(tmp_path, mps, compressed, dtype):
+    rng = np.random.default_rng(5)
+    n, e = 2000, 60000
+    src, dst = rng.integers(0, n, e).astype(dtype), rng.integers(0, n, e).astype(dtype)
+    src[0], dst[0] = n - 1, n - 1  # make sure the inferred size is n
+    p = str(tmp_path / "g.npz")
+    (np.savez_compressed if compressed else np.savez)(p, src_li=src, dst_li=dst, num_nodes=np.int64(n))
+    rp, col = mps.npz_to_csr(p)
+    want_rp, want_col = _scipy_csr(src, dst, n)
+    assert np.array_equal(rp, want_rp) and np.array_equal(col, want_col)
+    from mergepath_spmm_b200 import build
+    build.build_cli()
+    out = str(tmp_path / "g.csr")
+    r = subprocess.run([os.path.join(build.LIBDIR, "npz_to_csr"), "--graph", p, "--output", out], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    rp2, col2 = mps.load_csr(out)
+    assert np.array_equal(rp2, want_rp) and np.array_equal(col2, want_col)
+
+
+def test_npz_errors(tmp_path, mps):
+    p = str(tmp_path / "bad.npz")
+    np.savez(p, src_li=np.arange(5))
+    with pytest.raises(mps.MpsError) as e:
+        mps.npz_to_csr(p)
+    assert "dst_li" in str(e.value)
+    open(p, "wb").write(b"not a zip at all, just some bytes that are long enough........")
+    with pytest.raises(mps.MpsError):
+        mps.npz_to_csr(p)
+    np.savez(p, src_li=np.zeros((3, 2), np.int64), dst_li=np.zeros((3, 2), np.int64))
+    with pytest.raises(mps.MpsError) as e:
+        mps.npz_to_csr(p)
+    assert "one-dimensional" in str(e.value)
