@@ -267,7 +267,10 @@ def run_ours(args):
         try:
             tj = json.load(open(tpath)).get(workload_name(args, 1))
             if tj and world == 1:
+                # DRAM bytes of one launch from the committed ncu capture; beside the algorithmic figure it shows how
+                # much of the gather the L2 serves (the algorithmic count charges every gathered row to HBM)
                 roofline["traffic"] = tj["dram_bytes_per_launch"]
+                roofline["dram_frac"] = round(tj["dram_bytes_per_launch"] / (tile_ms_avg * 1e-3) / 1e9 / peak, 4)
         except Exception:
             pass
 
