@@ -51,3 +51,14 @@ def test_runs_and_checks_on_the_gpu(cli, c1_file, cuda, extra):
         r = subprocess.run([cli, path, dim, "8", "2", "3", "--check"] + extra, capture_output=True, text=True)
         assert r.returncode == 0, r.stdout + r.stderr
         assert "check: 0 elements outside tolerance" in r.stdout and "GFLOP/s" in r.stdout
+
+
+@pytest.mark.gpu
+def test_multi_gpu_with_nccl_gather(cli, c1_file, cuda):
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two devices")
+    path, n, nnz = c1_file
+    r = subprocess.run([cli, path, "32", "8", "1", "3", "--values=gcn", "--gpus=2", "--gather-c", "--check"], capture_output=True, text=True)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "check: 0 elements outside tolerance" in r.stdout and "all-gather of C over NCCL" in r.stdout

@@ -251,6 +251,38 @@ def test_deterministic_and_repeat_safe(mps, graphs, cuda):
     plan.close()
 
 
+@pytest.mark.parametrize("which", ["small_fused", "mid_unfused"])
+def test_launches_can_be_captured_in_a_cuda_graph(mps, graphs, cuda, which):
+    """mps_spmm only enqueues kernels on the given stream, so a loop of multiplies can be captured once and
+    replayed (launch-bound small graphs are where that pays).  Replays must reproduce the eager result."""
+    rp, col = cases.c1_rmat() if which == "small_fused" else graphs.rmat_csr(17, 32, seed=9)
+    val = graphs.gcn_values(rp, col)
+    n, nnz = len(rp) - 1, len(col)
+    d_rp, d_col, d_val = _dev(rp, cuda), _dev(col, cuda), _dev(val, cuda)
+    d_B = _dev(graphs.dense_uniform(n, 32, seed=6), cuda)
+    plan = mps.Plan(n, nnz, 32, mps.F32, 16, device=cuda)
+    plan.partition(d_rp)
+    assert plan.info()["kernels_per_call"] == (1 if which == "small_fused" else 3 if plan.info()["long_rows"] else 2)
+    eager = plan.spmm(d_rp, d_col, d_val, d_B).clone()
+    plan.sync_check()
+    out = torch.zeros_like(eager)
+    side = torch.cuda.Stream(device=cuda)
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            for _ in range(4):
+                plan.spmm(d_rp, d_col, d_val, d_B, out=out, stream=side)
+    torch.cuda.current_stream().wait_stream(side)
+    for _ in range(3):
+        out.fill_(float("nan"))
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(out, eager)
+    plan.sync_check()
+    plan.close()
+
+
 def test_errors_are_codes_not_faults(mps, cuda):
     plan = mps.Plan(10, 20, 16, mps.F32, 8, device=cuda)
     z = torch.zeros(64, dtype=torch.int32, device=cuda)
@@ -371,4 +403,40 @@ def test_full_size_rmat21_properties(mps, graphs, cuda):
     assert torch.equal(c1, again)
     # GCN values make every row an average-like sum with sum_k |a_ik| <= sqrt(deg_i); |b| < 2
     assert (c12 - (c1 + c2)).abs().max().item() < 1e-4
+    plan.close()
+    # configuration 4 on the same graph: fp16 storage, fp32 accumulation, dim 128.  Row lengths up to 2048 are
+    # exact in fp16, longer ones round once; the one-hot product is exact wherever a count is <= 2048.
+    del c1, c2, c12, again, b1, b2
+    dim = 128
+    plan = mps.Plan(n, nnz, dim, mps.F16, 16, device=cuda)
+    plan.partition(rp)
+    c = plan.spmm(rp, col, None, torch.ones((n, dim), dtype=torch.float16, device=cuda))
+    plan.sync_check()
+    assert torch.equal(c, lens.to(torch.float16)[:, None].expand(n, dim))  # one rounding of an exact fp32 sum
+    v16 = val.to(torch.float16)
+    b16 = graphs.dense_normal_f16(n, dim, seed=3, device=cuda)
+    x = plan.spmm(rp, col, v16, b16)
+    y = plan.spmm(rp, col, v16, b16)
+    plan.sync_check()
+    assert torch.equal(x, y) and torch.isfinite(x).all()
+    plan.close()
+
+
+def test_full_size_rmat24_properties(mps, graphs, cuda):
+    """Benchmark configuration 5 on one GPU (2^24 nodes, ~1.04e9 nnz, dim 32): 64-bit offsets, a million tiles,
+    hub rows of millions of non-zeros.  Unit values and B == 1 give every row's length exactly (< 2^24)."""
+    rp, col = graphs.rmat_csr(24, 64, seed=0, device=cuda)
+    n, nnz = rp.numel() - 1, col.numel()
+    assert n == 1 << 24 and 900_000_000 < nnz < (1 << 30) + n
+    torch.cuda.empty_cache()
+    dim = 32
+    plan = mps.Plan(n, nnz, dim, mps.F32, 16, device=cuda)
+    plan.partition(rp)
+    lens = (rp[1:] - rp[:-1]).to(torch.float32)
+    assert lens.max().item() < 2 ** 24
+    c = plan.spmm(rp, col, None, torch.ones((n, dim), dtype=torch.float32, device=cuda))
+    plan.sync_check()
+    assert torch.equal(c, lens[:, None].expand(n, dim))
+    info = plan.info()
+    assert info["n_tiles"] > 500_000 and info["long_rows"] > 0
     plan.close()
