@@ -86,6 +86,12 @@ MPS_API int mps_csr_load_bin(const char *path, mps_csr *out, void **val, int *va
 MPS_API int mps_coo_to_csr(int32_t n_nodes, int64_t n_edges, const int64_t *src, const int64_t *dst, int n_threads,
                    mps_csr *out);
 
+/* The same conversion on the device (no reference counterpart): d_src / d_dst are int64 device arrays,
+ * d_row_ptr receives n_nodes + 1 entries, d_col_idx (capacity n_edges) the columns, *nnz_out the number
+ * kept after duplicates collapse.  Allocates its temporaries, synchronises the stream once. */
+MPS_API int mps_coo_to_csr_device(int32_t n_nodes, int64_t n_edges, const int64_t *d_src, const int64_t *d_dst,
+                          int32_t *d_row_ptr, int32_t *d_col_idx, int32_t *nnz_out, void *stream);
+
 /* Replaces scripts/npz_to_csr.py as a whole up to the text writer: reads the members `src_li` and
  * `dst_li` (one-dimensional little-endian integer arrays) of a `.npz` archive, stored or deflated,
  * and converts them with mps_coo_to_csr; follow with mps_csr_save for the `.csr` text. */

@@ -29,7 +29,7 @@ try:
 except Exception:  # pragma: no cover
     torch = None
 
-__all__ = ["Plan", "MultiGpu", "coo_to_csr", "npz_to_csr", "spmm", "spmm_host", "spmm_noalloc", "partition_device", "schedule_device", "chunk_count", "load_csr", "save_csr",
+__all__ = ["Plan", "MultiGpu", "coo_to_csr", "coo_to_csr_device", "npz_to_csr", "spmm", "spmm_host", "spmm_noalloc", "partition_device", "schedule_device", "chunk_count", "load_csr", "save_csr",
            "save_csr_bin", "load_csr_bin", "slab_bounds", "slab_rebase", "algorithmic_bytes", "F32", "F16", "MpsError"]
 
 
@@ -268,6 +268,19 @@ def coo_to_csr(src, dst, n_nodes: int = 0, threads: int = 0):
     csr = capi.Csr()
     capi.check(capi.lib().mps_coo_to_csr(n_nodes, len(s), s.ctypes.data_as(C.c_void_p), d.ctypes.data_as(C.c_void_p), threads, C.byref(csr)))
     return _take_csr(csr)
+
+
+def coo_to_csr_device(src, dst, n_nodes: int, stream=None):
+    """Edge list (int64 CUDA tensors) -> (row_ptr, col_idx) int32 CUDA tensors, same result as coo_to_csr."""
+    _need_cuda(src, dst)
+    e = src.numel()
+    rp = torch.empty(n_nodes + 1, dtype=torch.int32, device=src.device)
+    col = torch.empty(max(e, 1), dtype=torch.int32, device=src.device)
+    nnz = C.c_int32()
+    with torch.cuda.device(src.device):
+        capi.check(capi.lib().mps_coo_to_csr_device(n_nodes, e, _dev_ptr(src), _dev_ptr(dst), _dev_ptr(rp), _dev_ptr(col), C.byref(nnz),
+                                                    _stream_ptr(stream)))
+    return rp, col[: nnz.value]
 
 
 def npz_to_csr(path: str, threads: int = 0):

@@ -35,16 +35,27 @@ def _sources(names):
 
 
 def build_library(force: bool = False, verbose: bool = False) -> str:
-    srcs = _sources(["mps_api.cu", "mps_noalloc.cu", "mps_multi.cu", "csr_io.cpp", "convert.cpp"])
+    """Compiles every source to an object (in parallel) and links libmps_b200.so."""
+    from concurrent.futures import ThreadPoolExecutor
+    srcs = _sources(["mps_api.cu", "mps_noalloc.cu", "mps_multi.cu", "convert_device.cu", "csr_io.cpp", "convert.cpp"])
     deps = srcs + _sources(["mps_kernels.cuh", "mps_internal.h", "mps_plan.h"]) + [os.path.join(ROOT, "include", "mps.h")]
     if not force and _newer(LIB, deps):
         return LIB
     os.makedirs(LIBDIR, exist_ok=True)
-    cmd = [_nvcc()] + ARCH + COMMON + ["-shared", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
-                                      "-Xcompiler", "-pthread", "-o", LIB] + srcs + ["-ldl", "-lz"]
+    objdir = os.path.join(PKG, "build")
+    os.makedirs(objdir, exist_ok=True)
+    flags = ARCH + COMMON + ["-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "-Xcompiler", "-pthread"]
     if verbose:
-        cmd.insert(1, "-Xptxas=-v")
-    subprocess.run(cmd, check=True)
+        flags = ["-Xptxas=-v"] + flags
+
+    def compile_one(src):
+        obj = os.path.join(objdir, os.path.basename(src) + ".o")
+        subprocess.run([_nvcc()] + flags + ["-c", "-o", obj, src], check=True)
+        return obj
+
+    with ThreadPoolExecutor(max_workers=len(srcs)) as pool:
+        objs = list(pool.map(compile_one, srcs))
+    subprocess.run([_nvcc()] + ARCH + ["-shared", "-o", LIB] + objs + ["-ldl", "-lz"], check=True)
     return LIB
 
 

@@ -68,3 +68,19 @@ def test_npz_errors(tmp_path, mps):
     with pytest.raises(mps.MpsError) as e:
         mps.npz_to_csr(p)
     assert "one-dimensional" in str(e.value)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("n,e,seed", [(300, 4000, 0), (70000, 300000, 4), (1 << 20, 3_000_000, 5), (7, 0, 6)])
+def test_device_conversion_equals_host(mps, cuda, n, e, seed):
+    import torch
+    rng = np.random.default_rng(seed)
+    src, dst = rng.integers(0, n, e), rng.integers(0, n, e)
+    rp, col = mps.coo_to_csr(src, dst, n)
+    d_rp, d_col = mps.coo_to_csr_device(torch.from_numpy(src).to(cuda), torch.from_numpy(dst).to(cuda), n)
+    assert np.array_equal(d_rp.cpu().numpy(), rp) and np.array_equal(d_col.cpu().numpy(), col)
+    if e:
+        bad = torch.from_numpy(src).to(cuda).clone()
+        bad[0] = n
+        with pytest.raises(mps.MpsError):
+            mps.coo_to_csr_device(bad, torch.from_numpy(dst).to(cuda), n)
