@@ -52,7 +52,6 @@ def parse_args():
     ap.add_argument("--unroll", type=int, default=0)
     ap.add_argument("--no-bulk", action="store_true")
     ap.add_argument("--block", type=int, default=0, help="threads per tile block (0 = automatic)")
-    ap.add_argument("--tma", type=int, default=-1, help="gather rows of B with the TMA unit: 1, 0, -1 = automatic")
     ap.add_argument("--fused", type=int, default=-1, help="cross-tile fix-up inside the tile kernel: 1, 0, -1 = automatic")
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--skip-baselines", action="store_true", help="leave out cpu_baseline and reference_gpu (tuning runs)")
@@ -216,8 +215,8 @@ def run_ours(args):
     n_slab, nnz_slab = w["r1"] - w["r0"], w["col"].numel()
     dt = mps.F16 if w["half"] else mps.F32
     plan = mps.Plan(n_slab, nnz_slab, args.dim, dt, cost, args.tpw, device=dev)
-    if args.chunks_per_unit or args.unroll or args.no_bulk or args.block or args.fused >= 0 or args.tma >= 0:
-        plan.tune(args.chunks_per_unit, args.unroll, not args.no_bulk, args.block, args.fused, args.tma)
+    if args.chunks_per_unit or args.unroll or args.no_bulk or args.block or args.fused >= 0:
+        plan.tune(args.chunks_per_unit, args.unroll, not args.no_bulk, args.block, args.fused)
     t0 = time.perf_counter()
     plan.partition(w["rp"])
     torch.cuda.synchronize()

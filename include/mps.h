@@ -137,10 +137,9 @@ MPS_API void mps_plan_destroy(mps_plan *plan);
  * block_threads/lanes_per_chunk units), gather unroll (4 or 8, 0 = automatic), staging through
  * bulk async copies (1, default) or plain loads (0), threads per tile block (64, 128, 256; 0 =
  * automatic: 64), cross-tile fix-up inside the tile kernel (1) or as a kernel of its own (0; -1 =
- * automatic: inside for up to 2048 tiles, where a second launch costs more than it saves), rows of B
- * gathered by the TMA unit into shared memory (1) or by the lanes into registers (0; -1 = automatic). */
+ * automatic: inside for up to 2048 tiles, where a second launch costs more than it saves). */
 MPS_API int mps_plan_tune(mps_plan *plan, int32_t chunks_per_unit, int32_t unroll, int32_t bulk_staging,
-                  int32_t block_threads, int32_t fused_fixup, int32_t tma_gather);
+                  int32_t block_threads, int32_t fused_fixup);
 
 /* Replaces the call of generate_mp_sched and the eleven uploads that follow it
  * (src/MergePathSpMM.cu:192-220): searches the tile boundaries on the device, records for every tile

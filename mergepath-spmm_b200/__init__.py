@@ -103,10 +103,9 @@ class Plan:
 
     __del__ = close
 
-    def tune(self, chunks_per_unit: int = 0, unroll: int = 0, bulk_staging: bool = True, block_threads: int = 0, fused_fixup: int = -1,
-             tma_gather: int = -1):
+    def tune(self, chunks_per_unit: int = 0, unroll: int = 0, bulk_staging: bool = True, block_threads: int = 0, fused_fixup: int = -1):
         with torch.cuda.device(self.device):
-            capi.check(capi.lib().mps_plan_tune(self._h, chunks_per_unit, unroll, int(bulk_staging), block_threads, fused_fixup, tma_gather))
+            capi.check(capi.lib().mps_plan_tune(self._h, chunks_per_unit, unroll, int(bulk_staging), block_threads, fused_fixup))
         return self
 
     def partition(self, row_ptr, stream=None):

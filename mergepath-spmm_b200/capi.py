@@ -64,7 +64,7 @@ def lib():
     L.mps_plan_create.argtypes = [i32, i32, i32, C.c_int, i32, i32, C.POINTER(vp)]
     L.mps_plan_destroy.argtypes = [vp]
     L.mps_plan_destroy.restype = None
-    L.mps_plan_tune.argtypes = [vp, i32, i32, i32, i32, i32, i32]
+    L.mps_plan_tune.argtypes = [vp, i32, i32, i32, i32, i32]
     L.mps_plan_partition.argtypes = [vp, vp, vp]
     L.mps_spmm.argtypes = [vp, vp, vp, vp, vp, vp, vp]
     L.mps_plan_sync_check.argtypes = [vp, vp]

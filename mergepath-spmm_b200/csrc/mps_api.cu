@@ -114,12 +114,9 @@ static int plan_layout(mps_plan *p) {
     if (!p->user_block) p->block = 64;  // small blocks wait least at the three block barriers of a tile; 12 of them fit an SM
     if (p->block < p->gl) p->block = p->gl;
     const int gpc = p->block / p->gl;  // units per tile
+    const int kSmemTarget = kSmemTargetPer256 * p->block / 256, kTileItems = kTileItemsPerThread * p->block;
     if (!p->user_unroll) p->unroll = 8;
     if (p->vec == 1) p->unroll = 4;
-    if (!p->user_tma) p->tma = 0;
-    if (p->vec == 1) p->tma = 0;  // the scalar path gathers single elements
-    const int ring_rows = p->tma ? p->unroll : 0;
-    const int kSmemTarget = kSmemTargetPer256 * p->block / 256 + (p->tma ? ring_rows * kRingStages * gpc * p->slab_cols * elem : 0), kTileItems = kTileItemsPerThread * p->block;
     if (!p->user_cpu) {
         // about kTileItems merge items per tile, fewer when the whole problem would otherwise leave SMs without
         // a tile (at least kTilesPerSm tiles per SM), as long as the windows fit the shared-memory target
@@ -135,11 +132,11 @@ static int plan_layout(mps_plan *p) {
         int cpu = (int)(items / ((long long)gpc * p->ipt));
         if (cpu < 1) cpu = 1;
         if (cpu > 64) cpu = 64;
-        while (cpu > 1 && TileSmem(gpc, gpc * cpu * p->ipt, p->slab_cols, elem, ring_rows).bytes > kSmemTarget) --cpu;
+        while (cpu > 1 && TileSmem(gpc, gpc * cpu * p->ipt, p->slab_cols, elem).bytes > kSmemTarget) --cpu;
         p->cpu = cpu;
     }
     p->nch = gpc * p->cpu;
-    p->smem_bytes = TileSmem(gpc, p->nch * p->ipt, p->slab_cols, elem, ring_rows).bytes;
+    p->smem_bytes = TileSmem(gpc, p->nch * p->ipt, p->slab_cols, elem).bytes;
     if (p->smem_bytes > kSmemLimit)
         return fail(MPS_ERR_UNSUPPORTED, "tile of %d chunks x %d items needs %d bytes of shared memory", p->nch, p->ipt, p->smem_bytes);
     p->n_tiles = (p->n_chunks + p->nch - 1) / p->nch;
@@ -230,7 +227,7 @@ extern "C" void mps_plan_destroy(mps_plan *plan) {
 }
 
 extern "C" int mps_plan_tune(mps_plan *p, int32_t chunks_per_unit, int32_t unroll, int32_t bulk_staging, int32_t block_threads,
-                             int32_t fused_fixup, int32_t tma_gather) {
+                             int32_t fused_fixup) {
     if (!p) return fail(MPS_ERR_ARG, "mps_plan_tune: plan is NULL");
     if (unroll != 0 && unroll != 4 && unroll != 8) return fail(MPS_ERR_ARG, "mps_plan_tune: unroll must be 0, 4 or 8");
     if (chunks_per_unit < 0 || chunks_per_unit > 4096) return fail(MPS_ERR_ARG, "mps_plan_tune: chunks_per_unit out of range");
@@ -238,9 +235,6 @@ extern "C" int mps_plan_tune(mps_plan *p, int32_t chunks_per_unit, int32_t unrol
         return fail(MPS_ERR_ARG, "mps_plan_tune: block_threads must be 0, 64, 128 or 256");
     if (block_threads != 0 && block_threads < p->gl) return fail(MPS_ERR_ARG, "mps_plan_tune: a block must hold at least one group of %d lanes", p->gl);
     if (fused_fixup < -1 || fused_fixup > 1) return fail(MPS_ERR_ARG, "mps_plan_tune: fused_fixup must be -1 (automatic), 0 or 1");
-    if (tma_gather < -1 || tma_gather > 1) return fail(MPS_ERR_ARG, "mps_plan_tune: tma_gather must be -1 (automatic), 0 or 1");
-    p->user_tma = tma_gather >= 0;
-    if (p->user_tma) p->tma = tma_gather;
     p->user_fused = fused_fixup >= 0;
     if (p->user_fused) p->fused = fused_fixup;
     p->user_block = block_threads != 0;
@@ -279,51 +273,17 @@ extern "C" int mps_plan_partition(mps_plan *p, const int32_t *d_row_ptr, void *s
     return MPS_OK;
 }
 
-// Tensor map over B for tile::gather4: 2-D (dim x rows), box = one row of slab_cols elements; the number of
-// rows is not known to the plan (B has as many rows as A has columns), so the bound is left wide open -
-// only rows named by col_idx are ever touched.
-static int build_b_tensor_map(mps_plan *p, const void *d_B) {
-    typedef CUresult (*encode_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
-                                  const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-    static encode_fn encode = nullptr;
-    if (!encode) {
-        void *fn = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        MPS_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q));
-        if (!fn || q != cudaDriverEntryPointSuccess) return fail(MPS_ERR_UNSUPPORTED, "cuTensorMapEncodeTiled is not available in this driver");
-        encode = (encode_fn)fn;
-    }
-    const cuuint64_t elem = p->dtype == MPS_F16 ? 2 : 4;
-    const cuuint64_t dims[2] = {(cuuint64_t)p->dim, (cuuint64_t)1 << 31};
-    const cuuint64_t strides[1] = {(cuuint64_t)p->dim * elem};
-    const cuuint32_t box[2] = {(cuuint32_t)p->slab_cols, 1u}, estr[2] = {1u, 1u};
-    const CUresult r = encode(&p->tmap, p->dtype == MPS_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void *>(d_B),
-                              dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return fail(MPS_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d (dim=%d slab=%d)", (int)r, p->dim, p->slab_cols);
-    p->tmap_b = d_B;
-    return MPS_OK;
-}
-
-template <typename T, int VEC, int GL, int U, int BLOCK, bool TMA>
-static int launch_tile_k(const mps_plan *p, const TileParams &tp, cudaStream_t st) {
-    auto kern = spmm_tile_kernel<T, VEC, GL, U, BLOCK, TMA>;
-    if (p->smem_bytes > 48 * 1024) MPS_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, p->smem_bytes));
-    dim3 grid((unsigned)p->n_tiles, (unsigned)p->n_col_slabs);
-    kern<<<grid, BLOCK, p->smem_bytes, st>>>(tp, p->tmap);
-    MPS_CUDA(cudaGetLastError());
-    return MPS_OK;
-}
-
 template <typename T, int VEC, int GL, int U, int BLOCK>
 static int launch_tile(const mps_plan *p, const TileParams &tp, cudaStream_t st) {
     if constexpr (BLOCK < GL) {
         return fail(MPS_ERR_STATE, "block of %d threads cannot hold a group of %d lanes", BLOCK, GL);
-    } else if constexpr (VEC > 1) {
-        if (p->tma) return launch_tile_k<T, VEC, GL, U, BLOCK, true>(p, tp, st);
-        return launch_tile_k<T, VEC, GL, U, BLOCK, false>(p, tp, st);
     } else {
-        return launch_tile_k<T, VEC, GL, U, BLOCK, false>(p, tp, st);
+        auto kern = spmm_tile_kernel<T, VEC, GL, U, BLOCK>;
+        if (p->smem_bytes > 48 * 1024) MPS_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, p->smem_bytes));
+        dim3 grid((unsigned)p->n_tiles, (unsigned)p->n_col_slabs);
+        kern<<<grid, BLOCK, p->smem_bytes, st>>>(tp);
+        MPS_CUDA(cudaGetLastError());
+        return MPS_OK;
     }
 }
 
@@ -397,8 +357,6 @@ extern "C" int mps_spmm(mps_plan *p, const int32_t *d_row_ptr, const int32_t *d_
     const bool aligned16 = !((uintptr_t)d_row_ptr % 16) && !((uintptr_t)d_col_idx % 16) && !((uintptr_t)d_val % 16);
     tp.bulk = (p->bulk && aligned16) ? 1 : 0;
     cudaStream_t st = (cudaStream_t)stream;
-    if (p->tma && p->tmap_b != d_B)
-        if (int rc = build_b_tensor_map(p, d_B)) return rc;
     if (p->dtype == MPS_F16) return spmm_typed<__half, 8>(p, tp, st);
     return spmm_typed<float, 4>(p, tp, st);
 }
@@ -448,7 +406,7 @@ extern "C" int mps_plan_info(const mps_plan *p, int64_t what[16]) {
     what[4] = p->gl; what[5] = p->vec; what[6] = p->unroll; what[7] = p->smem_bytes;
     what[8] = p->n_long; what[9] = p->tpw_effective;
     what[10] = 1 + ((!p->fused && p->n_tiles > 1) ? 1 : 0) + (p->n_long > 0 ? 1 : 0);
-    what[11] = p->long_chain; what[12] = p->cpu; what[13] = p->block / p->gl; what[14] = p->block; what[15] = p->very_long;  // (tma gather: see mps_plan_tune)
+    what[11] = p->long_chain; what[12] = p->cpu; what[13] = p->block / p->gl; what[14] = p->block; what[15] = p->very_long;
     return MPS_OK;
 }
 

@@ -20,7 +20,6 @@
 //            of C is stored exactly once, sums are bitwise reproducible.
 #pragma once
 
-#include <cuda.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -32,9 +31,8 @@ constexpr int kMaxBlock = 256;       // largest tile block (threads); 64 and 128
 constexpr int kStrands = 16;         // interleaved partial sums of the long-row fix-up
 constexpr int kAlign = 8;            // staging windows start on multiples of 8 elements (>= 16 bytes)
 constexpr int kWaitPolls = 1 << 22;  // bounded mbarrier wait
-constexpr int kRingStages = 4;       // batches of gathered rows in flight per unit (TMA gather path)
 
-enum DeviceStatus : int { kDevOk = 0, kDevStageTimeout = 1, kDevGatherTimeout = 2 };
+enum DeviceStatus : int { kDevOk = 0, kDevStageTimeout = 1 };
 
 struct TileParams {
     const int *rp;
@@ -139,14 +137,6 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t
                  "l"(src), "r"(bytes), "r"(bar), "l"(policy)
                  : "memory");
 }
-// Four rows of a 2-D tensor (B: n_cols x dim), picked by index, land as four consecutive rows of
-// box-width elements in shared memory; x is the first column (x * element size a multiple of 16 bytes).
-// One thread issues it; completion is counted in bytes on the mbarrier.
-__device__ __forceinline__ void tma_gather4(uint32_t dst, const CUtensorMap *map, int x, int r0, int r1, int r2, int r3, uint32_t bar) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];" ::"r"(dst),
-                 "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(r0), "r"(r1), "r"(r2), "r"(r3)
-                 : "memory");
-}
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
@@ -193,7 +183,6 @@ struct Lane<float, 4> {
     static __device__ __forceinline__ scalar value(float v) { return v; }
     static __device__ __forceinline__ scalar one() { return 1.0f; }
     static __device__ __forceinline__ raw load(const float *p) { return __ldg(reinterpret_cast<const float4 *>(p)); }
-    static __device__ __forceinline__ raw from_smem(const float *p) { return *reinterpret_cast<const float4 *>(p); }
     static __device__ __forceinline__ void fma(float (&acc)[4], float a, const raw &b) {
         acc[0] = fmaf(a, b.x, acc[0]); acc[1] = fmaf(a, b.y, acc[1]);
         acc[2] = fmaf(a, b.z, acc[2]); acc[3] = fmaf(a, b.w, acc[3]);
@@ -209,7 +198,6 @@ struct Lane<float, 1> {
     static __device__ __forceinline__ scalar value(float v) { return v; }
     static __device__ __forceinline__ scalar one() { return 1.0f; }
     static __device__ __forceinline__ raw load(const float *p) { return __ldg(p); }
-    static __device__ __forceinline__ raw from_smem(const float *p) { return *p; }
     static __device__ __forceinline__ void fma(float (&acc)[1], float a, const raw &b) { acc[0] = fmaf(a, b, acc[0]); }
     static __device__ __forceinline__ void store(float *p, const float (&v)[1]) { __stcs(p, v[0]); }
 };
@@ -220,7 +208,6 @@ struct Lane<__half, 8> {
     static __device__ __forceinline__ scalar value(__half v) { return __half_as_ushort(v); }
     static __device__ __forceinline__ scalar one() { return (unsigned short)0x3C00; }
     static __device__ __forceinline__ raw load(const __half *p) { return __ldg(reinterpret_cast<const uint4 *>(p)); }
-    static __device__ __forceinline__ raw from_smem(const __half *p) { return *reinterpret_cast<const uint4 *>(p); }
     static __device__ __forceinline__ void fma(float (&acc)[8], scalar a, const raw &b) {
         fma_f32_f16x2(acc[0], acc[1], a, b.x);
         fma_f32_f16x2(acc[2], acc[3], a, b.y);
@@ -242,7 +229,6 @@ struct Lane<__half, 1> {
     static __device__ __forceinline__ scalar value(__half v) { return __half2float(v); }
     static __device__ __forceinline__ scalar one() { return 1.0f; }
     static __device__ __forceinline__ raw load(const __half *p) { return __ldg(p); }
-    static __device__ __forceinline__ raw from_smem(const __half *p) { return *p; }
     static __device__ __forceinline__ void fma(float (&acc)[1], float a, const raw &b) { acc[0] = fmaf(a, __half2float(b), acc[0]); }
     static __device__ __forceinline__ void store(__half *p, const float (&v)[1]) { *p = __float2half_rn(v[0]); }
 };
@@ -283,10 +269,9 @@ __device__ __forceinline__ void gmem_put_f32(float *dst, const float (&v)[VEC]) 
 
 // Shared-memory layout of one tile block, shared by host (size) and device (offsets).
 struct TileSmem {
-    int off_fx, off_fy, off_rp, off_col, off_val, off_carry, off_head, off_full, off_ring, bytes;
+    int off_fx, off_fy, off_rp, off_col, off_val, off_carry, off_head, bytes;
     __host__ __device__ static int up16(int v) { return (v + 15) & ~15; }
-    // ring_rows > 0: the TMA gather path keeps, per unit, kRingStages batches of ring_rows gathered rows
-    __host__ __device__ TileSmem(int n_units, int tile_items, int slab_cols, int elem_bytes, int ring_rows = 0) {
+    __host__ __device__ TileSmem(int n_units, int tile_items, int slab_cols, int elem_bytes) {
         const int win = tile_items + 2 * kAlign + 8;  // window plus alignment slack on both sides
         int o = 16;                                   // mbarrier
         off_fx = o; o = up16(o + 4 * (n_units + 1));
@@ -296,9 +281,6 @@ struct TileSmem {
         off_val = o; o = up16(o + elem_bytes * win);
         off_carry = o; o = up16(o + 4 * n_units * slab_cols);
         off_head = o; o = up16(o + 4 * n_units * slab_cols);
-        off_full = o; o = up16(o + (ring_rows ? 8 * n_units * kRingStages : 0));
-        o = (o + 127) & ~127;
-        off_ring = o; o += ring_rows * kRingStages * n_units * slab_cols * elem_bytes;
         bytes = o;
     }
 };
@@ -381,16 +363,13 @@ __device__ __forceinline__ void block_fixup(const TileParams &p, int e, int chai
 // ---------------------------------------------------------------------------------------------
 // One block = one tile = GPC units; unit u = `cpu` consecutive chunks walked by one group of GL
 // lanes with the accumulator kept in registers across the chunk boundaries inside the unit.
-// TMA = true: the rows of B are gathered by the TMA unit (tile::gather4, four rows per instruction issued by
-// the group's first lane) into a per-unit ring of kRingStages batches of U rows in shared memory and folded
-// from there, so that no register holds a row in flight; TMA = false: the lanes gather with 128-bit loads.
-template <typename T, int VEC, int GL, int U, int BLOCK, bool TMA>
-__global__ void __launch_bounds__(BLOCK, kWarpsPerSm * 32 / BLOCK) spmm_tile_kernel(const TileParams p, const __grid_constant__ CUtensorMap tmap) {
+template <typename T, int VEC, int GL, int U, int BLOCK>
+__global__ void __launch_bounds__(BLOCK, kWarpsPerSm * 32 / BLOCK) spmm_tile_kernel(const TileParams p) {
     constexpr int kBlock = BLOCK;
     constexpr int GPC = kBlock / GL;   // units (lane groups) per block
     constexpr int SLAB = GL * VEC;     // columns covered by one block
     extern __shared__ __align__(128) unsigned char smem[];
-    const TileSmem L(GPC, p.nch * p.ipt, SLAB, (int)sizeof(T), TMA ? U : 0);
+    const TileSmem L(GPC, p.nch * p.ipt, SLAB, (int)sizeof(T));
     uint64_t *s_bar = reinterpret_cast<uint64_t *>(smem);
     int *s_fx = reinterpret_cast<int *>(smem + L.off_fx);
     int *s_fy = reinterpret_cast<int *>(smem + L.off_fy);
@@ -417,10 +396,6 @@ __global__ void __launch_bounds__(BLOCK, kWarpsPerSm * 32 / BLOCK) spmm_tile_ker
     const int rp_base = rp_first & ~(kAlign - 1);
     const int y_base = Y0 & ~(kAlign - 1);
 
-    if constexpr (TMA) {  // one "full" barrier per (unit, ring stage); made visible by the block barriers below
-        if (tid == 0)
-            for (int i = 0; i < GPC * kRingStages; ++i) mbar_init(smem_u32(smem + L.off_full) + 8u * i, 1);
-    }
     // ---- stage the tile's windows ----
     if (p.bulk) {
         const uint32_t bar = smem_u32(s_bar);
@@ -509,106 +484,48 @@ __global__ void __launch_bounds__(BLOCK, kWarpsPerSm * 32 / BLOCK) spmm_tile_ker
             next_mark = x < x1 ? w_rp[x] : 0x7fffffff;
         };
 
-        if constexpr (TMA) {
-            // ring of kRingStages batches of U rows; lane 0 of the group is the producer, the whole group folds
-            const uint32_t full0 = smem_u32(smem + L.off_full) + 8u * (uint32_t)(g * kRingStages);
-            T *ring = reinterpret_cast<T *>(smem + L.off_ring) + (size_t)g * kRingStages * U * SLAB;
-            const uint32_t ring0 = smem_u32(ring);
-            constexpr uint32_t kStageBytes = (uint32_t)(U * SLAB * sizeof(T));
-            const unsigned gmask = GL >= 32 ? 0xffffffffu : (((1u << GL) - 1u) << (((unsigned)tid % 32u) / GL * GL));
-            const int n_batches = (y1 - y0 + U - 1) / U;
-            const int xcol = (int)blockIdx.y * SLAB;
-            auto issue = [&](int j) {  // batch j -> stage j % kRingStages; rows past the unit's end repeat its last one
-                const int st = j % kRingStages, kb = y0 + j * U;
-                const uint32_t bar = full0 + 8u * (uint32_t)st;
-                mbar_arrive_expect(bar, kStageBytes);
+        int k = y0;
+        // full batches: U gathers in flight, no bound checks
+        for (; k + U <= y1; k += U) {
+            typename Lane<T, VEC>::raw b[U];
+            typename Lane<T, VEC>::scalar a[U];
 #pragma unroll
-                for (int q = 0; q < U; q += 4) {
-                    int r[4];
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) r[i] = w_col[(kb + q + i < y1) ? kb + q + i : y1 - 1];
-                    tma_gather4(ring0 + (uint32_t)st * kStageBytes + (uint32_t)(q * SLAB * sizeof(T)), &tmap, xcol, r[0], r[1], r[2], r[3], bar);
-                }
-            };
-            if (l == 0)
-                for (int j = 0; j < kRingStages && j < n_batches; ++j) issue(j);
-            bool alive = true;
-            for (int j = 0; j < n_batches && alive; ++j) {
-                const int st = j % kRingStages, kb = y0 + j * U;
-                bool landed = mbar_wait_bounded(full0 + 8u * (uint32_t)st, (uint32_t)(j / kRingStages) & 1u);
-                if (!landed) landed = mbar_wait_bounded(full0 + 8u * (uint32_t)st, (uint32_t)(j / kRingStages) & 1u);  // one more bounded chance
-                if (!__all_sync(gmask, landed)) {  // the same verdict for every lane of the group
-                    atomicExch(p.status, (int)kDevGatherTimeout);
-                    alive = false;  // give up on this unit; the block still reaches its barriers
-                }
-                const T *rows = ring + (size_t)st * U * SLAB + l * VEC;
-                const int cnt = y1 - kb < U ? y1 - kb : U;
-                while (alive && next_mark <= kb) end_row();
-                if (alive && cnt == U && next_mark >= kb + U) {  // full batch, no row ends inside it
-                    if (active) {
-#pragma unroll
-                        for (int u = 0; u < U; ++u)
-                            Lane<T, VEC>::fma(acc, has_val ? Lane<T, VEC>::value(w_val[kb + u]) : Lane<T, VEC>::one(),
-                                              Lane<T, VEC>::from_smem(rows + u * SLAB));
-                    }
-                } else if (alive) {
-#pragma unroll
-                    for (int u = 0; u < U; ++u) {
-                        if (u < cnt) {
-                            while (next_mark <= kb + u) end_row();
-                            if (active)
-                                Lane<T, VEC>::fma(acc, has_val ? Lane<T, VEC>::value(w_val[kb + u]) : Lane<T, VEC>::one(),
-                                                  Lane<T, VEC>::from_smem(rows + u * SLAB));
-                        }
-                    }
-                }
-                __syncwarp(gmask);  // every lane of the group has read the stage before it is refilled
-                if (l == 0 && alive && j + kRingStages < n_batches) issue(j + kRingStages);
+            for (int u = 0; u < U; ++u) {
+                const unsigned ci = (unsigned)w_col[k + u];
+                a[u] = has_val ? Lane<T, VEC>::value(w_val[k + u]) : Lane<T, VEC>::one();
+                if (active) b[u] = Lane<T, VEC>::load(Bl + (size_t)ci * dim);
             }
-        } else {
-            int k = y0;
-            // full batches: U gathers in flight, no bound checks
-            for (; k + U <= y1; k += U) {
-                typename Lane<T, VEC>::raw b[U];
-                typename Lane<T, VEC>::scalar a[U];
-    #pragma unroll
+            while (next_mark <= k) end_row();
+            if (next_mark >= k + U) {  // no row ends inside the batch
+                if (active) {
+#pragma unroll
+                    for (int u = 0; u < U; ++u) Lane<T, VEC>::fma(acc, a[u], b[u]);
+                }
+            } else {
+#pragma unroll
                 for (int u = 0; u < U; ++u) {
+                    while (next_mark <= k + u) end_row();
+                    if (active) Lane<T, VEC>::fma(acc, a[u], b[u]);
+                }
+            }
+        }
+        // remainder: fewer than U non-zeros
+        if (k < y1) {
+            typename Lane<T, VEC>::raw b[U];
+            typename Lane<T, VEC>::scalar a[U];
+#pragma unroll
+            for (int u = 0; u < U - 1; ++u) {
+                if (k + u < y1) {
                     const unsigned ci = (unsigned)w_col[k + u];
                     a[u] = has_val ? Lane<T, VEC>::value(w_val[k + u]) : Lane<T, VEC>::one();
                     if (active) b[u] = Lane<T, VEC>::load(Bl + (size_t)ci * dim);
                 }
-                while (next_mark <= k) end_row();
-                if (next_mark >= k + U) {  // no row ends inside the batch
-                    if (active) {
-    #pragma unroll
-                        for (int u = 0; u < U; ++u) Lane<T, VEC>::fma(acc, a[u], b[u]);
-                    }
-                } else {
-    #pragma unroll
-                    for (int u = 0; u < U; ++u) {
-                        while (next_mark <= k + u) end_row();
-                        if (active) Lane<T, VEC>::fma(acc, a[u], b[u]);
-                    }
-                }
             }
-            // remainder: fewer than U non-zeros
-            if (k < y1) {
-                typename Lane<T, VEC>::raw b[U];
-                typename Lane<T, VEC>::scalar a[U];
-    #pragma unroll
-                for (int u = 0; u < U - 1; ++u) {
-                    if (k + u < y1) {
-                        const unsigned ci = (unsigned)w_col[k + u];
-                        a[u] = has_val ? Lane<T, VEC>::value(w_val[k + u]) : Lane<T, VEC>::one();
-                        if (active) b[u] = Lane<T, VEC>::load(Bl + (size_t)ci * dim);
-                    }
-                }
-    #pragma unroll
-                for (int u = 0; u < U - 1; ++u) {
-                    if (k + u < y1) {
-                        while (next_mark <= k + u) end_row();
-                        if (active) Lane<T, VEC>::fma(acc, a[u], b[u]);
-                    }
+#pragma unroll
+            for (int u = 0; u < U - 1; ++u) {
+                if (k + u < y1) {
+                    while (next_mark <= k + u) end_row();
+                    if (active) Lane<T, VEC>::fma(acc, a[u], b[u]);
                 }
             }
         }

@@ -1,7 +1,6 @@
 // The plan object behind the opaque mps_plan of the public header.  Internal: shared by the .cu
 // translation units of libmps_b200.so only.
 #pragma once
-#include <cuda.h>
 #include <cuda_runtime.h>
 
 static const int kProfSlots = 256;  // event pairs kept between two profile reads
@@ -16,8 +15,6 @@ struct mps_plan {
     int long_chain, very_long, n_long, long_capacity;  // chain lengths (tiles): strand order above long_chain, own kernel above very_long
     int device, sm_count;
     bool user_cpu, user_unroll, user_block, user_fused;
-    bool user_tma;
-    int tma;    // rows of B gathered by the TMA unit into shared memory (1) or by the lanes into registers (0)
     int fused;  // cross-tile fix-up inside the tile kernel (small problems) or as a kernel of its own
     bool partitioned;
     int2 *d_tile_xy;
@@ -27,8 +24,6 @@ struct mps_plan {
     bool profiling;
     int prof_used;
     cudaEvent_t prof_ev[2 * kProfSlots];
-    CUtensorMap tmap;          // over B, for the TMA gather path; rebuilt when B moves
-    const void *tmap_b;
 };
 
 namespace mps {
