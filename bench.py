@@ -468,9 +468,9 @@ def run_baselines(args):
 
     steps = max(min(args.steps, 10), 1)
     # this library, unit values and GCN values
-    plan = mps.Plan(n, nnz, dim, mps.F32, args.cost or DEFAULT_COST, args.tpw, device=dev)
+    plan = mps.Plan(n, nnz, dim, mps.F16 if w["half"] else mps.F32, args.cost or DEFAULT_COST, args.tpw, device=dev)
     plan.partition(w["rp"])
-    Cm = torch.empty((n, dim), dtype=torch.float32, device=dev)
+    Cm = torch.empty((n, dim), dtype=w["B"].dtype, device=dev)
     for name, val in (("this_library_unit_values", None), ("this_library_gcn_values", w["val"])):
         for _ in range(3):
             plan.spmm(w["rp"], w["col"], val, w["B"], out=Cm)
@@ -484,6 +484,11 @@ def run_baselines(args):
             rec(f"reference_mergepath_cost{cost}", r["ms_per_step"], kernel=r["kernel"])
         except Exception as e:
             res[f"reference_mergepath_cost{cost}"] = {"unavailable": str(e)[:160]}
+    if w["half"]:  # the other baselines are fp32 programs; the fp16 table has this library and MergePathSpMM_fp16 only
+        print(json.dumps({"impl": "baselines", "metric": "SpMM GFLOP/s (2*nnz*dim/t)", "unit": "GFLOP/s", "n_gpus": 1,
+                          "config": {"workload": workload_name(args, 1), "nodes": n, "nnz": nnz, "dim": dim, "values": "unit unless named",
+                                     "reference": "MergePathSpMM_fp16 kernels (fp16 accumulation)"}, "results": res}), flush=True)
+        return
     deg = torch.ones(n + 1, dtype=torch.int32, device=dev)
     B1 = torch.zeros((n + 1, dim), dtype=torch.float32, device=dev)
     B1[:n] = w["B"]
