@@ -202,13 +202,18 @@ extern "C" int mps_csr_load(const char *path, int n_threads, mps_csr *out) {
 namespace {
 // Formats cells [b,e) of a, each followed by ','.
 void format_cells(const int32_t *a, size_t b, size_t e, std::string &s) {
-    s.clear();
-    s.reserve((e - b) * 8);
-    char tmp[16];
+    s.resize((e - b) * 12);  // "-2147483648," is the longest cell
+    char *out = &s[0];
     for (size_t i = b; i < e; ++i) {
-        int n = snprintf(tmp, sizeof tmp, "%d,", a[i]);
-        s.append(tmp, (size_t)n);
+        int64_t v = a[i];
+        if (v < 0) { *out++ = '-'; v = -v; }
+        char digits[12];
+        int n = 0;
+        do { digits[n++] = (char)('0' + v % 10); v /= 10; } while (v);
+        while (n) *out++ = digits[--n];
+        *out++ = ',';
     }
+    s.resize((size_t)(out - &s[0]));
 }
 int write_line(FILE *f, const int32_t *a, size_t n) {
     const size_t block = 1 << 20;
