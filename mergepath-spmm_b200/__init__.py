@@ -123,6 +123,17 @@ class Plan:
                                            _stream_ptr(stream)))
         return out
 
+    def spmm_scaled(self, row_ptr, col_idx, row_scale, col_scale, B, out=None, stream=None):
+        """C[i] = row_scale[i] * sum_k col_scale[col[k]] * B[col[k]] (fp32): A's values are the outer product of two
+        scale vectors, e.g. GCN normalisation, and are never stored."""
+        _need_cuda(row_ptr, col_idx, row_scale, col_scale, B, out)
+        if out is None:
+            out = torch.empty((self.n_rows, self.dim), dtype=B.dtype, device=B.device)
+        with torch.cuda.device(self.device):
+            capi.check(capi.lib().mps_spmm_scaled(self._h, _dev_ptr(row_ptr), _dev_ptr(col_idx), _dev_ptr(row_scale), _dev_ptr(col_scale),
+                                                  _dev_ptr(B), _dev_ptr(out), _stream_ptr(stream)))
+        return out
+
     def sync_check(self, stream=None):
         with torch.cuda.device(self.device):
             capi.check(capi.lib().mps_plan_sync_check(self._h, _stream_ptr(stream)))

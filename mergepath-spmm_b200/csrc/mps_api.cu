@@ -331,14 +331,14 @@ static int spmm_typed(mps_plan *p, const TileParams &tp, cudaStream_t st) {
     }
     if (p->n_long > 0) {
         fixup_long_kernel<T><<<p->n_long, kStrands * 32, 0, st>>>(p->d_tile_xy, tp.rp, p->d_tcarry, p->d_thead, static_cast<T *>(tp.C),
-                                                                 p->d_long_list, p->dim);
+                                                                 p->d_long_list, p->dim, tp.row_scale);
         MPS_CUDA(cudaGetLastError());
     }
     return MPS_OK;
 }
 
-extern "C" int mps_spmm(mps_plan *p, const int32_t *d_row_ptr, const int32_t *d_col_idx, const void *d_val, const void *d_B,
-                        void *d_C, void *stream) {
+static int spmm_launch(mps_plan *p, const int32_t *d_row_ptr, const int32_t *d_col_idx, const void *d_val, const float *d_row_scale,
+                       const float *d_col_scale, const void *d_B, void *d_C, void *stream) {
     if (!p || !d_row_ptr || !d_B || !d_C || (!d_col_idx && p->nnz > 0)) return fail(MPS_ERR_ARG, "mps_spmm: NULL argument");
     if (!p->partitioned) return fail(MPS_ERR_STATE, "mps_spmm: call mps_plan_partition first");
     const uintptr_t elem = p->dtype == MPS_F16 ? 2 : 4;
@@ -349,6 +349,7 @@ extern "C" int mps_spmm(mps_plan *p, const int32_t *d_row_ptr, const int32_t *d_
         return fail(MPS_ERR_ALIGN, "mps_spmm: row_ptr/col_idx/val not aligned to their element size");
     TileParams tp;
     tp.rp = d_row_ptr; tp.col = d_col_idx; tp.val = d_val; tp.B = d_B; tp.C = d_C;
+    tp.row_scale = d_row_scale; tp.col_scale = d_col_scale;
     tp.tile_xy = p->d_tile_xy; tp.tcarry = p->d_tcarry; tp.thead = p->d_thead; tp.status = p->d_status;
     tp.consumer = p->d_consumer; tp.need = p->d_need; tp.cnt = p->d_cnt; tp.long_chain = p->long_chain; tp.very_long = p->very_long; tp.fused = p->fused;
     tp.total = (long long)p->n_rows + 1 + p->nnz;
@@ -359,6 +360,19 @@ extern "C" int mps_spmm(mps_plan *p, const int32_t *d_row_ptr, const int32_t *d_
     cudaStream_t st = (cudaStream_t)stream;
     if (p->dtype == MPS_F16) return spmm_typed<__half, 8>(p, tp, st);
     return spmm_typed<float, 4>(p, tp, st);
+}
+
+extern "C" int mps_spmm(mps_plan *p, const int32_t *d_row_ptr, const int32_t *d_col_idx, const void *d_val, const void *d_B,
+                        void *d_C, void *stream) {
+    return spmm_launch(p, d_row_ptr, d_col_idx, d_val, nullptr, nullptr, d_B, d_C, stream);
+}
+
+extern "C" int mps_spmm_scaled(mps_plan *p, const int32_t *d_row_ptr, const int32_t *d_col_idx, const float *d_row_scale,
+                               const float *d_col_scale, const void *d_B, void *d_C, void *stream) {
+    if (!d_row_scale || !d_col_scale) return fail(MPS_ERR_ARG, "mps_spmm_scaled: NULL scale array");
+    if (p && p->dtype != MPS_F32) return fail(MPS_ERR_UNSUPPORTED, "mps_spmm_scaled: fp32 plans only");
+    if (((uintptr_t)d_row_scale % 4) || ((uintptr_t)d_col_scale % 4)) return fail(MPS_ERR_ALIGN, "mps_spmm_scaled: scale arrays must be 4-byte aligned");
+    return spmm_launch(p, d_row_ptr, d_col_idx, nullptr, d_row_scale, d_col_scale, d_B, d_C, stream);
 }
 
 extern "C" int mps_plan_sync_check(mps_plan *p, void *stream) {

@@ -38,6 +38,8 @@ struct TileParams {
     const int *rp;
     const int *col;
     const void *val;  // nullptr: all ones
+    const float *row_scale;  // with col_scale (fp32 plans): value of non-zero (i, j) = row_scale[i] * col_scale[j], the row
+    const float *col_scale;  // factor applied once, to the finished row; both nullptr otherwise
     const void *B;
     void *C;
     const int2 *tile_xy;  // n_tiles + 1 boundary coordinates, reference convention
@@ -181,6 +183,7 @@ struct Lane<float, 4> {
     typedef float4 raw;
     typedef float scalar;
     static __device__ __forceinline__ scalar value(float v) { return v; }
+    static __device__ __forceinline__ scalar from_float(float v) { return v; }
     static __device__ __forceinline__ scalar one() { return 1.0f; }
     static __device__ __forceinline__ raw load(const float *p) { return __ldg(reinterpret_cast<const float4 *>(p)); }
     static __device__ __forceinline__ void fma(float (&acc)[4], float a, const raw &b) {
@@ -196,6 +199,7 @@ struct Lane<float, 1> {
     typedef float raw;
     typedef float scalar;
     static __device__ __forceinline__ scalar value(float v) { return v; }
+    static __device__ __forceinline__ scalar from_float(float v) { return v; }
     static __device__ __forceinline__ scalar one() { return 1.0f; }
     static __device__ __forceinline__ raw load(const float *p) { return __ldg(p); }
     static __device__ __forceinline__ void fma(float (&acc)[1], float a, const raw &b) { acc[0] = fmaf(a, b, acc[0]); }
@@ -206,6 +210,7 @@ struct Lane<__half, 8> {
     typedef uint4 raw;
     typedef unsigned short scalar;
     static __device__ __forceinline__ scalar value(__half v) { return __half_as_ushort(v); }
+    static __device__ __forceinline__ scalar from_float(float) { return (unsigned short)0x3C00; }  // scaled products are fp32-only
     static __device__ __forceinline__ scalar one() { return (unsigned short)0x3C00; }
     static __device__ __forceinline__ raw load(const __half *p) { return __ldg(reinterpret_cast<const uint4 *>(p)); }
     static __device__ __forceinline__ void fma(float (&acc)[8], scalar a, const raw &b) {
@@ -227,6 +232,7 @@ struct Lane<__half, 1> {
     typedef __half raw;
     typedef float scalar;
     static __device__ __forceinline__ scalar value(__half v) { return __half2float(v); }
+    static __device__ __forceinline__ scalar from_float(float v) { return v; }
     static __device__ __forceinline__ scalar one() { return 1.0f; }
     static __device__ __forceinline__ raw load(const __half *p) { return __ldg(p); }
     static __device__ __forceinline__ void fma(float (&acc)[1], float a, const raw &b) { acc[0] = fmaf(a, __half2float(b), acc[0]); }
@@ -255,6 +261,11 @@ __device__ __forceinline__ void vec_add(float (&acc)[VEC], const float *src) {
 #pragma unroll
         for (int i = 0; i < VEC; ++i) acc[i] += src[i];
     }
+}
+template <int VEC>
+__device__ __forceinline__ void scale_by(float (&v)[VEC], float f) {
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) v[i] *= f;
 }
 template <int VEC>
 __device__ __forceinline__ void gmem_put_f32(float *dst, const float (&v)[VEC]) {
@@ -354,6 +365,7 @@ __device__ __forceinline__ void block_fixup(const TileParams &p, int e, int chai
             for (int g = 0; g < kStrands; ++g) sum += sg[g];
         }
         sum += __ldcg(p.thead + (size_t)e * dim + j);
+        if (p.row_scale) sum *= __ldg(p.row_scale + row);
         store_c(static_cast<T *>(p.C) + (size_t)row * dim + j, sum);
     }
 }
@@ -385,6 +397,7 @@ __global__ void __launch_bounds__(BLOCK, kWarpsPerSm * 32 / BLOCK) spmm_tile_ker
     const int coff = blockIdx.y * SLAB + l * VEC;  // first column of this lane
     const bool active = coff < p.dim;
     const bool has_val = p.val != nullptr;
+    const float *__restrict__ cs = p.col_scale, *__restrict__ rs = p.row_scale;
     const T *__restrict__ Bl = static_cast<const T *>(p.B) + coff;  // this lane's columns of B
     T *__restrict__ Cl = static_cast<T *>(p.C) + coff;
     const unsigned dim = (unsigned)p.dim;
@@ -475,6 +488,7 @@ __global__ void __launch_bounds__(BLOCK, kWarpsPerSm * 32 / BLOCK) spmm_tile_ker
                     smem_put<VEC>(s_head + g * SLAB + l * VEC, acc);
                     head_pending = false;
                 } else if (active) {
+                    if (rs) scale_by<VEC>(acc, __ldg(rs + x - 1));
                     Lane<T, VEC>::store(Cl + (size_t)(x - 1) * dim, acc);
                 }
 #pragma unroll
@@ -492,7 +506,7 @@ __global__ void __launch_bounds__(BLOCK, kWarpsPerSm * 32 / BLOCK) spmm_tile_ker
 #pragma unroll
             for (int u = 0; u < U; ++u) {
                 const unsigned ci = (unsigned)w_col[k + u];
-                a[u] = has_val ? Lane<T, VEC>::value(w_val[k + u]) : Lane<T, VEC>::one();
+                a[u] = cs ? Lane<T, VEC>::from_float(__ldg(cs + ci)) : has_val ? Lane<T, VEC>::value(w_val[k + u]) : Lane<T, VEC>::one();
                 if (active) b[u] = Lane<T, VEC>::load(Bl + (size_t)ci * dim);
             }
             while (next_mark <= k) end_row();
@@ -517,7 +531,7 @@ __global__ void __launch_bounds__(BLOCK, kWarpsPerSm * 32 / BLOCK) spmm_tile_ker
             for (int u = 0; u < U - 1; ++u) {
                 if (k + u < y1) {
                     const unsigned ci = (unsigned)w_col[k + u];
-                    a[u] = has_val ? Lane<T, VEC>::value(w_val[k + u]) : Lane<T, VEC>::one();
+                    a[u] = cs ? Lane<T, VEC>::from_float(__ldg(cs + ci)) : has_val ? Lane<T, VEC>::value(w_val[k + u]) : Lane<T, VEC>::one();
                     if (active) b[u] = Lane<T, VEC>::load(Bl + (size_t)ci * dim);
                 }
             }
@@ -548,7 +562,10 @@ __global__ void __launch_bounds__(BLOCK, kWarpsPerSm * 32 / BLOCK) spmm_tile_ker
             vec_add<VEC>(sum, s_head + g * SLAB + l * VEC);
             if (active) {
                 if (from_prev) gmem_put_f32<VEC>(p.thead + (size_t)t * dim + coff, sum);
-                else Lane<T, VEC>::store(Cl + (size_t)(x0 - 1) * dim, sum);
+                else {
+                    if (rs) scale_by<VEC>(sum, __ldg(rs + x0 - 1));
+                    Lane<T, VEC>::store(Cl + (size_t)(x0 - 1) * dim, sum);
+                }
             }
         }
     }
@@ -653,7 +670,8 @@ __global__ void fixup_warp_kernel(const TileParams p) {
 template <typename T>
 __global__ void __launch_bounds__(kStrands * 32) fixup_long_kernel(const int2 *__restrict__ xy, const int *__restrict__ rp,
                                                                     const float *__restrict__ tcarry, const float *__restrict__ thead,
-                                                                    T *__restrict__ C, const int *__restrict__ list, int dim) {
+                                                                    T *__restrict__ C, const int *__restrict__ list, int dim,
+                                                                    const float *__restrict__ row_scale) {
     __shared__ float part[kStrands][32];
     const int t = list[blockIdx.x];
     const int g = threadIdx.x / 32, lane = threadIdx.x % 32;
@@ -672,6 +690,7 @@ __global__ void __launch_bounds__(kStrands * 32) fixup_long_kernel(const int2 *_
 #pragma unroll
             for (int k = 0; k < kStrands; ++k) sum += part[k][lane];
             sum += thead[(size_t)t * dim + j];
+            if (row_scale) sum *= __ldg(row_scale + row);
             store_c(C + (size_t)row * dim + j, sum);
         }
         __syncthreads();

@@ -299,9 +299,11 @@ typedef struct {
     const void *val, *B;
     void *C;
     int dim, is_half;
+    const float *row_scale, *col_scale; /* scaled variant: value(i,j) = row_scale[i]*col_scale[j]; NULL otherwise */
 } model_io;
 
 static inline float model_val(const model_io *io, int k) {
+    if (io->col_scale) return io->col_scale[io->col[k]];
     if (!io->val) return 1.0f;
     return io->is_half ? half_bits_to_float(((const uint16_t *)io->val)[k]) : ((const float *)io->val)[k];
 }
@@ -309,17 +311,23 @@ static inline float model_b(const model_io *io, int c, int j) {
     size_t at = (size_t)c * io->dim + j;
     return io->is_half ? half_bits_to_float(((const uint16_t *)io->B)[at]) : ((const float *)io->B)[at];
 }
-static inline void model_store(const model_io *io, int row, const float *v) {
+static inline void model_store(const model_io *io, int row, const float *v_in) {
     size_t at = (size_t)row * io->dim;
+    float scaled[1024];
+    const float *v = v_in;
+    if (io->row_scale) { /* the row factor multiplies the finished row once */
+        for (int j = 0; j < io->dim; ++j) scaled[j] = v_in[j] * io->row_scale[row];
+        v = scaled;
+    }
     if (io->is_half) for (int j = 0; j < io->dim; ++j) ((uint16_t *)io->C)[at + j] = float_to_half_bits(v[j]);
     else memcpy((float *)io->C + at, v, sizeof(float) * io->dim);
 }
 
-ORC_API int orc_tile_model(const int *row_ptr, const int *col, const void *val, const void *B,
-                           void *C, int n_rows, int nnz, int dim, int is_half, int cost,
-                           int nch, int cpu, int long_chain) {
-    if (cost < 1 || nch < 1 || cpu < 1 || nch % cpu != 0 || dim < 1) return -1;
-    model_io io = {row_ptr, col, val, B, C, dim, is_half};
+static int tile_model_impl(const int *row_ptr, const int *col, const void *val, const float *row_scale, const float *col_scale,
+                           const void *B, void *C, int n_rows, int nnz, int dim, int is_half, int cost, int nch, int cpu,
+                           int long_chain) {
+    if (cost < 1 || nch < 1 || cpu < 1 || nch % cpu != 0 || dim < 1 || dim > 1024) return -1;
+    model_io io = {row_ptr, col, val, B, C, dim, is_half, row_scale, col_scale};
     const int nu = nch / cpu; /* units per tile */
     const int64_t total = (int64_t)n_rows + 1 + nnz;
     const int P = orc_chunk_count(n_rows, nnz, cost);
@@ -408,6 +416,21 @@ ORC_API int orc_tile_model(const int *row_ptr, const int *col, const void *val, 
     free(tx); free(ty); free(tcarry); free(thead); free(fx); free(fy); free(carry); free(head);
     free(has_head); free(acc); free(sum); free(strand);
     return 0;
+}
+
+ORC_API int orc_tile_model(const int *row_ptr, const int *col, const void *val, const void *B,
+                           void *C, int n_rows, int nnz, int dim, int is_half, int cost,
+                           int nch, int cpu, int long_chain) {
+    return tile_model_impl(row_ptr, col, val, NULL, NULL, B, C, n_rows, nnz, dim, is_half, cost, nch, cpu, long_chain);
+}
+
+/* The scaled variant (fp32): value(i,j) = row_scale[i] * col_scale[j]; the column factor enters each fused
+ * multiply-add, the row factor multiplies the finished row once.  No reference counterpart beyond the gesture
+ * at src/MergePathSpMM.cu:436-441. */
+ORC_API int orc_tile_model_scaled(const int *row_ptr, const int *col, const float *row_scale, const float *col_scale,
+                                  const float *B, float *C, int n_rows, int nnz, int dim, int cost, int nch, int cpu,
+                                  int long_chain) {
+    return tile_model_impl(row_ptr, col, NULL, row_scale, col_scale, B, C, n_rows, nnz, dim, 0, cost, nch, cpu, long_chain);
 }
 
 /* Nnz-balanced row slabs for G devices: bounds[g] = first row whose start

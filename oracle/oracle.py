@@ -60,6 +60,8 @@ def lib():
         L.orc_spmm_f32_omp.argtypes = [_i32p, _i32p, vp, vp, vp, C.c_int, C.c_int, C.c_int]
         L.orc_tile_model.restype = C.c_int
         L.orc_tile_model.argtypes = [_i32p, _i32p, vp, vp, vp] + [C.c_int] * 8
+        L.orc_tile_model_scaled.restype = C.c_int
+        L.orc_tile_model_scaled.argtypes = [_i32p, _i32p, vp, vp, vp, vp] + [C.c_int] * 7
         L.orc_slab_bounds.restype = None
         L.orc_slab_bounds.argtypes = [_i32p, C.c_int, C.c_int, _i32p]
         _lib = L
@@ -162,6 +164,18 @@ def tile_model(row_ptr, col, val, B, cost: int, nch: int, cpu: int, long_chain: 
                               cost, nch, cpu, long_chain)
     if rc != 0:
         raise ValueError("orc_tile_model: bad arguments")
+    return out
+
+
+def tile_model_scaled(row_ptr, col, row_scale, col_scale, B, cost: int, nch: int, cpu: int, long_chain: int) -> np.ndarray:
+    """Model of mps_spmm_scaled: value(i, j) = row_scale[i] * col_scale[j], row factor applied to the finished row."""
+    rp, ci = _i32(row_ptr), _i32(col)
+    rs, cs, Bm = (np.ascontiguousarray(a, np.float32) for a in (row_scale, col_scale, B))
+    n, dim = len(rp) - 1, Bm.shape[1]
+    out = np.zeros((n, dim), np.float32)
+    rc = lib().orc_tile_model_scaled(rp, ci, _ptr(rs), _ptr(cs), _ptr(Bm), _ptr(out), n, int(rp[-1]), dim, cost, nch, cpu, long_chain)
+    if rc != 0:
+        raise ValueError("orc_tile_model_scaled: bad arguments")
     return out
 
 

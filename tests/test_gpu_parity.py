@@ -341,6 +341,62 @@ def test_host_buffer_call_pipelines_large_inputs_over_row_slabs(mps, orc, graphs
     mps.capi.lib().mps_host_workspace_release()
 
 
+@pytest.mark.parametrize("dim,tune", [(16, None), (64, None), (64, dict(fused_fixup=0)), (20, None), (128, dict(chunks_per_unit=1, block_threads=128))])
+def test_scaled_product_bit_exact_with_its_model(mps, orc, graphs, cuda, dim, tune):
+    """mps_spmm_scaled: A's values are row_scale[i] * col_scale[j] (GCN: both = degree^-1/2), never stored."""
+    rp, col = cases.c1_rmat()
+    n, nnz = len(rp) - 1, len(col)
+    rng = np.random.default_rng(11)
+    rs = (1.0 / np.sqrt(np.diff(rp).astype(np.float64))).astype(np.float32)
+    cs = rng.uniform(0.5, 1.5, n).astype(np.float32)
+    B = graphs.dense_uniform(n, dim, seed=1)
+    plan = mps.Plan(n, nnz, dim, mps.F32, 8, device=cuda)
+    if tune:
+        plan.tune(**tune)
+    d_rp, d_col, d_rs, d_cs, d_B = (_dev(a, cuda) for a in (rp, col, rs, cs, B))
+    plan.partition(d_rp)
+    out = torch.full((n, dim), float("nan"), dtype=torch.float32, device=cuda)
+    plan.spmm_scaled(d_rp, d_col, d_rs, d_cs, d_B, out=out)
+    plan.sync_check()
+    info = plan.info()
+    got = out.cpu().numpy()
+    model = orc.tile_model_scaled(rp, col, rs, cs, B, 8, info["chunks_per_tile"], info["chunks_per_unit"], info["long_chain"])
+    assert np.array_equal(_bits(got), _bits(model))
+    rows = np.repeat(np.arange(n), np.diff(rp))
+    val = (rs.astype(np.float64)[rows] * cs.astype(np.float64)[col]).astype(np.float32)
+    scale = orc.spmm_abs_f64(rp, col, val, B)
+    assert (np.abs(got.astype(np.float64) - orc.spmm_f64(rp, col, val, B)) <= 2e-6 + 2e-5 * scale).all()
+    # the unscaled entry point still works on the same plan afterwards
+    plain = plan.spmm(d_rp, d_col, None, d_B).cpu().numpy()
+    assert np.array_equal(_bits(plain), _bits(orc.tile_model(rp, col, None, B, 8, info["chunks_per_tile"], info["chunks_per_unit"], info["long_chain"])))
+    plan.close()
+    with pytest.raises(mps.MpsError) as e:
+        ph = mps.Plan(n, nnz, 16, mps.F16, 8, device=cuda)
+        ph.partition(d_rp)
+        ph.spmm_scaled(d_rp, d_col, d_rs, d_cs, _dev(B[:, :16].astype(np.float16), cuda))
+    assert e.value.code == mps.capi.ERR_UNSUPPORTED
+
+
+def test_scaled_product_on_long_rows(mps, orc, cuda):
+    rp, col = cases.from_lengths([3, 30000, 2, 0, 5], 40000, 21)
+    rng = np.random.default_rng(6)
+    rs = rng.uniform(0.5, 1.5, len(rp) - 1).astype(np.float32)
+    cs = rng.uniform(-1, 1, 40000).astype(np.float32)
+    B = rng.uniform(-1, 1, (40000, 32)).astype(np.float32)
+    n, nnz = len(rp) - 1, len(col)
+    for tune in (dict(chunks_per_unit=1), dict(chunks_per_unit=1, fused_fixup=1)):
+        plan = mps.Plan(n, nnz, 32, mps.F32, 1, device=cuda)
+        plan.tune(**tune)
+        d = [_dev(a, cuda) for a in (rp, col, rs, cs, B)]
+        plan.partition(d[0])
+        got = plan.spmm_scaled(*d).cpu().numpy()
+        plan.sync_check()
+        info = plan.info()
+        model = orc.tile_model_scaled(rp, col, rs, cs, B, 1, info["chunks_per_tile"], info["chunks_per_unit"], info["long_chain"])
+        assert np.array_equal(_bits(got), _bits(model)), tune
+        plan.close()
+
+
 # ------------------------------------------------------------------ slabs
 
 def test_row_slabs_are_bit_identical_to_their_own_model_and_close_to_the_whole(mps, orc, graphs, cuda):

@@ -132,3 +132,21 @@ def test_generators_host_equals_torch_cpu(graphs):
     assert np.array_equal(rp, rpt.numpy()) and np.array_equal(col, colt.numpy())
     assert np.array_equal(graphs.gcn_values(rp, col), graphs.gcn_values(rpt, colt).numpy())
     assert np.array_equal(graphs.dense_uniform(100, 7, 5), graphs.dense_uniform(100, 7, 5, device=torch.device("cpu")).numpy())
+
+
+def test_scaled_model_close_to_fp64(orc, graphs):
+    """value(i, j) = row_scale[i] * col_scale[j] with the row factor applied to the finished row."""
+    rp, col = cases.c1_rmat()
+    n = len(rp) - 1
+    dinv = (1.0 / np.sqrt(np.diff(rp).astype(np.float64))).astype(np.float32)
+    B = _rand_b(n, 24)
+    got = orc.tile_model_scaled(rp, col, dinv, dinv, B, 8, 64, 4, 32)
+    rows = np.repeat(np.arange(n), np.diff(rp))
+    val64 = dinv.astype(np.float64)[rows] * dinv.astype(np.float64)[col]
+    A = sp.csr_matrix((val64, col, rp), shape=(n, n))
+    ref = A @ B.astype(np.float64)
+    scale = abs(A) @ np.abs(B.astype(np.float64))
+    assert (np.abs(got - ref) <= 1e-6 + 1e-5 * scale).all()
+    # and close to the explicit GCN values (which round the product of the two factors once more)
+    explicit = orc.tile_model(rp, col, graphs.gcn_values(rp, col), B, 8, 64, 4, 32)
+    assert (np.abs(got - explicit) <= 1e-6 + 1e-5 * scale).all()
