@@ -273,17 +273,25 @@ extern "C" int mps_plan_partition(mps_plan *p, const int32_t *d_row_ptr, void *s
     return MPS_OK;
 }
 
+template <typename T, int VEC, int GL, int U, int BLOCK, bool SCALED>
+static int launch_tile_k(const mps_plan *p, const TileParams &tp, cudaStream_t st) {
+    auto kern = spmm_tile_kernel<T, VEC, GL, U, BLOCK, SCALED>;
+    if (p->smem_bytes > 48 * 1024) MPS_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, p->smem_bytes));
+    dim3 grid((unsigned)p->n_tiles, (unsigned)p->n_col_slabs);
+    kern<<<grid, BLOCK, p->smem_bytes, st>>>(tp);
+    MPS_CUDA(cudaGetLastError());
+    return MPS_OK;
+}
+
 template <typename T, int VEC, int GL, int U, int BLOCK>
 static int launch_tile(const mps_plan *p, const TileParams &tp, cudaStream_t st) {
     if constexpr (BLOCK < GL) {
         return fail(MPS_ERR_STATE, "block of %d threads cannot hold a group of %d lanes", BLOCK, GL);
     } else {
-        auto kern = spmm_tile_kernel<T, VEC, GL, U, BLOCK>;
-        if (p->smem_bytes > 48 * 1024) MPS_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, p->smem_bytes));
-        dim3 grid((unsigned)p->n_tiles, (unsigned)p->n_col_slabs);
-        kern<<<grid, BLOCK, p->smem_bytes, st>>>(tp);
-        MPS_CUDA(cudaGetLastError());
-        return MPS_OK;
+        if constexpr (sizeof(T) == 4) {  // the scaled product exists for fp32 plans only
+            if (tp.col_scale) return launch_tile_k<T, VEC, GL, U, BLOCK, true>(p, tp, st);
+        }
+        return launch_tile_k<T, VEC, GL, U, BLOCK, false>(p, tp, st);
     }
 }
 

@@ -375,7 +375,9 @@ __device__ __forceinline__ void block_fixup(const TileParams &p, int e, int chai
 // ---------------------------------------------------------------------------------------------
 // One block = one tile = GPC units; unit u = `cpu` consecutive chunks walked by one group of GL
 // lanes with the accumulator kept in registers across the chunk boundaries inside the unit.
-template <typename T, int VEC, int GL, int U, int BLOCK>
+// SCALED: the value of non-zero (i, j) is row_scale[i] * col_scale[j] instead of a stored value (a kernel of
+// its own so that the plain product carries none of its selects).
+template <typename T, int VEC, int GL, int U, int BLOCK, bool SCALED>
 __global__ void __launch_bounds__(BLOCK, kWarpsPerSm * 32 / BLOCK) spmm_tile_kernel(const TileParams p) {
     constexpr int kBlock = BLOCK;
     constexpr int GPC = kBlock / GL;   // units (lane groups) per block
@@ -397,7 +399,7 @@ __global__ void __launch_bounds__(BLOCK, kWarpsPerSm * 32 / BLOCK) spmm_tile_ker
     const int coff = blockIdx.y * SLAB + l * VEC;  // first column of this lane
     const bool active = coff < p.dim;
     const bool has_val = p.val != nullptr;
-    const float *__restrict__ cs = p.col_scale, *__restrict__ rs = p.row_scale;
+    [[maybe_unused]] const float *__restrict__ cs = p.col_scale, *__restrict__ rs = p.row_scale;
     const T *__restrict__ Bl = static_cast<const T *>(p.B) + coff;  // this lane's columns of B
     T *__restrict__ Cl = static_cast<T *>(p.C) + coff;
     const unsigned dim = (unsigned)p.dim;
@@ -488,7 +490,7 @@ __global__ void __launch_bounds__(BLOCK, kWarpsPerSm * 32 / BLOCK) spmm_tile_ker
                     smem_put<VEC>(s_head + g * SLAB + l * VEC, acc);
                     head_pending = false;
                 } else if (active) {
-                    if (rs) scale_by<VEC>(acc, __ldg(rs + x - 1));
+                    if constexpr (SCALED) scale_by<VEC>(acc, __ldg(rs + x - 1));
                     Lane<T, VEC>::store(Cl + (size_t)(x - 1) * dim, acc);
                 }
 #pragma unroll
@@ -506,7 +508,8 @@ __global__ void __launch_bounds__(BLOCK, kWarpsPerSm * 32 / BLOCK) spmm_tile_ker
 #pragma unroll
             for (int u = 0; u < U; ++u) {
                 const unsigned ci = (unsigned)w_col[k + u];
-                a[u] = cs ? Lane<T, VEC>::from_float(__ldg(cs + ci)) : has_val ? Lane<T, VEC>::value(w_val[k + u]) : Lane<T, VEC>::one();
+                if constexpr (SCALED) a[u] = Lane<T, VEC>::from_float(__ldg(cs + ci));
+                else a[u] = has_val ? Lane<T, VEC>::value(w_val[k + u]) : Lane<T, VEC>::one();
                 if (active) b[u] = Lane<T, VEC>::load(Bl + (size_t)ci * dim);
             }
             while (next_mark <= k) end_row();
@@ -531,7 +534,8 @@ __global__ void __launch_bounds__(BLOCK, kWarpsPerSm * 32 / BLOCK) spmm_tile_ker
             for (int u = 0; u < U - 1; ++u) {
                 if (k + u < y1) {
                     const unsigned ci = (unsigned)w_col[k + u];
-                    a[u] = cs ? Lane<T, VEC>::from_float(__ldg(cs + ci)) : has_val ? Lane<T, VEC>::value(w_val[k + u]) : Lane<T, VEC>::one();
+                    if constexpr (SCALED) a[u] = Lane<T, VEC>::from_float(__ldg(cs + ci));
+                else a[u] = has_val ? Lane<T, VEC>::value(w_val[k + u]) : Lane<T, VEC>::one();
                     if (active) b[u] = Lane<T, VEC>::load(Bl + (size_t)ci * dim);
                 }
             }
@@ -563,7 +567,7 @@ __global__ void __launch_bounds__(BLOCK, kWarpsPerSm * 32 / BLOCK) spmm_tile_ker
             if (active) {
                 if (from_prev) gmem_put_f32<VEC>(p.thead + (size_t)t * dim + coff, sum);
                 else {
-                    if (rs) scale_by<VEC>(sum, __ldg(rs + x0 - 1));
+                    if constexpr (SCALED) scale_by<VEC>(sum, __ldg(rs + x0 - 1));
                     Lane<T, VEC>::store(Cl + (size_t)(x0 - 1) * dim, sum);
                 }
             }
