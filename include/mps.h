@@ -162,7 +162,9 @@ MPS_API int mps_spmm(mps_plan *plan, const int32_t *d_row_ptr, const int32_t *d_
  * (src/MergePathSpMM.cu:436-441,450,459): C[i,:] = row_scale[i] * sum_k col_scale[col[k]] * B[col[k],:]
  * for the non-zeros k of row i - e.g. GCN's D^-1/2 (A+I) D^-1/2 X with both scales = degree^-1/2 - without
  * a stored value per non-zero.  The column factor is gathered per non-zero, the row factor multiplies the
- * finished row once.  fp32 plans only; scales are fp32 device arrays (n_rows and n_cols entries). */
+ * finished row once.  Either scale may be NULL (= all ones), not both: with d_col_scale == NULL and B already
+ * multiplied by the column factor where it was produced, the multiply reads no per-non-zero value at all,
+ * which is the fastest form.  fp32 plans only; scales are fp32 device arrays (n_rows and n_cols entries). */
 MPS_API int mps_spmm_scaled(mps_plan *plan, const int32_t *d_row_ptr, const int32_t *d_col_idx,
                     const float *d_row_scale, const float *d_col_scale, const void *d_B, void *d_C, void *stream);
 

@@ -289,7 +289,7 @@ static int launch_tile(const mps_plan *p, const TileParams &tp, cudaStream_t st)
         return fail(MPS_ERR_STATE, "block of %d threads cannot hold a group of %d lanes", BLOCK, GL);
     } else {
         if constexpr (sizeof(T) == 4) {  // the scaled product exists for fp32 plans only
-            if (tp.col_scale) return launch_tile_k<T, VEC, GL, U, BLOCK, true>(p, tp, st);
+            if (tp.col_scale || tp.row_scale) return launch_tile_k<T, VEC, GL, U, BLOCK, true>(p, tp, st);
         }
         return launch_tile_k<T, VEC, GL, U, BLOCK, false>(p, tp, st);
     }
@@ -377,7 +377,7 @@ extern "C" int mps_spmm(mps_plan *p, const int32_t *d_row_ptr, const int32_t *d_
 
 extern "C" int mps_spmm_scaled(mps_plan *p, const int32_t *d_row_ptr, const int32_t *d_col_idx, const float *d_row_scale,
                                const float *d_col_scale, const void *d_B, void *d_C, void *stream) {
-    if (!d_row_scale || !d_col_scale) return fail(MPS_ERR_ARG, "mps_spmm_scaled: NULL scale array");
+    if (!d_row_scale && !d_col_scale) return fail(MPS_ERR_ARG, "mps_spmm_scaled: both scale arrays are NULL (use mps_spmm)");
     if (p && p->dtype != MPS_F32) return fail(MPS_ERR_UNSUPPORTED, "mps_spmm_scaled: fp32 plans only");
     if (((uintptr_t)d_row_scale % 4) || ((uintptr_t)d_col_scale % 4)) return fail(MPS_ERR_ALIGN, "mps_spmm_scaled: scale arrays must be 4-byte aligned");
     return spmm_launch(p, d_row_ptr, d_col_idx, nullptr, d_row_scale, d_col_scale, d_B, d_C, stream);

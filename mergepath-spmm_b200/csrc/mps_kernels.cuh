@@ -38,8 +38,8 @@ struct TileParams {
     const int *rp;
     const int *col;
     const void *val;  // nullptr: all ones
-    const float *row_scale;  // with col_scale (fp32 plans): value of non-zero (i, j) = row_scale[i] * col_scale[j], the row
-    const float *col_scale;  // factor applied once, to the finished row; both nullptr otherwise
+    const float *row_scale;  // scaled product (fp32 plans): value of non-zero (i, j) = row_scale[i] * col_scale[j], the row factor
+    const float *col_scale;  // applied once, to the finished row; a nullptr factor is 1; both nullptr for the plain product
     const void *B;
     void *C;
     const int2 *tile_xy;  // n_tiles + 1 boundary coordinates, reference convention
@@ -483,6 +483,10 @@ __global__ void __launch_bounds__(BLOCK, kWarpsPerSm * 32 / BLOCK) spmm_tile_ker
         float acc[VEC];
 #pragma unroll
         for (int i = 0; i < VEC; ++i) acc[i] = 0.0f;
+        // scaled product: the factor of the row being summed, fetched when the row starts so that its latency
+        // hides behind the row's gathers
+        [[maybe_unused]] float row_s = 1.0f;
+        if constexpr (SCALED) { if (rs && x >= 1 && x < x1) row_s = __ldg(rs + x - 1); }
 
         auto end_row = [&]() {
             if (x >= 1) {  // marker x ends row x-1 (marker 0 ends nothing)
@@ -490,7 +494,7 @@ __global__ void __launch_bounds__(BLOCK, kWarpsPerSm * 32 / BLOCK) spmm_tile_ker
                     smem_put<VEC>(s_head + g * SLAB + l * VEC, acc);
                     head_pending = false;
                 } else if (active) {
-                    if constexpr (SCALED) scale_by<VEC>(acc, __ldg(rs + x - 1));
+                    if constexpr (SCALED) scale_by<VEC>(acc, row_s);
                     Lane<T, VEC>::store(Cl + (size_t)(x - 1) * dim, acc);
                 }
 #pragma unroll
@@ -498,6 +502,7 @@ __global__ void __launch_bounds__(BLOCK, kWarpsPerSm * 32 / BLOCK) spmm_tile_ker
             }
             ++x;
             next_mark = x < x1 ? w_rp[x] : 0x7fffffff;
+            if constexpr (SCALED) { if (rs && x < x1) row_s = __ldg(rs + x - 1); }
         };
 
         int k = y0;
@@ -508,7 +513,7 @@ __global__ void __launch_bounds__(BLOCK, kWarpsPerSm * 32 / BLOCK) spmm_tile_ker
 #pragma unroll
             for (int u = 0; u < U; ++u) {
                 const unsigned ci = (unsigned)w_col[k + u];
-                if constexpr (SCALED) a[u] = Lane<T, VEC>::from_float(__ldg(cs + ci));
+                if constexpr (SCALED) a[u] = cs ? Lane<T, VEC>::from_float(__ldg(cs + ci)) : Lane<T, VEC>::one();
                 else a[u] = has_val ? Lane<T, VEC>::value(w_val[k + u]) : Lane<T, VEC>::one();
                 if (active) b[u] = Lane<T, VEC>::load(Bl + (size_t)ci * dim);
             }
@@ -534,7 +539,7 @@ __global__ void __launch_bounds__(BLOCK, kWarpsPerSm * 32 / BLOCK) spmm_tile_ker
             for (int u = 0; u < U - 1; ++u) {
                 if (k + u < y1) {
                     const unsigned ci = (unsigned)w_col[k + u];
-                    if constexpr (SCALED) a[u] = Lane<T, VEC>::from_float(__ldg(cs + ci));
+                    if constexpr (SCALED) a[u] = cs ? Lane<T, VEC>::from_float(__ldg(cs + ci)) : Lane<T, VEC>::one();
                 else a[u] = has_val ? Lane<T, VEC>::value(w_val[k + u]) : Lane<T, VEC>::one();
                     if (active) b[u] = Lane<T, VEC>::load(Bl + (size_t)ci * dim);
                 }
@@ -567,7 +572,7 @@ __global__ void __launch_bounds__(BLOCK, kWarpsPerSm * 32 / BLOCK) spmm_tile_ker
             if (active) {
                 if (from_prev) gmem_put_f32<VEC>(p.thead + (size_t)t * dim + coff, sum);
                 else {
-                    if constexpr (SCALED) scale_by<VEC>(sum, __ldg(rs + x0 - 1));
+                    if constexpr (SCALED) { if (rs) scale_by<VEC>(sum, __ldg(rs + x0 - 1)); }
                     Lane<T, VEC>::store(Cl + (size_t)(x0 - 1) * dim, sum);
                 }
             }

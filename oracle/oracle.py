@@ -168,9 +168,10 @@ def tile_model(row_ptr, col, val, B, cost: int, nch: int, cpu: int, long_chain: 
 
 
 def tile_model_scaled(row_ptr, col, row_scale, col_scale, B, cost: int, nch: int, cpu: int, long_chain: int) -> np.ndarray:
-    """Model of mps_spmm_scaled: value(i, j) = row_scale[i] * col_scale[j], row factor applied to the finished row."""
+    """Model of mps_spmm_scaled: value(i, j) = row_scale[i] * col_scale[j], row factor applied to the finished row;
+    a scale given as None is all ones."""
     rp, ci = _i32(row_ptr), _i32(col)
-    rs, cs, Bm = (np.ascontiguousarray(a, np.float32) for a in (row_scale, col_scale, B))
+    rs, cs, Bm = (None if a is None else np.ascontiguousarray(a, np.float32) for a in (row_scale, col_scale, B))
     n, dim = len(rp) - 1, Bm.shape[1]
     out = np.zeros((n, dim), np.float32)
     rc = lib().orc_tile_model_scaled(rp, ci, _ptr(rs), _ptr(cs), _ptr(Bm), _ptr(out), n, int(rp[-1]), dim, cost, nch, cpu, long_chain)

@@ -397,6 +397,35 @@ def test_scaled_product_on_long_rows(mps, orc, cuda):
         plan.close()
 
 
+def test_scaled_product_with_one_factor_only(mps, orc, graphs, cuda):
+    """Either scale may be absent (= ones); the row-only form equals the full form on a B that already carries the
+    column factor, which is how a caller avoids the per-non-zero gather of col_scale."""
+    rp, col = cases.c1_rmat()
+    n, nnz, dim = len(rp) - 1, len(col), 64
+    rng = np.random.default_rng(12)
+    rs = rng.uniform(0.5, 1.5, n).astype(np.float32)
+    cs = rng.uniform(0.5, 1.5, n).astype(np.float32)
+    B = graphs.dense_uniform(n, dim, seed=2)
+    plan = mps.Plan(n, nnz, dim, mps.F32, 8, device=cuda)
+    d_rp, d_col, d_rs, d_cs, d_B = (_dev(a, cuda) for a in (rp, col, rs, cs, B))
+    plan.partition(d_rp)
+    info = plan.info()
+    shape = (8, info["chunks_per_tile"], info["chunks_per_unit"], info["long_chain"])
+    for r, c, dr, dc in ((rs, None, d_rs, None), (None, cs, None, d_cs)):
+        got = plan.spmm_scaled(d_rp, d_col, dr, dc, d_B).cpu().numpy()
+        plan.sync_check()
+        assert np.array_equal(_bits(got), _bits(orc.tile_model_scaled(rp, col, r, c, B, *shape)))
+    Bs = (B * cs[:, None]).astype(np.float32)
+    got = plan.spmm_scaled(d_rp, d_col, d_rs, None, _dev(Bs, cuda)).cpu().numpy()
+    rows = np.repeat(np.arange(n), np.diff(rp))
+    val = (rs.astype(np.float64)[rows] * cs.astype(np.float64)[col]).astype(np.float32)
+    scale = orc.spmm_abs_f64(rp, col, val, B)
+    assert (np.abs(got.astype(np.float64) - orc.spmm_f64(rp, col, val, B)) <= 2e-6 + 2e-5 * scale).all()
+    with pytest.raises(mps.MpsError):
+        plan.spmm_scaled(d_rp, d_col, None, None, d_B)
+    plan.close()
+
+
 # ------------------------------------------------------------------ slabs
 
 def test_row_slabs_are_bit_identical_to_their_own_model_and_close_to_the_whole(mps, orc, graphs, cuda):
