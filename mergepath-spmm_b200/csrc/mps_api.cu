@@ -435,11 +435,13 @@ extern "C" int mps_plan_info(const mps_plan *p, int64_t what[16]) {
 // ------------------------------------------------------------------------------------- host-buffer call
 //
 // The call is cut into row slabs (equal nnz + 4*rows) so that PCIe runs in both directions at once:
-//   B stream       : all of B, from the start;
-//   copy-in stream : row_ptr, rebasing + partition of every slab, then col_idx/val slab by slab;
-//   work stream    : waits for B and for slab s, multiplies slab s, copies its rows of C back
-// so the download of C overlaps the upload of the later slabs of A.  Device buffers and the
-// per-slab plans live in a per-thread workspace that only grows / is rebuilt when shapes change.
+//   upload stream  : all of B first (no row of C can be formed before it is whole), then col_idx/val slab by slab;
+//   plan stream    : row_ptr, rebasing + partition of every slab, beside the upload of B;
+//   work stream    : waits for slab s, multiplies it;
+//   download stream: copies slab s of C back as soon as it is multiplied
+// so the download of C starts right after B and the first slab of A have landed and overlaps the upload of
+// the later slabs.  Device buffers and the per-slab plans live in a per-thread workspace that only grows /
+// is rebuilt when shapes change.
 
 // out[i] = rp[row0 + i] - rp[row0], i = 0..rows
 __global__ void rebase_kernel(const int *__restrict__ rp, int row0, int rows, int *__restrict__ out) {
@@ -455,21 +457,23 @@ struct HostWorkspace {
     void *buf[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};  // rp, col, val, B, C, rebased rp slabs
     size_t cap[6] = {0, 0, 0, 0, 0, 0};
     mps_plan *plan[kMaxHostSlabs] = {};
-    cudaStream_t s_in = nullptr, s_b = nullptr, s_work = nullptr;
-    cudaEvent_t ev_b = nullptr, ev_slab[kMaxHostSlabs] = {};
+    cudaStream_t s_in = nullptr, s_b = nullptr, s_work = nullptr, s_out = nullptr;  // plan, upload, work, download
+    cudaEvent_t ev_b = nullptr, ev_slab[kMaxHostSlabs] = {}, ev_done[kMaxHostSlabs] = {};
     int device = -1;
     void release() {
         for (int i = 0; i < 6; ++i) { cudaFree(buf[i]); buf[i] = nullptr; cap[i] = 0; }
         for (int i = 0; i < kMaxHostSlabs; ++i) {
             mps_plan_destroy(plan[i]); plan[i] = nullptr;
             if (ev_slab[i]) cudaEventDestroy(ev_slab[i]);
-            ev_slab[i] = nullptr;
+            if (ev_done[i]) cudaEventDestroy(ev_done[i]);
+            ev_slab[i] = ev_done[i] = nullptr;
         }
         if (ev_b) cudaEventDestroy(ev_b);
         if (s_in) cudaStreamDestroy(s_in);
         if (s_b) cudaStreamDestroy(s_b);
         if (s_work) cudaStreamDestroy(s_work);
-        ev_b = nullptr; s_in = s_b = s_work = nullptr; device = -1;
+        if (s_out) cudaStreamDestroy(s_out);
+        ev_b = nullptr; s_in = s_b = s_work = s_out = nullptr; device = -1;
     }
 };
 thread_local HostWorkspace g_ws;
@@ -500,8 +504,12 @@ extern "C" int mps_spmm_host(int32_t n_rows, int32_t n_cols, int32_t nnz, int32_
         MPS_CUDA(cudaStreamCreateWithFlags(&g_ws.s_in, cudaStreamNonBlocking));
         MPS_CUDA(cudaStreamCreateWithFlags(&g_ws.s_b, cudaStreamNonBlocking));
         MPS_CUDA(cudaStreamCreateWithFlags(&g_ws.s_work, cudaStreamNonBlocking));
+        MPS_CUDA(cudaStreamCreateWithFlags(&g_ws.s_out, cudaStreamNonBlocking));
         MPS_CUDA(cudaEventCreateWithFlags(&g_ws.ev_b, cudaEventDisableTiming));
-        for (int i = 0; i < kMaxHostSlabs; ++i) MPS_CUDA(cudaEventCreateWithFlags(&g_ws.ev_slab[i], cudaEventDisableTiming));
+        for (int i = 0; i < kMaxHostSlabs; ++i) {
+            MPS_CUDA(cudaEventCreateWithFlags(&g_ws.ev_slab[i], cudaEventDisableTiming));
+            MPS_CUDA(cudaEventCreateWithFlags(&g_ws.ev_done[i], cudaEventDisableTiming));
+        }
     }
     const size_t elem = dtype == MPS_F16 ? 2 : 4;
     const long long items = (long long)n_rows + nnz;
@@ -527,11 +535,11 @@ extern "C" int mps_spmm_host(int32_t n_rows, int32_t n_cols, int32_t nnz, int32_
     int32_t *d_rp = (int32_t *)g_ws.buf[0], *d_col = (int32_t *)g_ws.buf[1], *d_rps = (int32_t *)g_ws.buf[5];
     char *d_val = (char *)g_ws.buf[2], *d_C = (char *)g_ws.buf[4];
 
-    cudaStream_t s_in = g_ws.s_in, s_work = g_ws.s_work;
-    // B starts uploading at once on its own stream; row_ptr, rebasing and the partitions run beside it
-    MPS_CUDA(cudaMemcpyAsync(g_ws.buf[3], B, bytes[3], cudaMemcpyHostToDevice, g_ws.s_b));
-    MPS_CUDA(cudaEventRecord(g_ws.ev_b, g_ws.s_b));
+    cudaStream_t s_in = g_ws.s_in, s_up = g_ws.s_b, s_work = g_ws.s_work, s_out = g_ws.s_out;
+    // row_ptr first (small; the partitions need it), then B at once; rebasing and the partitions run beside B
     MPS_CUDA(cudaMemcpyAsync(d_rp, row_ptr, bytes[0], cudaMemcpyHostToDevice, s_in));
+    MPS_CUDA(cudaMemcpyAsync(g_ws.buf[3], B, bytes[3], cudaMemcpyHostToDevice, s_up));
+    MPS_CUDA(cudaEventRecord(g_ws.ev_b, s_up));
     size_t rps_off[kMaxHostSlabs];
     size_t at = 0;
     for (int s = 0; s < n_slabs; ++s) {
@@ -564,19 +572,22 @@ extern "C" int mps_spmm_host(int32_t n_rows, int32_t n_cols, int32_t nnz, int32_
         const int r0 = bounds[s], rows = bounds[s + 1] - bounds[s];
         const size_t k0 = (size_t)row_ptr[r0], len = (size_t)(row_ptr[bounds[s + 1]] - row_ptr[r0]);
         if (len) {
-            MPS_CUDA(cudaMemcpyAsync(d_col + off[s], col_idx + k0, 4 * len, cudaMemcpyHostToDevice, s_in));
-            if (val) MPS_CUDA(cudaMemcpyAsync(d_val + elem * off[s], (const char *)val + elem * k0, elem * len, cudaMemcpyHostToDevice, s_in));
+            MPS_CUDA(cudaMemcpyAsync(d_col + off[s], col_idx + k0, 4 * len, cudaMemcpyHostToDevice, s_up));
+            if (val) MPS_CUDA(cudaMemcpyAsync(d_val + elem * off[s], (const char *)val + elem * k0, elem * len, cudaMemcpyHostToDevice, s_up));
         }
-        MPS_CUDA(cudaEventRecord(g_ws.ev_slab[s], s_in));
+        MPS_CUDA(cudaEventRecord(g_ws.ev_slab[s], s_up));  // behind B on the same stream: B is whole when this fires
         MPS_CUDA(cudaStreamWaitEvent(s_work, g_ws.ev_slab[s], 0));
         char *c_slab = d_C + elem * (size_t)r0 * dim;
         if (int rc = mps_spmm(g_ws.plan[s], d_rps + rps_off[s], d_col + off[s], val ? (const void *)(d_val + elem * off[s]) : nullptr,
                               g_ws.buf[3], c_slab, s_work))
             return rc;
-        if (rows) MPS_CUDA(cudaMemcpyAsync((char *)C + elem * (size_t)r0 * dim, c_slab, elem * (size_t)rows * dim, cudaMemcpyDeviceToHost, s_work));
+        MPS_CUDA(cudaEventRecord(g_ws.ev_done[s], s_work));
+        MPS_CUDA(cudaStreamWaitEvent(s_out, g_ws.ev_done[s], 0));
+        if (rows) MPS_CUDA(cudaMemcpyAsync((char *)C + elem * (size_t)r0 * dim, c_slab, elem * (size_t)rows * dim, cudaMemcpyDeviceToHost, s_out));
     }
     MPS_CUDA(cudaStreamSynchronize(s_in));
-    MPS_CUDA(cudaStreamSynchronize(g_ws.s_b));
+    MPS_CUDA(cudaStreamSynchronize(s_up));
+    MPS_CUDA(cudaStreamSynchronize(s_out));
     for (int s = 0; s < n_slabs; ++s)
         if (int rc = mps_plan_sync_check(g_ws.plan[s], s_work)) return rc;
     return MPS_OK;
