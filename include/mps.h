@@ -92,6 +92,15 @@ MPS_API int mps_coo_to_csr(int32_t n_nodes, int64_t n_edges, const int64_t *src,
 MPS_API int mps_coo_to_csr_device(int32_t n_nodes, int64_t n_edges, const int64_t *d_src, const int64_t *d_dst,
                           int32_t *d_row_ptr, int32_t *d_col_idx, int32_t *nnz_out, void *stream);
 
+/* CSR of the transpose, on the device (no reference counterpart: the reference has no backward pass; this is
+ * what dB = A^T dC of its GCN use case multiplies with - for a symmetric A the transpose is A itself and
+ * nothing has to be built).  A is n_rows x n_cols; d_row_ptr_t receives n_cols + 1 entries, d_col_idx_t and
+ * d_val_t (NULL together with d_val; dtype gives the value width) nnz entries; every transposed row's
+ * columns come out ascending.  Allocates its temporaries (12 bytes per non-zero), synchronises the stream. */
+MPS_API int mps_csr_transpose_device(int32_t n_rows, int32_t n_cols, int32_t nnz, int dtype, const int32_t *d_row_ptr,
+                             const int32_t *d_col_idx, const void *d_val, int32_t *d_row_ptr_t, int32_t *d_col_idx_t,
+                             void *d_val_t, void *stream);
+
 /* Replaces scripts/npz_to_csr.py as a whole up to the text writer: reads the members `src_li` and
  * `dst_li` (one-dimensional little-endian integer arrays) of a `.npz` archive, stored or deflated,
  * and converts them with mps_coo_to_csr; follow with mps_csr_save for the `.csr` text. */

@@ -294,6 +294,23 @@ def coo_to_csr_device(src, dst, n_nodes: int, stream=None):
     return rp, col[: nnz.value]
 
 
+def csr_transpose_device(row_ptr, col_idx, val, n_cols: int, stream=None):
+    """CSR of the transpose of an (n_rows x n_cols) matrix given as int32 CUDA tensors (val: fp32 / fp16 tensor or None).
+    Returns (row_ptr_t, col_idx_t, val_t); each transposed row's columns are ascending."""
+    _need_cuda(row_ptr, col_idx, val)
+    n_rows, nnz = row_ptr.numel() - 1, col_idx.numel()
+    dtype = F16 if (val is not None and val.dtype == torch.float16) else F32
+    if val is not None and val.dtype not in (torch.float16, torch.float32):
+        raise ValueError("values must be float32 or float16")
+    rp_t = torch.empty(n_cols + 1, dtype=torch.int32, device=row_ptr.device)
+    col_t = torch.empty(nnz, dtype=torch.int32, device=row_ptr.device)
+    val_t = None if val is None else torch.empty_like(val)
+    with torch.cuda.device(row_ptr.device):
+        capi.check(capi.lib().mps_csr_transpose_device(n_rows, n_cols, nnz, dtype, _dev_ptr(row_ptr), _dev_ptr(col_idx), _dev_ptr(val),
+                                                       _dev_ptr(rp_t), _dev_ptr(col_t), _dev_ptr(val_t), _stream_ptr(stream)))
+    return rp_t, col_t, val_t
+
+
 def npz_to_csr(path: str, threads: int = 0):
     """(row_ptr, col_idx) from a `.npz` with members src_li / dst_li (scripts/npz_to_csr.py's input)."""
     csr = capi.Csr()

@@ -16,7 +16,7 @@ F32, F16 = 0, 1
 
 SYMBOLS = [
     "mps_last_error", "mps_version", "mps_csr_load", "mps_csr_free", "mps_csr_save", "mps_csr_save_bin",
-    "mps_csr_load_bin", "mps_coo_to_csr", "mps_coo_to_csr_device", "mps_npz_to_csr", "mps_chunk_count", "mps_partition_device", "mps_schedule_device", "mps_plan_create",
+    "mps_csr_load_bin", "mps_coo_to_csr", "mps_coo_to_csr_device", "mps_csr_transpose_device", "mps_npz_to_csr", "mps_chunk_count", "mps_partition_device", "mps_schedule_device", "mps_plan_create",
     "mps_plan_destroy", "mps_plan_tune", "mps_plan_partition", "mps_spmm", "mps_spmm_scaled", "mps_plan_sync_check", "mps_plan_info", "mps_plan_profile", "mps_plan_profile_read",
     "mps_algorithmic_bytes", "mps_spmm_host", "mps_host_workspace_release", "mps_spmm_noalloc", "mps_slab_bounds", "mps_slab_bounds_items", "mps_slab_rebase", "mps_multi_create", "mps_multi_destroy", "mps_multi_slab",
     "mps_multi_set_b", "mps_multi_spmm", "mps_multi_get_c",
@@ -57,6 +57,7 @@ def lib():
     L.mps_csr_load_bin.argtypes = [C.c_char_p, C.POINTER(Csr), C.POINTER(vp), C.POINTER(C.c_int)]
     L.mps_coo_to_csr.argtypes = [i32, i64, vp, vp, C.c_int, C.POINTER(Csr)]
     L.mps_coo_to_csr_device.argtypes = [i32, i64, vp, vp, vp, vp, C.POINTER(i32), vp]
+    L.mps_csr_transpose_device.argtypes = [i32, i32, i32, C.c_int, vp, vp, vp, vp, vp, vp, vp]
     L.mps_npz_to_csr.argtypes = [C.c_char_p, C.c_int, C.POINTER(Csr)]
     L.mps_chunk_count.argtypes = [i32, i32, i32, C.POINTER(i32), C.POINTER(i32)]
     L.mps_partition_device.argtypes = [vp, i32, i32, i32, vp, vp]

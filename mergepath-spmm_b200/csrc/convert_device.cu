@@ -1,8 +1,16 @@
-// Edge list -> CSR on the device (no reference counterpart; the reference converts on the host in Python,
+// Device-side structure conversions.
+//
+// (1) Edge list -> CSR (no reference counterpart; the reference converts on the host in Python,
 // scripts/npz_to_csr.py:13-19).  Same result as mps_coo_to_csr: duplicates collapsed, columns sorted.
 //   keys = src * n + dst  ->  radix sort  ->  drop repeats  ->  row_ptr[r] = first key >= r * n
 // Sort, select and scan come from CUB (shipped with the CUDA toolkit); this is set-up work before the
 // multiply, not part of it.
+//
+// (2) CSR -> CSR of the transpose (no reference counterpart): what the backward pass of the reference's use
+// case multiplies with, dB = A^T dC.  A stable radix sort of the non-zeros by column keeps each transposed
+// row's entries in ascending source-row order:
+//   perm = argsort(col, stable)  ->  col_t[k'] = row_of(perm[k']),  val_t[k'] = val[perm[k']],
+//   row_ptr_t[c] = first k' whose column >= c.
 #include "mps.h"
 
 #include <cuda_runtime.h>
@@ -90,5 +98,92 @@ extern "C" int mps_coo_to_csr_device(int32_t n_nodes, int64_t n_edges, const int
     else *nnz_out = h_count[0];
 done:
     cudaFree(keys); cudaFree(sorted); cudaFree(tmp); cudaFree(d_count);
+    return rc;
+}
+
+namespace {
+
+__global__ void iota_and_check(const int *__restrict__ col, int nnz, int n_cols, int *__restrict__ perm, int *__restrict__ bad) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= nnz) return;
+    perm[i] = i;
+    if ((unsigned)col[i] >= (unsigned)n_cols) atomicExch(bad, 1);
+}
+
+// k' -> source non-zero k = perm[k']; its row is the last i with row_ptr[i] <= k
+template <typename V>
+__global__ void transpose_fill(const int *__restrict__ rp, int n_rows, const int *__restrict__ perm, int nnz, const V *__restrict__ val,
+                               int *__restrict__ col_t, V *__restrict__ val_t) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= nnz) return;
+    const int k = perm[i];
+    int lo = 0, hi = n_rows + 1;  // first index with row_ptr > k
+    while (lo < hi) {
+        const int mid = (lo + hi) >> 1;
+        if (rp[mid] <= k) lo = mid + 1;
+        else hi = mid;
+    }
+    col_t[i] = lo - 1;
+    if (val) val_t[i] = val[k];
+}
+
+__global__ void row_ptr_of_sorted(const int *__restrict__ keys, int nnz, int n_cols, int *__restrict__ rp_t) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c > n_cols) return;
+    int lo = 0, hi = nnz;  // first k' with keys[k'] >= c
+    while (lo < hi) {
+        const int mid = (lo + hi) >> 1;
+        if (keys[mid] < c) lo = mid + 1;
+        else hi = mid;
+    }
+    rp_t[c] = lo;
+}
+
+}  // namespace
+
+extern "C" int mps_csr_transpose_device(int32_t n_rows, int32_t n_cols, int32_t nnz, int dtype, const int32_t *d_row_ptr,
+                                        const int32_t *d_col_idx, const void *d_val, int32_t *d_row_ptr_t, int32_t *d_col_idx_t,
+                                        void *d_val_t, void *stream) {
+    if (n_rows < 0 || n_cols < 1 || nnz < 0 || !d_row_ptr || !d_row_ptr_t || (nnz > 0 && (!d_col_idx || !d_col_idx_t)) ||
+        ((d_val != nullptr) != (d_val_t != nullptr)))
+        return fail(MPS_ERR_ARG, "mps_csr_transpose_device: bad argument");
+    if (dtype != MPS_F32 && dtype != MPS_F16) return fail(MPS_ERR_ARG, "mps_csr_transpose_device: unknown dtype %d", dtype);
+    cudaStream_t st = (cudaStream_t)stream;
+    int rc = MPS_OK;
+    int *perm = nullptr, *perm_sorted = nullptr, *keys_sorted = nullptr, *d_bad = nullptr;
+    void *tmp = nullptr;
+    size_t tmp_bytes = 0;
+    int h_bad = 0;
+    const size_t m = (size_t)(nnz ? nnz : 1);
+    int bits = 1;
+    while (bits < 31 && ((unsigned)(n_cols - 1) >> bits)) ++bits;
+    CD_CUDA(cudaMalloc(&perm, 4 * m));
+    CD_CUDA(cudaMalloc(&perm_sorted, 4 * m));
+    CD_CUDA(cudaMalloc(&keys_sorted, 4 * m));
+    CD_CUDA(cudaMalloc(&d_bad, sizeof(int)));
+    CD_CUDA(cudaMemsetAsync(d_bad, 0, sizeof(int), st));
+    CD_CUDA(cub::DeviceRadixSort::SortPairs(nullptr, tmp_bytes, d_col_idx, keys_sorted, perm, perm_sorted, nnz, 0, bits, st));
+    CD_CUDA(cudaMalloc(&tmp, tmp_bytes + 16));
+    if (nnz > 0) {
+        const unsigned blocks = (unsigned)((nnz + 255) / 256);
+        iota_and_check<<<blocks, 256, 0, st>>>(d_col_idx, nnz, n_cols, perm, d_bad);
+        CD_CUDA(cudaGetLastError());
+        CD_CUDA(cudaMemcpyAsync(&h_bad, d_bad, sizeof(int), cudaMemcpyDeviceToHost, st));
+        CD_CUDA(cudaStreamSynchronize(st));
+        if (h_bad) { rc = fail(MPS_ERR_ARG, "mps_csr_transpose_device: a column index lies outside [0, %d)", n_cols); goto done; }
+        CD_CUDA(cub::DeviceRadixSort::SortPairs(tmp, tmp_bytes, d_col_idx, keys_sorted, perm, perm_sorted, nnz, 0, bits, st));
+        if (dtype == MPS_F16)
+            transpose_fill<unsigned short><<<blocks, 256, 0, st>>>(d_row_ptr, n_rows, perm_sorted, nnz, (const unsigned short *)d_val, d_col_idx_t,
+                                                                   (unsigned short *)d_val_t);
+        else
+            transpose_fill<unsigned int><<<blocks, 256, 0, st>>>(d_row_ptr, n_rows, perm_sorted, nnz, (const unsigned int *)d_val, d_col_idx_t,
+                                                                 (unsigned int *)d_val_t);
+        CD_CUDA(cudaGetLastError());
+    }
+    row_ptr_of_sorted<<<(unsigned)((n_cols + 1 + 255) / 256), 256, 0, st>>>(keys_sorted, nnz, n_cols, d_row_ptr_t);
+    CD_CUDA(cudaGetLastError());
+    CD_CUDA(cudaStreamSynchronize(st));
+done:
+    cudaFree(perm); cudaFree(perm_sorted); cudaFree(keys_sorted); cudaFree(tmp); cudaFree(d_bad);
     return rc;
 }
