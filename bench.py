@@ -217,10 +217,14 @@ def run_ours(args):
     plan = mps.Plan(n_slab, nnz_slab, args.dim, dt, cost, args.tpw, device=dev)
     if args.chunks_per_unit or args.unroll or args.no_bulk or args.block or args.fused >= 0:
         plan.tune(args.chunks_per_unit, args.unroll, not args.no_bulk, args.block, args.fused)
-    t0 = time.perf_counter()
-    plan.partition(w["rp"])
-    torch.cuda.synchronize()
-    partition_ms = (time.perf_counter() - t0) * 1e3
+    partition_first_ms = partition_ms = 0.0
+    for i in range(2):  # the first call also loads the library's kernels onto the device
+        t0 = time.perf_counter()
+        plan.partition(w["rp"])
+        torch.cuda.synchronize()
+        partition_ms = (time.perf_counter() - t0) * 1e3
+        if i == 0:
+            partition_first_ms = partition_ms
     info = plan.info()
     C_out = torch.empty((n_slab, args.dim), dtype=w["B"].dtype, device=dev)
 
@@ -307,7 +311,7 @@ def run_ours(args):
                    "items_per_chunk": info["items_per_chunk"], "unroll": info["unroll"], "block_threads": info["block_threads"], "tiles": info["n_tiles"],
                    "long_rows": info["long_rows"]},
         "roofline": roofline, "e2e": e2e, "gpu_launches": args.steps * info["kernels_per_call"],
-        "clocks": clocks.summary(), "partition_ms": round(partition_ms, 3),
+        "clocks": clocks.summary(), "partition_ms": round(partition_ms, 3), "partition_first_call_ms": round(partition_first_ms, 3),
         "hbm_algorithmic_gbs": round(sum_over_ranks(alg, world) / (ms_step * 1e-3) / 1e9, 1),
     }
 
