@@ -69,6 +69,11 @@ def build_cli(force: bool = False) -> str:
         cmd = [_nvcc()] + ARCH + COMMON + ["-Xcompiler", "-pthread", "-o", exe, src, "-L" + LIBDIR, "-lmps_b200",
                                           "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN"]
         subprocess.run(cmd, check=True)
+    twin = CLI + "_fp16"  # the reference's fp16 program has the same argv; the program looks at its own name
+    if not os.path.exists(twin) or os.path.getmtime(twin) < os.path.getmtime(CLI):
+        if os.path.lexists(twin):
+            os.remove(twin)
+        shutil.copy2(CLI, twin)
     return CLI
 
 

@@ -7,6 +7,9 @@
 // algorithmic GB/s.  B is filled with ones as in the reference (:180-182); A's values are all ones
 // (the file has none) unless --values=gcn.
 //
+// Installed under a name that ends in "_fp16" (the build links MergePathSpMM_fp16 to the same program) it is the
+// twin of the reference's fp16 program: the same argv, fp16 storage unless --dtype says otherwise.
+//
 // Options (all optional, after the positionals):
 //   --dtype=f32|f16   --values=unit|gcn   --check   --device=K
 //   --gpus=G          row slabs of equal (nnz + 4*rows) over G devices of this node (mps_multi_*)
@@ -67,6 +70,11 @@ int main(int argc, char *argv[]) {
     }
     const int dim = atoi(argv[2]), cost = atoi(argv[3]), tpw = atoi(argv[4]), repeat = atoi(argv[5]);
     Options o;
+    {
+        const std::string self(argv[0]);
+        const std::string tail("_fp16");
+        if (self.size() >= tail.size() && self.compare(self.size() - tail.size(), tail.size(), tail) == 0) o.dtype = "f16";
+    }
     for (int i = 6; i < argc; ++i)
         if (!parse_option(argv[i], o)) { fprintf(stderr, "unknown or malformed option %s\n", argv[i]); return 2; }
 

@@ -54,6 +54,17 @@ def test_runs_and_checks_on_the_gpu(cli, c1_file, cuda, extra):
 
 
 @pytest.mark.gpu
+def test_fp16_twin_program_defaults_to_fp16_storage(cli, c1_file, cuda):
+    """MergePathSpMM_fp16: the reference's second program (src/MergePathSpMM_fp16.cu:111-125), same argv."""
+    path, n, nnz = c1_file
+    r = subprocess.run([cli + "_fp16", path, "32", "8", "1", "2", "--check", "--values=gcn"], capture_output=True, text=True)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "dtype: f16" in r.stdout and "check: 0 elements outside tolerance" in r.stdout
+    r = subprocess.run([cli + "_fp16", path, "32", "8"], capture_output=True, text=True)
+    assert r.returncode == 255
+
+
+@pytest.mark.gpu
 def test_multi_gpu_with_nccl_gather(cli, c1_file, cuda):
     import torch
     if torch.cuda.device_count() < 2:
