@@ -377,9 +377,6 @@ __device__ __forceinline__ void block_fixup(const TileParams &p, int e, int chai
 // lanes with the accumulator kept in registers across the chunk boundaries inside the unit.
 // SCALED: the value of non-zero (i, j) is row_scale[i] * col_scale[j] instead of a stored value (a kernel of
 // its own so that the plain product carries none of its selects).
-#ifndef MPS_PREFETCH_B
-#define MPS_PREFETCH_B 0
-#endif
 template <typename T, int VEC, int GL, int U, int BLOCK, bool SCALED>
 __global__ void __launch_bounds__(BLOCK, kWarpsPerSm * 32 / BLOCK) spmm_tile_kernel(const TileParams p) {
     constexpr int kBlock = BLOCK;
@@ -520,19 +517,6 @@ __global__ void __launch_bounds__(BLOCK, kWarpsPerSm * 32 / BLOCK) spmm_tile_ker
                 else a[u] = has_val ? Lane<T, VEC>::value(w_val[k + u]) : Lane<T, VEC>::one();
                 if (active) b[u] = Lane<T, VEC>::load(Bl + (size_t)ci * dim);
             }
-#if MPS_PREFETCH_B
-            if (k + 2 * U <= y1 && active) {  // rows of the next batch, on their way while this one is folded
-#pragma unroll
-                for (int u = 0; u < U; ++u) {
-                    const T *q = Bl + (size_t)(unsigned)w_col[k + U + u] * dim;
-#if MPS_PREFETCH_B == 1
-                    asm volatile("prefetch.global.L2 [%0];" ::"l"(q));
-#else
-                    asm volatile("prefetch.global.L1 [%0];" ::"l"(q));
-#endif
-                }
-            }
-#endif
             while (next_mark <= k) end_row();
             if (next_mark >= k + U) {  // no row ends inside the batch
                 if (active) {
