@@ -333,8 +333,14 @@ static int spmm_typed(mps_plan *p, const TileParams &tp, cudaStream_t st) {
     if (rc != MPS_OK) return rc;
     if (prof) { MPS_CUDA(cudaEventRecord(p->prof_ev[2 * p->prof_used + 1], st)); ++p->prof_used; }
     if (!p->fused && p->n_tiles > 1) {
-        const int warps = p->n_tiles - 1;
-        fixup_warp_kernel<T><<<(warps + 7) / 8, 256, 0, st>>>(tp);
+        const long long tiles = p->n_tiles - 1;
+        const int quads = p->dim / 4;  // lanes a row needs at four columns each
+        auto blocks = [&](int lanes) { return (unsigned)((tiles * lanes + 255) / 256); };
+        if (p->vec == 1) fixup_warp_kernel<T, 32, false><<<blocks(32), 256, 0, st>>>(tp);
+        else if (quads <= 4) fixup_warp_kernel<T, 4, true><<<blocks(4), 256, 0, st>>>(tp);
+        else if (quads <= 8) fixup_warp_kernel<T, 8, true><<<blocks(8), 256, 0, st>>>(tp);
+        else if (quads <= 16) fixup_warp_kernel<T, 16, true><<<blocks(16), 256, 0, st>>>(tp);
+        else fixup_warp_kernel<T, 32, true><<<blocks(32), 256, 0, st>>>(tp);
         MPS_CUDA(cudaGetLastError());
     }
     if (p->n_long > 0) {

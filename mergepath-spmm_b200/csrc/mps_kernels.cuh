@@ -662,15 +662,46 @@ __global__ void fixup_plan_kernel(const int2 *__restrict__ xy, const int *__rest
     consumer[t] = e;
 }
 
-// Cross-tile fix-up as a kernel of its own (large problems): one warp per tile that ends a carried-in
-// row, same sums in the same order as block_fixup in the tile kernel.
-template <typename T>
+__device__ __forceinline__ void store_c4(float *p, const float4 v) { *reinterpret_cast<float4 *>(p) = v; }
+__device__ __forceinline__ void store_c4(__half *p, const float4 v) {
+    const __half2 lo = __floats2half2_rn(v.x, v.y), hi = __floats2half2_rn(v.z, v.w);
+    uint2 w;
+    w.x = *reinterpret_cast<const unsigned *>(&lo);
+    w.y = *reinterpret_cast<const unsigned *>(&hi);
+    *reinterpret_cast<uint2 *>(p) = w;
+}
+
+// Cross-tile fix-up as a kernel of its own (large problems): L lanes per tile that ends a carried-in row,
+// same sums in the same order as block_fixup in the tile kernel.  V4 (dim a multiple of 4): a lane takes four
+// columns at a time, so L = dim/4 lanes finish a row in one pass and a warp serves 32/L tiles.
+template <typename T, int L, bool V4>
 __global__ void fixup_warp_kernel(const TileParams p) {
-    const int t = 1 + (blockIdx.x * blockDim.x + threadIdx.x) / 32;
+    const int gid = blockIdx.x * blockDim.x + threadIdx.x;
+    const int t = 1 + gid / L, lane = gid % L;
     if (t >= p.n_tiles) return;
     const int n = __ldg(p.need + t);
     if (n <= 0 || n - 1 > p.very_long) return;
-    block_fixup<T, 32>(p, t, n - 1, 0, p.dim, (int)(threadIdx.x % 32));
+    const int chain = n - 1;
+    if (!V4 || chain > p.long_chain) {
+        block_fixup<T, L>(p, t, chain, 0, p.dim, lane);
+        return;
+    }
+    const int row = __ldg(p.tile_xy + t).x - 1;
+    const size_t dim = (size_t)p.dim;
+    for (int j = lane * 4; j < p.dim; j += L * 4) {
+        float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        for (int q = t - chain; q < t; ++q) {
+            const float4 c = __ldcg(reinterpret_cast<const float4 *>(p.tcarry + (size_t)q * dim + j));
+            sum.x += c.x; sum.y += c.y; sum.z += c.z; sum.w += c.w;
+        }
+        const float4 h = __ldcg(reinterpret_cast<const float4 *>(p.thead + (size_t)t * dim + j));
+        sum.x += h.x; sum.y += h.y; sum.z += h.z; sum.w += h.w;
+        if (p.row_scale) {
+            const float r = __ldg(p.row_scale + row);
+            sum.x *= r; sum.y *= r; sum.z *= r; sum.w *= r;
+        }
+        store_c4(static_cast<T *>(p.C) + (size_t)row * dim + j, sum);
+    }
 }
 
 // Chains longer than very_long (a row spanning thousands of tiles): one block of kStrands warps per
