@@ -102,7 +102,7 @@ static int pow2_at_least(int v) {
 }
 
 static const int kSmemTargetPer256 = 64 * 1024;   // three tile blocks per SM, which the registers allow anyway
-static const int kVeryLongFused = 8192;       // chain length (tiles) above which even the fused form hands a row to fixup_long_kernel
+static const int kVeryLongFused = 8192;       // chain length (tiles) above which even the fused form hands a row to a block of fixup_kernel
 static const int kFuseMaxTiles = 2048;       // up to here a second launch costs more than the fence the fused fix-up needs
 static const int kTilesPerSm = 6;            // smaller tiles rather than idle SMs on small problems
 static const int kUnitItems = 272;           // merge items one lane group walks per tile, at most
@@ -141,8 +141,8 @@ static int plan_layout(mps_plan *p) {
         return fail(MPS_ERR_UNSUPPORTED, "tile of %d chunks x %d items needs %d bytes of shared memory", p->nch, p->ipt, p->smem_bytes);
     p->n_tiles = (p->n_chunks + p->nch - 1) / p->nch;
     if (!p->user_fused) p->fused = (long long)p->n_tiles * p->n_col_slabs <= kFuseMaxTiles ? 1 : 0;
-    // a tile block sums chains of any realistic length itself; a lone warp of fixup_warp_kernel should not:
-    // there every strand-order chain goes to fixup_long_kernel (512 threads per row)
+    // a tile block sums chains of any realistic length itself; a lone lane group of fixup_kernel should not:
+    // there every strand-order chain goes to a whole block of fixup_kernel (512 threads per row)
     p->very_long = p->fused ? kVeryLongFused : p->long_chain;
     return MPS_OK;
 }
@@ -332,20 +332,18 @@ static int spmm_typed(mps_plan *p, const TileParams &tp, cudaStream_t st) {
     else rc = launch_tile_gl<T, FULLVEC>(p, tp, st);
     if (rc != MPS_OK) return rc;
     if (prof) { MPS_CUDA(cudaEventRecord(p->prof_ev[2 * p->prof_used + 1], st)); ++p->prof_used; }
-    if (!p->fused && p->n_tiles > 1) {
-        const long long tiles = p->n_tiles - 1;
+    // one launch after the tile kernel: a block per row whose chain is too long for anyone else, then (large
+    // problems, where the tile kernel does not fix up across tiles itself) dim/4 lanes per remaining tile
+    const long long tiles = (!p->fused && p->n_tiles > 1) ? p->n_tiles - 1 : 0;
+    if (tiles > 0 || p->n_long > 0) {
+        const int threads = kStrands * 32;
         const int quads = p->dim / 4;  // lanes a row needs at four columns each
-        auto blocks = [&](int lanes) { return (unsigned)((tiles * lanes + 255) / 256); };
-        if (p->vec == 1) fixup_warp_kernel<T, 32, false><<<blocks(32), 256, 0, st>>>(tp);
-        else if (quads <= 4) fixup_warp_kernel<T, 4, true><<<blocks(4), 256, 0, st>>>(tp);
-        else if (quads <= 8) fixup_warp_kernel<T, 8, true><<<blocks(8), 256, 0, st>>>(tp);
-        else if (quads <= 16) fixup_warp_kernel<T, 16, true><<<blocks(16), 256, 0, st>>>(tp);
-        else fixup_warp_kernel<T, 32, true><<<blocks(32), 256, 0, st>>>(tp);
-        MPS_CUDA(cudaGetLastError());
-    }
-    if (p->n_long > 0) {
-        fixup_long_kernel<T><<<p->n_long, kStrands * 32, 0, st>>>(p->d_tile_xy, tp.rp, p->d_tcarry, p->d_thead, static_cast<T *>(tp.C),
-                                                                 p->d_long_list, p->dim, tp.row_scale);
+        auto blocks = [&](int lanes) { return (unsigned)(p->n_long + (tiles * lanes + threads - 1) / threads); };
+        if (p->vec == 1) fixup_kernel<T, 32, false><<<blocks(32), threads, 0, st>>>(tp, p->d_long_list, p->n_long);
+        else if (quads <= 4) fixup_kernel<T, 4, true><<<blocks(4), threads, 0, st>>>(tp, p->d_long_list, p->n_long);
+        else if (quads <= 8) fixup_kernel<T, 8, true><<<blocks(8), threads, 0, st>>>(tp, p->d_long_list, p->n_long);
+        else if (quads <= 16) fixup_kernel<T, 16, true><<<blocks(16), threads, 0, st>>>(tp, p->d_long_list, p->n_long);
+        else fixup_kernel<T, 32, true><<<blocks(32), threads, 0, st>>>(tp, p->d_long_list, p->n_long);
         MPS_CUDA(cudaGetLastError());
     }
     return MPS_OK;
@@ -433,7 +431,7 @@ extern "C" int mps_plan_info(const mps_plan *p, int64_t what[16]) {
     what[0] = p->n_chunks; what[1] = p->ipt; what[2] = p->nch; what[3] = p->n_tiles;
     what[4] = p->gl; what[5] = p->vec; what[6] = p->unroll; what[7] = p->smem_bytes;
     what[8] = p->n_long; what[9] = p->tpw_effective;
-    what[10] = 1 + ((!p->fused && p->n_tiles > 1) ? 1 : 0) + (p->n_long > 0 ? 1 : 0);
+    what[10] = 1 + (((!p->fused && p->n_tiles > 1) || p->n_long > 0) ? 1 : 0);
     what[11] = p->long_chain; what[12] = p->cpu; what[13] = p->block / p->gl; what[14] = p->block; what[15] = p->very_long;
     return MPS_OK;
 }

@@ -50,7 +50,7 @@ struct TileParams {
     const int *need;      // per tile: contributions its cross-tile fix-up waits for (0 = none)
     int *cnt;             // per (column slab, tile): contributions that have arrived; zero between launches
     int long_chain, very_long;
-    int fused;  // 1: the tile kernel signals and performs the cross-tile fix-up itself; 0: fixup_warp_kernel follows
+    int fused;  // 1: the tile kernel signals and performs the cross-tile fix-up itself; 0: fixup_kernel follows
     long long total;  // N + 1 + nnz
     int n_rows, nnz, dim;
     int ipt, nch, cpu, n_tiles;  // items per chunk, chunks per tile, chunks per unit
@@ -594,7 +594,7 @@ __global__ void __launch_bounds__(BLOCK, kWarpsPerSm * 32 / BLOCK) spmm_tile_ker
     // every contribution (a tile's carry, the ending tile's head) bumps the counter of the tile that ends
     // the row; the block that brings the count to `need` finds everything in place and sums it, in the
     // fixed order.  No block ever waits for another.  The fence below has to wait for this thread's
-    // stores to C as well, which is why large problems run fixup_warp_kernel after the tile kernel instead.
+    // stores to C as well, which is why large problems run fixup_kernel after the tile kernel instead.
     if (!p.fused) return;
     __threadfence();  // this thread's tcarry / thead stores are visible device-wide before the count moves
     __syncthreads();
@@ -620,7 +620,7 @@ __global__ void __launch_bounds__(BLOCK, kWarpsPerSm * 32 / BLOCK) spmm_tile_ker
         const int e = s_todo[i];
         if (e < 0) continue;
         const int chain = __ldg(p.need + e) - 1;
-        if (chain <= p.very_long) block_fixup<T, kBlock>(p, e, chain, col0, col1, tid);  // longer chains: fixup_long_kernel
+        if (chain <= p.very_long) block_fixup<T, kBlock>(p, e, chain, col0, col1, tid);  // longer chains: fixup_kernel, after this one
     }
 }
 
@@ -662,6 +662,37 @@ __global__ void fixup_plan_kernel(const int2 *__restrict__ xy, const int *__rest
     consumer[t] = e;
 }
 
+// Chains longer than very_long (a row spanning thousands of tiles): one block of kStrands warps per
+// listed tile (the first blocks of fixup_kernel).  Strand g adds carries s+g, s+g+16, ... in order, then strand 0
+// adds the strands in order and the tile's head last - the same order block_fixup uses.
+template <typename T>
+__device__ __forceinline__ void fixup_long_block(const int2 *__restrict__ xy, const int *__restrict__ rp, const float *__restrict__ tcarry,
+                                                 const float *__restrict__ thead, T *__restrict__ C, int t, int dim,
+                                                 const float *__restrict__ row_scale) {
+    __shared__ float part[kStrands][32];
+    const int g = threadIdx.x / 32, lane = threadIdx.x % 32;
+    int s;
+    const int row = fixup_candidate(xy, rp, t, s);
+    if (row < 0) return;  // cannot happen for a listed tile
+    for (int j0 = 0; j0 < dim; j0 += 32) {
+        const int j = j0 + lane;
+        float sg = 0.0f;
+        if (j < dim)
+            for (int q = s + g; q < t; q += kStrands) sg += tcarry[(size_t)q * dim + j];
+        part[g][lane] = sg;
+        __syncthreads();
+        if (g == 0 && j < dim) {
+            float sum = 0.0f;
+#pragma unroll
+            for (int k = 0; k < kStrands; ++k) sum += part[k][lane];
+            sum += thead[(size_t)t * dim + j];
+            if (row_scale) sum *= __ldg(row_scale + row);
+            store_c(C + (size_t)row * dim + j, sum);
+        }
+        __syncthreads();
+    }
+}
+
 __device__ __forceinline__ void store_c4(float *p, const float4 v) { *reinterpret_cast<float4 *>(p) = v; }
 __device__ __forceinline__ void store_c4(__half *p, const float4 v) {
     const __half2 lo = __floats2half2_rn(v.x, v.y), hi = __floats2half2_rn(v.z, v.w);
@@ -671,12 +702,19 @@ __device__ __forceinline__ void store_c4(__half *p, const float4 v) {
     *reinterpret_cast<uint2 *>(p) = w;
 }
 
-// Cross-tile fix-up as a kernel of its own (large problems): L lanes per tile that ends a carried-in row,
-// same sums in the same order as block_fixup in the tile kernel.  V4 (dim a multiple of 4): a lane takes four
-// columns at a time, so L = dim/4 lanes finish a row in one pass and a warp serves 32/L tiles.
+// Cross-tile fix-up after the tile kernel, one launch of kStrands * 32 threads per block:
+//   blocks [0, n_long): one block per listed tile whose chain exceeds very_long (fixup_long_block);
+//   the other blocks (large problems only; none when the tile kernel does the fix-up itself): L lanes per
+//   tile that ends a carried-in row, same sums in the same order as block_fixup in the tile kernel.  V4 (dim a
+//   multiple of 4): a lane takes four columns at a time, so L = dim/4 lanes finish a row in one pass and a warp
+//   serves 32/L tiles.
 template <typename T, int L, bool V4>
-__global__ void fixup_warp_kernel(const TileParams p) {
-    const int gid = blockIdx.x * blockDim.x + threadIdx.x;
+__global__ void __launch_bounds__(kStrands * 32) fixup_kernel(const TileParams p, const int *__restrict__ long_list, int n_long) {
+    if ((int)blockIdx.x < n_long) {
+        fixup_long_block<T>(p.tile_xy, p.rp, p.tcarry, p.thead, static_cast<T *>(p.C), long_list[blockIdx.x], p.dim, p.row_scale);
+        return;
+    }
+    const int gid = ((int)blockIdx.x - n_long) * (kStrands * 32) + (int)threadIdx.x;
     const int t = 1 + gid / L, lane = gid % L;
     if (t >= p.n_tiles) return;
     const int n = __ldg(p.need + t);
@@ -701,39 +739,6 @@ __global__ void fixup_warp_kernel(const TileParams p) {
             sum.x *= r; sum.y *= r; sum.z *= r; sum.w *= r;
         }
         store_c4(static_cast<T *>(p.C) + (size_t)row * dim + j, sum);
-    }
-}
-
-// Chains longer than very_long (a row spanning thousands of tiles): one block of kStrands warps per
-// listed tile, after the tile kernel.  Strand g adds carries s+g, s+g+16, ... in order, then strand 0
-// adds the strands in order and the tile's head last - the same order block_fixup uses.
-template <typename T>
-__global__ void __launch_bounds__(kStrands * 32) fixup_long_kernel(const int2 *__restrict__ xy, const int *__restrict__ rp,
-                                                                    const float *__restrict__ tcarry, const float *__restrict__ thead,
-                                                                    T *__restrict__ C, const int *__restrict__ list, int dim,
-                                                                    const float *__restrict__ row_scale) {
-    __shared__ float part[kStrands][32];
-    const int t = list[blockIdx.x];
-    const int g = threadIdx.x / 32, lane = threadIdx.x % 32;
-    int s;
-    const int row = fixup_candidate(xy, rp, t, s);
-    if (row < 0) return;  // cannot happen for a listed tile
-    for (int j0 = 0; j0 < dim; j0 += 32) {
-        const int j = j0 + lane;
-        float sg = 0.0f;
-        if (j < dim)
-            for (int q = s + g; q < t; q += kStrands) sg += tcarry[(size_t)q * dim + j];
-        part[g][lane] = sg;
-        __syncthreads();
-        if (g == 0 && j < dim) {
-            float sum = 0.0f;
-#pragma unroll
-            for (int k = 0; k < kStrands; ++k) sum += part[k][lane];
-            sum += thead[(size_t)t * dim + j];
-            if (row_scale) sum *= __ldg(row_scale + row);
-            store_c(C + (size_t)row * dim + j, sum);
-        }
-        __syncthreads();
     }
 }
 

@@ -177,8 +177,8 @@ def test_long_rows_take_the_strand_order(mps, orc, cuda):
     B = rng.uniform(-1, 1, (6000, 64)).astype(np.float32)
     for fused in (1, 0):
         got, info = _run(mps, cuda, rp, col, None, B, 1, dict(chunks_per_unit=1, fused_fixup=fused))
-        # fused: the last-arriving tile block sums the 150-tile chain; unfused: fix-up kernel + long-row kernel
-        assert (info["kernels_per_call"], info["long_rows"]) == ((1, 0) if fused else (3, 1))
+        # fused: the last-arriving tile block sums the 150-tile chain; unfused: one fix-up launch whose first block takes the long row
+        assert (info["kernels_per_call"], info["long_rows"]) == ((1, 0) if fused else (2, 1))
         assert 5000 // (info["chunks_per_tile"] * info["items_per_chunk"]) > info["long_chain"]
         _check(orc, rp, col, None, B, got, info, 1, 1e-5)
 
@@ -189,7 +189,7 @@ def test_rows_spanning_thousands_of_tiles_take_the_second_kernel(mps, orc, cuda)
     val = rng.uniform(-1, 1, len(col)).astype(np.float32)
     B = rng.uniform(-1, 1, (90000, 64)).astype(np.float32)
     got, info = _run(mps, cuda, rp, col, val, B, 1, dict(chunks_per_unit=1))
-    assert info["long_rows"] == 1 and info["kernels_per_call"] == 3  # 10,000+ tiles: fix-up kernel of its own, plus the long-row kernel
+    assert info["long_rows"] == 1 and info["kernels_per_call"] == 2  # 10,000+ tiles: one fix-up launch after the tile kernel, its first block for the long row
     assert 80000 // (info["chunks_per_tile"] * info["items_per_chunk"]) > info["very_long"]
     _check(orc, rp, col, val, B, got, info, 1, 1e-5)
 
@@ -262,7 +262,7 @@ def test_launches_can_be_captured_in_a_cuda_graph(mps, graphs, cuda, which):
     d_B = _dev(graphs.dense_uniform(n, 32, seed=6), cuda)
     plan = mps.Plan(n, nnz, 32, mps.F32, 16, device=cuda)
     plan.partition(d_rp)
-    assert plan.info()["kernels_per_call"] == (1 if which == "small_fused" else 3 if plan.info()["long_rows"] else 2)
+    assert plan.info()["kernels_per_call"] == (1 if which == "small_fused" else 2)
     eager = plan.spmm(d_rp, d_col, d_val, d_B).clone()
     plan.sync_check()
     out = torch.zeros_like(eager)
