@@ -1,6 +1,6 @@
 // mps_spmm_noalloc: the SpMM for callers that must not allocate device memory.
 //
-// Who cannot allocate: code that runs inside somebody else's memory budget or under a rule that
+// Who cannot allocate: code that runs inside somebody else's memory allotment or under a rule that
 // forbids the allocator at call time - a plugin handed a fixed arena by its host framework, a
 // service whose device memory is fully pre-committed at start-up, a latency-critical loop where
 // cudaMalloc's implicit device synchronisation is not acceptable.  Such a caller still owns A, B
