@@ -273,81 +273,12 @@ extern "C" int mps_plan_partition(mps_plan *p, const int32_t *d_row_ptr, void *s
     return MPS_OK;
 }
 
-template <typename T, int VEC, int GL, int U, int BLOCK, bool SCALED>
-static int launch_tile_k(const mps_plan *p, const TileParams &tp, cudaStream_t st) {
-    auto kern = spmm_tile_kernel<T, VEC, GL, U, BLOCK, SCALED>;
-    if (p->smem_bytes > 48 * 1024) MPS_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, p->smem_bytes));
-    dim3 grid((unsigned)p->n_tiles, (unsigned)p->n_col_slabs);
-    kern<<<grid, BLOCK, p->smem_bytes, st>>>(tp);
-    MPS_CUDA(cudaGetLastError());
-    return MPS_OK;
-}
-
-template <typename T, int VEC, int GL, int U, int BLOCK>
-static int launch_tile(const mps_plan *p, const TileParams &tp, cudaStream_t st) {
-    if constexpr (BLOCK < GL) {
-        return fail(MPS_ERR_STATE, "block of %d threads cannot hold a group of %d lanes", BLOCK, GL);
-    } else {
-        if constexpr (sizeof(T) == 4) {  // the scaled product exists for fp32 plans only
-            if (tp.col_scale || tp.row_scale) return launch_tile_k<T, VEC, GL, U, BLOCK, true>(p, tp, st);
-        }
-        return launch_tile_k<T, VEC, GL, U, BLOCK, false>(p, tp, st);
-    }
-}
-
-template <typename T, int VEC, int GL, int U>
-static int launch_tile_b(const mps_plan *p, const TileParams &tp, cudaStream_t st) {
-    switch (p->block) {
-        case 64: return launch_tile<T, VEC, GL, U, 64>(p, tp, st);
-        case 128: return launch_tile<T, VEC, GL, U, 128>(p, tp, st);
-        case 256: return launch_tile<T, VEC, GL, U, 256>(p, tp, st);
-    }
-    return fail(MPS_ERR_STATE, "no kernel for blocks of %d threads", p->block);
-}
-
-template <typename T, int VEC, int GL>
-static int launch_tile_u(const mps_plan *p, const TileParams &tp, cudaStream_t st) {
-    if (p->unroll == 8) return launch_tile_b<T, VEC, GL, 8>(p, tp, st);
-    return launch_tile_b<T, VEC, GL, 4>(p, tp, st);
-}
-
-template <typename T, int VEC>
-static int launch_tile_gl(const mps_plan *p, const TileParams &tp, cudaStream_t st) {
-    switch (p->gl) {
-        case 2: return launch_tile_u<T, VEC, 2>(p, tp, st);
-        case 4: return launch_tile_u<T, VEC, 4>(p, tp, st);
-        case 8: return launch_tile_u<T, VEC, 8>(p, tp, st);
-        case 16: return launch_tile_u<T, VEC, 16>(p, tp, st);
-        case 32: return launch_tile_u<T, VEC, 32>(p, tp, st);
-    }
-    return fail(MPS_ERR_STATE, "no kernel for %d lanes per chunk", p->gl);
-}
-
-template <typename T, int FULLVEC>
-static int spmm_typed(mps_plan *p, const TileParams &tp, cudaStream_t st) {
-    int rc;
-    const bool prof = p->profiling && p->prof_used < kProfSlots;
-    if (prof) MPS_CUDA(cudaEventRecord(p->prof_ev[2 * p->prof_used], st));
-    if (p->vec == 1) rc = launch_tile_b<T, 1, 32, 4>(p, tp, st);
-    else rc = launch_tile_gl<T, FULLVEC>(p, tp, st);
-    if (rc != MPS_OK) return rc;
-    if (prof) { MPS_CUDA(cudaEventRecord(p->prof_ev[2 * p->prof_used + 1], st)); ++p->prof_used; }
-    // one launch after the tile kernel: a block per row whose chain is too long for anyone else, then (large
-    // problems, where the tile kernel does not fix up across tiles itself) dim/4 lanes per remaining tile
-    const long long tiles = (!p->fused && p->n_tiles > 1) ? p->n_tiles - 1 : 0;
-    if (tiles > 0 || p->n_long > 0) {
-        const int threads = kStrands * 32;
-        const int quads = p->dim / 4;  // lanes a row needs at four columns each
-        auto blocks = [&](int lanes) { return (unsigned)(p->n_long + (tiles * lanes + threads - 1) / threads); };
-        if (p->vec == 1) fixup_kernel<T, 32, false><<<blocks(32), threads, 0, st>>>(tp, p->d_long_list, p->n_long);
-        else if (quads <= 4) fixup_kernel<T, 4, true><<<blocks(4), threads, 0, st>>>(tp, p->d_long_list, p->n_long);
-        else if (quads <= 8) fixup_kernel<T, 8, true><<<blocks(8), threads, 0, st>>>(tp, p->d_long_list, p->n_long);
-        else if (quads <= 16) fixup_kernel<T, 16, true><<<blocks(16), threads, 0, st>>>(tp, p->d_long_list, p->n_long);
-        else fixup_kernel<T, 32, true><<<blocks(32), threads, 0, st>>>(tp, p->d_long_list, p->n_long);
-        MPS_CUDA(cudaGetLastError());
-    }
-    return MPS_OK;
-}
+namespace mps {
+// one multiply on a partitioned plan, defined in mps_spmm_f32.cu / mps_spmm_f32_scaled.cu / mps_spmm_f16.cu
+int spmm_f32(mps_plan *p, const TileParams &tp, cudaStream_t st);
+int spmm_f32_scaled(mps_plan *p, const TileParams &tp, cudaStream_t st);
+int spmm_f16(mps_plan *p, const TileParams &tp, cudaStream_t st);
+}  // namespace mps
 
 static int spmm_launch(mps_plan *p, const int32_t *d_row_ptr, const int32_t *d_col_idx, const void *d_val, const float *d_row_scale,
                        const float *d_col_scale, const void *d_B, void *d_C, void *stream) {
@@ -370,8 +301,8 @@ static int spmm_launch(mps_plan *p, const int32_t *d_row_ptr, const int32_t *d_c
     const bool aligned16 = !((uintptr_t)d_row_ptr % 16) && !((uintptr_t)d_col_idx % 16) && !((uintptr_t)d_val % 16);
     tp.bulk = (p->bulk && aligned16) ? 1 : 0;
     cudaStream_t st = (cudaStream_t)stream;
-    if (p->dtype == MPS_F16) return spmm_typed<__half, 8>(p, tp, st);
-    return spmm_typed<float, 4>(p, tp, st);
+    if (p->dtype == MPS_F16) return spmm_f16(p, tp, st);
+    return (d_row_scale || d_col_scale) ? spmm_f32_scaled(p, tp, st) : spmm_f32(p, tp, st);
 }
 
 extern "C" int mps_spmm(mps_plan *p, const int32_t *d_row_ptr, const int32_t *d_col_idx, const void *d_val, const void *d_B,

@@ -74,7 +74,7 @@ __device__ __forceinline__ int2 merge_path_search_global(long long diag, const i
 }
 
 // count coordinates for diagonals min(step * t, total), t = 0..count-1
-__global__ void partition_kernel(const int *__restrict__ rp, int n_rows, int nnz, long long step, long long total,
+static __global__ void partition_kernel(const int *__restrict__ rp, int n_rows, int nnz, long long step, long long total,
                                  int count, int2 *__restrict__ out) {
     int t = blockIdx.x * blockDim.x + threadIdx.x;
     if (t >= count) return;
@@ -84,7 +84,7 @@ __global__ void partition_kernel(const int *__restrict__ rp, int n_rows, int nnz
 }
 
 // The reference's six per-chunk arrays (src/MergePathSpMM.cu:336-376), one thread per chunk.
-__global__ void schedule_kernel(const int *__restrict__ rp, int n_rows, int nnz, long long ipt, long long total,
+static __global__ void schedule_kernel(const int *__restrict__ rp, int n_rows, int nnz, long long ipt, long long total,
                                 int n_chunks, int *__restrict__ six) {
     int t = blockIdx.x * blockDim.x + threadIdx.x;
     if (t >= n_chunks) return;
@@ -630,7 +630,7 @@ __global__ void __launch_bounds__(BLOCK, kWarpsPerSm * 32 / BLOCK) spmm_tile_ker
 // Plan time, one thread per tile: how many contributions the tile's cross-tile fix-up waits for
 // (its own head plus one carry per tile of the chain), which tile consumes this tile's carry, and the
 // list of tiles whose chain is too long to be summed by one tile block (very_long).
-__global__ void fixup_plan_kernel(const int2 *__restrict__ xy, const int *__restrict__ rp, int n_tiles, int very_long,
+static __global__ void fixup_plan_kernel(const int2 *__restrict__ xy, const int *__restrict__ rp, int n_tiles, int very_long,
                                   int *__restrict__ consumer, int *__restrict__ need, int *__restrict__ list, int *__restrict__ count,
                                   int capacity) {
     const int t = blockIdx.x * blockDim.x + threadIdx.x;
