@@ -89,3 +89,25 @@ def test_slab_bounds_match_oracle_and_balance(mps, orc):
         assert np.array_equal(mps.slab_bounds(rp, g, "items", 0), mps.slab_bounds(rp, g))
     sl = mps.slab_rebase(rp, int(b[1]), int(b[2]))
     assert sl[0] == 0 and sl[-1] == rp[b[2]] - rp[b[1]]
+
+
+def test_header_is_plain_c_and_links_from_a_c_program(mps, tmp_path):
+    """The boundary is a C ABI: include/mps.h compiles as C99 and a C program links against the library."""
+    import subprocess
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    src = tmp_path / "use_mps.c"
+    src.write_text('#include <stdio.h>\n#include "mps.h"\n'
+                   'int main(void) {\n'
+                   '    int32_t p = 0, ipt = 0;\n'
+                   '    if (mps_chunk_count(4096, 100882, 8, &p, &ipt) != MPS_OK) return 1;\n'
+                   '    printf("%d %d %s\\n", (int)p, (int)ipt, mps_version());\n'
+                   '    return mps_csr_load("/nonexistent.csr", 1, (mps_csr *)0) == MPS_OK;\n'
+                   '}\n')
+    libdir = os.path.join(root, "mergepath-spmm_b200", "lib")
+    exe = tmp_path / "use_mps"
+    subprocess.run(["gcc", "-std=c99", "-Wall", "-Werror", "-pedantic", "-I" + os.path.join(root, "include"), "-o", str(exe), str(src),
+                    "-L" + libdir, "-lmps_b200", "-Wl,-rpath," + libdir], check=True)
+    r = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    n_chunks, ipt, _ = r.stdout.split(None, 2)
+    assert (int(n_chunks), int(ipt)) == mps.chunk_count(4096, 100882, 8)
