@@ -7,6 +7,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <initializer_list>
 #include <new>
 #include <string>
 
@@ -425,8 +426,8 @@ static int ws_reserve(int i, size_t bytes) {
 
 extern "C" void mps_host_workspace_release(void) { g_ws.release(); }
 
-extern "C" int mps_spmm_host(int32_t n_rows, int32_t n_cols, int32_t nnz, int32_t dim, int dtype, int32_t cost, int32_t threads_per_warp,
-                             const int32_t *row_ptr, const int32_t *col_idx, const void *val, const void *B, void *C) {
+static int host_call(int32_t n_rows, int32_t n_cols, int32_t nnz, int32_t dim, int dtype, int32_t cost, int32_t threads_per_warp,
+                     const int32_t *row_ptr, const int32_t *col_idx, const void *val, const void *B, void *C) {
     if (!row_ptr || !B || !C || (!col_idx && nnz > 0)) return fail(MPS_ERR_ARG, "mps_spmm_host: NULL argument");
     if (dim < 1 || cost < 1 || n_cols < 0) return fail(MPS_ERR_ARG, "mps_spmm_host: dim and cost must be >= 1, n_cols >= 0");
     if (dtype != MPS_F32 && dtype != MPS_F16) return fail(MPS_ERR_ARG, "mps_spmm_host: unknown dtype %d", dtype);
@@ -526,6 +527,18 @@ extern "C" int mps_spmm_host(int32_t n_rows, int32_t n_cols, int32_t nnz, int32_
     for (int s = 0; s < n_slabs; ++s)
         if (int rc = mps_plan_sync_check(g_ws.plan[s], s_work)) return rc;
     return MPS_OK;
+}
+
+extern "C" int mps_spmm_host(int32_t n_rows, int32_t n_cols, int32_t nnz, int32_t dim, int dtype, int32_t cost, int32_t threads_per_warp,
+                             const int32_t *row_ptr, const int32_t *col_idx, const void *val, const void *B, void *C) {
+    const int rc = host_call(n_rows, n_cols, nnz, dim, dtype, cost, threads_per_warp, row_ptr, col_idx, val, B, C);
+    if (rc != MPS_OK) {
+        // a step failed with copies possibly still queued on the caller's buffers: let them drain before the caller
+        // may free those buffers (the message of the failure stays the one reported)
+        for (cudaStream_t st : {g_ws.s_in, g_ws.s_b, g_ws.s_work, g_ws.s_out})
+            if (st) cudaStreamSynchronize(st);
+    }
+    return rc;
 }
 
 // ------------------------------------------------------------------------------------- slabs (host)
