@@ -1,4 +1,4 @@
-"""The N > 1 host logic on CPU ranks (gloo, world size 2): slab bounds, rebasing, the padded
+"""The N > 1 host logic on CPU ranks (gloo, world sizes 2 and 3): slab bounds, rebasing, the padded
 all-gather of C.  The multiply itself is the GPU's job; here each rank fills its slab with the
 oracle's fp64 loop (as the checker's stand-in) so that the plumbing can be verified without a GPU."""
 import os
@@ -59,8 +59,8 @@ def _worker(rank, world, port, out_dir):
 
 
 @pytest.mark.timeout(300)
-def test_two_cpu_ranks_slab_and_gather(tmp_path):
-    world = 2
+@pytest.mark.parametrize("world", [2, 3])
+def test_cpu_ranks_slab_and_gather(tmp_path, world):
     mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
     for r in range(world):
         assert open(tmp_path / f"rank{r}.ok").read() == "1"
