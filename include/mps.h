@@ -61,12 +61,19 @@ typedef struct {
 
 /* Replaces the two-pass getline/stringstream/stoi loader (src/MergePathSpMM.cu:119-173).
  * Same grammar: line 1 = row_ptr, line 2 = col_idx, decimal integers separated by ',', trailing
- * ',' optional, final newline optional, blanks before a number allowed, '\r' rejected.
+ * ',' optional, final newline optional, blanks before and after a number allowed, '\r' rejected.
  * Unlike the reference a missing file, a malformed cell, a cell count that disagrees with nnz, a
  * decreasing row_ptr or a column index outside [0, n_rows) is an error.  n_threads <= 0 picks
  * the hardware concurrency. */
 MPS_API int mps_csr_load(const char *path, int n_threads, mps_csr *out);
 MPS_API void mps_csr_free(mps_csr *csr);
+
+/* The same loader for a file whose columns reach beyond its rows.  scripts/npz_to_csr.py:13-19 builds its
+ * coo_matrix without a shape, so a destination index above every source index gives such a file; the
+ * reference program would gather past the end of its N-row B for it (src/MergePathSpMM.cu:176-182,441).
+ * Any non-negative column index is accepted and *n_cols = max(n_rows, largest index + 1) is the number of
+ * rows B must have. */
+MPS_API int mps_csr_load_rect(const char *path, int n_threads, mps_csr *out, int32_t *n_cols);
 
 /* Replaces the writers scripts/npz_to_csr.py:21-28 and scripts/fetch_dataset.py:14-21:
  * every cell followed by ',', one '\n' between the lines, none at the end. */
@@ -74,7 +81,8 @@ MPS_API int mps_csr_save(const char *path, int32_t n_rows, const int32_t *row_pt
 
 /* Binary sidecar (no reference counterpart; the text format cannot carry values and a
  * 10^9-nnz graph is ~10 GB of text): 32-byte header, then raw row_ptr, col_idx and, when
- * val_bytes != 0, values of that element size (4 = fp32, 2 = fp16).  Load mallocs the arrays. */
+ * val_bytes != 0, values of that element size (4 = fp32, 2 = fp16).  Load mallocs the arrays and applies
+ * the text loader's checks (row_ptr non-decreasing, columns inside [0, n_rows)). */
 MPS_API int mps_csr_save_bin(const char *path, int32_t n_rows, const int32_t *row_ptr, const int32_t *col_idx,
                      const void *val, int val_bytes);
 MPS_API int mps_csr_load_bin(const char *path, mps_csr *out, void **val, int *val_bytes);
@@ -127,6 +135,14 @@ MPS_API int mps_partition_device(const int32_t *d_row_ptr, int32_t n_rows, int32
 MPS_API int mps_schedule_device(const int32_t *d_row_ptr, int32_t n_rows, int32_t nnz, int32_t n_chunks,
                         int32_t *d_six, void *stream);
 
+/* The same two results on the host, on n_threads host threads (<= 0: all): replaces MergePathSearch over
+ * all chunk boundaries and generate_mp_sched where they run in the reference - on the host
+ * (src/MergePathSpMM.cu:280-297, 300-385) - for callers without a device at hand.  xy receives
+ * n_chunks + 1 interleaved (x, y) pairs, six the six arrays of n_chunks entries in the reference's return
+ * order; both bit-exact with the reference and with the device entry points above.  Host row_ptr. */
+MPS_API int mps_partition_host(const int32_t *row_ptr, int32_t n_rows, int32_t n_chunks, int32_t *xy, int n_threads);
+MPS_API int mps_schedule_host(const int32_t *row_ptr, int32_t n_rows, int32_t n_chunks, int32_t *six, int n_threads);
+
 /* ------------------------------------------------------------------ SpMM plan ------------ */
 
 typedef struct mps_plan mps_plan;
@@ -177,7 +193,9 @@ MPS_API int mps_spmm(mps_plan *plan, const int32_t *d_row_ptr, const int32_t *d_
 MPS_API int mps_spmm_scaled(mps_plan *plan, const int32_t *d_row_ptr, const int32_t *d_col_idx,
                     const float *d_row_scale, const float *d_col_scale, const void *d_B, void *d_C, void *stream);
 
-/* Waits for the stream and returns MPS_ERR_DEVICE if any kernel of this plan gave up a wait. */
+/* Waits for the stream and returns MPS_ERR_DEVICE if any kernel of this plan gave up a wait (a tile block whose
+ * staged window did not arrive in time fetches it again with plain loads and finishes its rows, but the call
+ * counts as failed: treat C as undefined until this returns MPS_OK). */
 MPS_API int mps_plan_sync_check(mps_plan *plan, void *stream);
 
 /* Facts about a plan: what[0]=n_chunks what[1]=items_per_chunk what[2]=chunks_per_tile
@@ -186,6 +204,17 @@ MPS_API int mps_plan_sync_check(mps_plan *plan, void *stream);
  * what[10]=kernels per mps_spmm call what[11]=long_chain threshold what[12]=chunks_per_unit
  * what[13]=units_per_tile what[14]=threads per tile block what[15]=very_long chain threshold. */
 MPS_API int mps_plan_info(const mps_plan *plan, int64_t what[16]);
+
+/* The layout behind those facts in merge items (no reference counterpart): what[0]=merge items per unit
+ * (one lane group's walk), what[1]=units per tile, what[2]=merge items per tile, what[3]=n_tiles,
+ * what[4]=units per reference chunk (1 unless `cost` asks for chunks longer than a tile can stage: then a
+ * unit is the what[4]-th part of a chunk and what[0] = ceil(items_per_chunk / what[4]); any `cost` the
+ * reference's command line accepts is therefore accepted here), what[5]=shared bytes per block,
+ * what[6]=column slabs, what[7]=1 when the tile kernel performs the cross-tile fix-up itself.
+ * mps_layout_query gives the same numbers for a shape without a plan or a CUDA device (the automatic
+ * layout for 148 SMs). */
+MPS_API int mps_plan_layout(const mps_plan *plan, int64_t what[8]);
+MPS_API int mps_layout_query(int32_t n_rows, int32_t nnz, int32_t dim, int dtype, int32_t cost, int64_t what[8]);
 
 /* Per-kernel timing (no reference counterpart; the reference is timed from outside with nvprof,
  * README.md:41-46): while enabled, every mps_spmm records a CUDA event pair around its tile
@@ -198,16 +227,43 @@ MPS_API int mps_plan_profile_read(mps_plan *plan, void *stream, double *tile_ms,
  * has_val = 0 drops the value term. */
 MPS_API int64_t mps_algorithmic_bytes(int32_t n_rows, int32_t nnz, int32_t dim, int dtype, int has_val);
 
+/* Measures what this GPU can do with the multiply's access pattern (no reference counterpart): whole rows
+ * of `row_bytes` (32..512, a power of two) fetched at random with 128-bit loads from a device table of
+ * `table_rows` rows, about `gathers` of them in one launch after one warm-up launch, 1024 threads per SM with
+ * eight loads in flight each.  *ms = the timed launch (CUDA events on `stream`), *gathered_bytes = the bytes it
+ * fetched.  A table well inside the L2 gives the L2 -> SM gather rate, a table far larger than the L2 the
+ * random-row rate of HBM; the multiply's gathered bytes per second belong beside these two, not beside a copy
+ * bandwidth.  d_sink: 4 bytes per thread of the launch (148 SMs x 1024 x 4 bytes = 0.6 MB on a B200).
+ * Allocates nothing but two events; blocking. */
+MPS_API int mps_gather_probe(const void *d_table, int64_t table_rows, int32_t row_bytes, int64_t gathers, void *d_sink,
+                     int64_t sink_bytes, void *stream, float *ms, int64_t *gathered_bytes);
+
 /* ------------------------------------------------------------------ host-buffer call ----- */
 
 /* The whole reference program body on HOST buffers (src/MergePathSpMM.cu:187-267): upload A and
  * B, partition, multiply once, download C.  B has n_cols rows (n_cols = n_rows for the square
  * matrices of the file format; a row slab of a larger matrix has fewer rows than columns).
  * Device buffers live in a per-thread workspace that only grows, so repeated calls do not
- * reallocate.  Blocking. */
+ * reallocate.  Blocking.
+ * The caller's arrays are validated on host threads before any kernel indexes by them (the reference
+ * checks nothing, its helper :41-52 is never called): row_ptr[0] == 0, row_ptr non-decreasing,
+ * row_ptr[n_rows] == nnz, every col_idx inside [0, n_cols) - else MPS_ERR_ARG naming the position.  The
+ * scan of col_idx runs beside the upload of B, and a bad index is reported in preference to any other
+ * failure of the call (also on a machine without a device). */
 MPS_API int mps_spmm_host(int32_t n_rows, int32_t n_cols, int32_t nnz, int32_t dim, int dtype, int32_t cost,
                   int32_t threads_per_warp, const int32_t *row_ptr, const int32_t *col_idx,
                   const void *val, const void *B, void *C);
+
+/* As mps_spmm_host, with B already in device memory (no reference counterpart: the reference is one
+ * process on one GPU).  This is the call of a rank in a multi-process job: every rank uploads only its
+ * share of B's rows into a full-size device buffer and an all-gather over NVLink (NCCL, the caller's)
+ * completes it, instead of every rank pulling all of B over PCIe.  d_B must be whole once the work
+ * queued so far on `b_ready_stream` has run; the call orders its multiplies behind that point and
+ * uploads A meanwhile, so the gather overlaps the upload.  A (row_ptr, col_idx, val) and C stay host
+ * buffers; validation as for mps_spmm_host. */
+MPS_API int mps_spmm_host_resident_b(int32_t n_rows, int32_t n_cols, int32_t nnz, int32_t dim, int dtype, int32_t cost,
+                             int32_t threads_per_warp, const int32_t *row_ptr, const int32_t *col_idx,
+                             const void *val, const void *d_B, void *b_ready_stream, void *C);
 MPS_API void mps_host_workspace_release(void);
 
 /* ------------------------------------------------------------------ no-allocation call --- */
@@ -259,8 +315,12 @@ MPS_API int mps_slab_rebase(const int32_t *row_ptr, int32_t row0, int32_t row1, 
 
 /* Single-process driver over n_gpus devices of one node (no reference counterpart).  create: cuts
  * the HOST CSR into row slabs of equal (nnz + 4*rows), uploads slab g to devices[g] (NULL = 0..n-1),
- * plans and partitions it there, and allocates on every device a full copy of B and a full-height C.
- * set_b: replicates a host B (n_cols x dim).  spmm: `repeat` multiplies on all devices at once, each
+ * plans and partitions it there, and allocates on every device a full copy of B and a full-height C.  The host
+ * arrays are validated first (as in mps_spmm_host: MPS_ERR_ARG for a decreasing row_ptr or a column index
+ * outside [0, n_cols), before any device is touched).
+ * set_b: replicates a host B (n_cols x dim): with NCCL at hand and every slab on a device of its own each device
+ * uploads 1/n_gpus of B's rows and one in-place all-gather over NVLink completes every copy (B crosses PCIe once
+ * in total, not once per device); otherwise every device uploads all of it.  spmm: `repeat` multiplies on all devices at once, each
  * into its own rows of its C; *ms_spmm = time per multiply, the maximum over devices (CUDA events).
  * gather_c != 0 then makes every device's C complete with one grouped NCCL broadcast per slab over
  * NVLink (*ms_gather); NCCL is loaded on first use, and only this option needs it.  get_c: from_gpu

@@ -29,7 +29,7 @@ try:
 except Exception:  # pragma: no cover
     torch = None
 
-__all__ = ["Plan", "MultiGpu", "coo_to_csr", "coo_to_csr_device", "npz_to_csr", "spmm", "spmm_host", "spmm_noalloc", "partition_device", "schedule_device", "chunk_count", "load_csr", "save_csr",
+__all__ = ["Plan", "MultiGpu", "layout_query", "coo_to_csr", "coo_to_csr_device", "npz_to_csr", "spmm", "spmm_host", "spmm_host_resident_b", "gather_probe", "partition_host", "schedule_host", "load_csr_rect", "spmm_noalloc", "partition_device", "schedule_device", "chunk_count", "load_csr", "save_csr",
            "save_csr_bin", "load_csr_bin", "slab_bounds", "slab_rebase", "algorithmic_bytes", "F32", "F16", "MpsError"]
 
 
@@ -152,7 +152,21 @@ class Plan:
     def info(self) -> dict:
         arr = (C.c_int64 * 16)()
         capi.check(capi.lib().mps_plan_info(self._h, arr))
-        return dict(zip(self.INFO, [int(v) for v in arr]))
+        out = dict(zip(self.INFO, [int(v) for v in arr]))
+        lay = (C.c_int64 * 8)()
+        capi.check(capi.lib().mps_plan_layout(self._h, lay))
+        out.update(zip(LAYOUT, [int(v) for v in lay]))
+        return out
+
+
+LAYOUT = ("unit_items", "units_per_tile", "tile_items", "n_tiles", "units_per_chunk", "shared_bytes_per_block", "column_slabs", "fused_fixup")
+
+
+def layout_query(n_rows: int, nnz: int, dim: int, dtype=F32, cost: int = 8) -> dict:
+    """The automatic tile layout for a shape (mps_layout_query): no plan, no CUDA device needed."""
+    lay = (C.c_int64 * 8)()
+    capi.check(capi.lib().mps_layout_query(n_rows, nnz, dim, dtype, cost, lay))
+    return dict(zip(LAYOUT, [int(v) for v in lay]))
 
 
 def spmm(row_ptr, col_idx, val, B, cost: int = 8, threads_per_warp: int = 1):
@@ -201,6 +215,56 @@ def spmm_host(row_ptr, col_idx, val, B, out=None, cost: int = 8, threads_per_war
         out = np.empty((n_rows, dim), np.float16 if is_half else np.float32)
     capi.check(capi.lib().mps_spmm_host(n_rows, int(B.shape[0]), nnz, dim, F16 if is_half else F32, cost, threads_per_warp, host_ptr(row_ptr),
                                         host_ptr(col_idx), host_ptr(val), host_ptr(B), host_ptr(out)))
+    return out
+
+
+def spmm_host_resident_b(row_ptr, col_idx, val, d_B, out, cost: int = 8, threads_per_warp: int = 1, stream=None):
+    """mps_spmm_host with B already on the device (a CUDA tensor, complete once the work queued on `stream` -
+    default: torch's current stream - has run): A and `out` are host arrays (numpy, or pinned torch CPU tensors).
+    The call of a rank whose share of B arrives over NVLink (see multi.replicate_b)."""
+    def host_ptr(a):
+        if a is None:
+            return None
+        if isinstance(a, torch.Tensor):
+            return C.c_void_p(a.data_ptr())
+        return a.ctypes.data_as(C.c_void_p)
+
+    _need_cuda(d_B)
+    is_half = d_B.dtype == torch.float16
+    with torch.cuda.device(d_B.device):
+        capi.check(capi.lib().mps_spmm_host_resident_b(int(row_ptr.shape[0]) - 1, int(d_B.shape[0]), int(col_idx.shape[0]), int(d_B.shape[1]),
+                                                       F16 if is_half else F32, cost, threads_per_warp, host_ptr(row_ptr), host_ptr(col_idx),
+                                                       host_ptr(val), _dev_ptr(d_B), _stream_ptr(stream), host_ptr(out)))
+    return out
+
+
+def gather_probe(table, row_bytes: int, gathers: int, stream=None) -> float:
+    """GB/s at which this GPU fetches random whole rows of `row_bytes` from `table` (any CUDA tensor; its bytes are
+    the table) with 128-bit loads - mps_gather_probe.  A table inside the L2 gives the L2 -> SM gather rate, one far
+    larger than the L2 the random-row rate of HBM."""
+    _need_cuda(table)
+    rows = table.numel() * table.element_size() // row_bytes
+    sink = torch.empty(1 << 20, dtype=torch.int32, device=table.device)
+    ms, nbytes = C.c_float(), C.c_int64()
+    with torch.cuda.device(table.device):
+        capi.check(capi.lib().mps_gather_probe(_dev_ptr(table), rows, row_bytes, gathers, _dev_ptr(sink), sink.numel() * 4, _stream_ptr(stream),
+                                               C.byref(ms), C.byref(nbytes)))
+    return nbytes.value / (ms.value * 1e-3) / 1e9
+
+
+def partition_host(row_ptr, n_chunks: int, threads: int = 0):
+    """(n_chunks+1, 2) int32 numpy array of (x, y): mps_partition_device's result computed on the host."""
+    rp = np.ascontiguousarray(row_ptr, np.int32)
+    out = np.empty((n_chunks + 1, 2), np.int32)
+    capi.check(capi.lib().mps_partition_host(rp.ctypes.data_as(C.c_void_p), len(rp) - 1, n_chunks, out.ctypes.data_as(C.c_void_p), threads))
+    return out
+
+
+def schedule_host(row_ptr, n_chunks: int, threads: int = 0):
+    """(6, n_chunks) int32 numpy array in generate_mp_sched's return order, computed on the host."""
+    rp = np.ascontiguousarray(row_ptr, np.int32)
+    out = np.empty((6, n_chunks), np.int32)
+    capi.check(capi.lib().mps_schedule_host(rp.ctypes.data_as(C.c_void_p), len(rp) - 1, n_chunks, out.ctypes.data_as(C.c_void_p), threads))
     return out
 
 
@@ -260,6 +324,14 @@ def load_csr(path: str, threads: int = 0):
     finally:
         capi.lib().mps_csr_free(C.byref(csr))
     return rp, col
+
+
+def load_csr_rect(path: str, threads: int = 0):
+    """As load_csr for a file whose column indices reach beyond its rows; returns (row_ptr, col_idx, n_cols)."""
+    csr, n_cols = capi.Csr(), C.c_int32()
+    capi.check(capi.lib().mps_csr_load_rect(path.encode(), threads, C.byref(csr), C.byref(n_cols)))
+    rp, col = _take_csr(csr)
+    return rp, col, n_cols.value
 
 
 def _take_csr(csr):

@@ -15,10 +15,10 @@ ERR_ARG, ERR_IO, ERR_FORMAT, ERR_CUDA, ERR_UNSUPPORTED, ERR_NOMEM, ERR_DEVICE, E
 F32, F16 = 0, 1
 
 SYMBOLS = [
-    "mps_last_error", "mps_version", "mps_csr_load", "mps_csr_free", "mps_csr_save", "mps_csr_save_bin",
+    "mps_last_error", "mps_version", "mps_csr_load", "mps_csr_load_rect", "mps_csr_free", "mps_csr_save", "mps_csr_save_bin",
     "mps_csr_load_bin", "mps_coo_to_csr", "mps_coo_to_csr_device", "mps_csr_transpose_device", "mps_npz_to_csr", "mps_chunk_count", "mps_partition_device", "mps_schedule_device", "mps_plan_create",
-    "mps_plan_destroy", "mps_plan_tune", "mps_plan_partition", "mps_spmm", "mps_spmm_scaled", "mps_plan_sync_check", "mps_plan_info", "mps_plan_profile", "mps_plan_profile_read",
-    "mps_algorithmic_bytes", "mps_spmm_host", "mps_host_workspace_release", "mps_spmm_noalloc", "mps_slab_bounds", "mps_slab_bounds_items", "mps_slab_rebase", "mps_multi_create", "mps_multi_destroy", "mps_multi_slab",
+    "mps_plan_destroy", "mps_plan_tune", "mps_plan_partition", "mps_spmm", "mps_spmm_scaled", "mps_plan_sync_check", "mps_plan_info", "mps_plan_layout", "mps_layout_query", "mps_plan_profile", "mps_plan_profile_read",
+    "mps_algorithmic_bytes", "mps_gather_probe", "mps_spmm_host", "mps_spmm_host_resident_b", "mps_partition_host", "mps_schedule_host", "mps_host_workspace_release", "mps_spmm_noalloc", "mps_slab_bounds", "mps_slab_bounds_items", "mps_slab_rebase", "mps_multi_create", "mps_multi_destroy", "mps_multi_slab",
     "mps_multi_set_b", "mps_multi_spmm", "mps_multi_get_c",
 ]
 
@@ -50,6 +50,7 @@ def lib():
     L.mps_last_error.restype = C.c_char_p
     L.mps_version.restype = C.c_char_p
     L.mps_csr_load.argtypes = [C.c_char_p, C.c_int, C.POINTER(Csr)]
+    L.mps_csr_load_rect.argtypes = [C.c_char_p, C.c_int, C.POINTER(Csr), C.POINTER(i32)]
     L.mps_csr_free.argtypes = [C.POINTER(Csr)]
     L.mps_csr_free.restype = None
     L.mps_csr_save.argtypes = [C.c_char_p, i32, vp, vp]
@@ -71,11 +72,17 @@ def lib():
     L.mps_spmm_scaled.argtypes = [vp] * 8
     L.mps_plan_sync_check.argtypes = [vp, vp]
     L.mps_plan_info.argtypes = [vp, C.POINTER(i64)]
+    L.mps_plan_layout.argtypes = [vp, C.POINTER(i64)]
+    L.mps_layout_query.argtypes = [i32, i32, i32, C.c_int, i32, C.POINTER(i64)]
     L.mps_plan_profile.argtypes = [vp, C.c_int]
     L.mps_plan_profile_read.argtypes = [vp, vp, C.POINTER(C.c_double), C.POINTER(i32)]
     L.mps_algorithmic_bytes.argtypes = [i32, i32, i32, C.c_int, C.c_int]
     L.mps_algorithmic_bytes.restype = i64
     L.mps_spmm_host.argtypes = [i32, i32, i32, i32, C.c_int, i32, i32, vp, vp, vp, vp, vp]
+    L.mps_spmm_host_resident_b.argtypes = [i32, i32, i32, i32, C.c_int, i32, i32, vp, vp, vp, vp, vp, vp]
+    L.mps_partition_host.argtypes = [vp, i32, i32, vp, C.c_int]
+    L.mps_schedule_host.argtypes = [vp, i32, i32, vp, C.c_int]
+    L.mps_gather_probe.argtypes = [vp, i64, i32, i64, vp, i64, vp, C.POINTER(C.c_float), C.POINTER(i64)]
     L.mps_host_workspace_release.restype = None
     L.mps_spmm_noalloc.argtypes = [i32, i32, i32, C.c_int, i32, i32, vp, vp, vp, vp, vp, vp]
     L.mps_slab_bounds.argtypes = [vp, i32, i32, vp]

@@ -84,6 +84,7 @@ long parse_cells(Span s, int32_t *out) {
         if (neg) v = -v;
         if (v > INT32_MAX || v < INT32_MIN) return (long)(p - s.b);
         *out++ = (int32_t)v;
+        while (p < s.e && (*p == ' ' || *p == '\t')) ++p;  // blanks after a cell: stoi stops at them, getline cut at the ','
         if (p < s.e) {
             if (*p != ',') return (long)(p - s.b);
             ++p;
@@ -151,7 +152,9 @@ extern "C" void mps_csr_free(mps_csr *csr) {
     csr->n_rows = csr->nnz = 0;
 }
 
-extern "C" int mps_csr_load(const char *path, int n_threads, mps_csr *out) {
+// n_cols == nullptr: the square matrix of the reference program (every column index below n_rows); otherwise any
+// non-negative column index is accepted and *n_cols receives max(n_rows, largest index + 1).
+static int load_text(const char *path, int n_threads, mps_csr *out, int32_t *n_cols) {
     if (!path || !out) return fail(MPS_ERR_ARG, "mps_csr_load: NULL argument");
     memset(out, 0, sizeof *out);
     Mapping m;
@@ -187,16 +190,33 @@ extern "C" int mps_csr_load(const char *path, int n_threads, mps_csr *out) {
         rc = fail(MPS_ERR_FORMAT, "%s: row_ptr[0] is %d, expected 0", path, rp[0]);
     else if (n_rows + 1 + nnz >= (int64_t)1 << 31)
         rc = fail(MPS_ERR_UNSUPPORTED, "%s: N+1+nnz = %lld does not fit 31 bits", path, (long long)(n_rows + 1 + nnz));
-    for (int64_t i = 0; rc == MPS_OK && i < n_rows; ++i)
-        if (rp[i + 1] < rp[i]) rc = fail(MPS_ERR_FORMAT, "%s: row_ptr decreases at row %lld", path, (long long)i);
-    for (int64_t k = 0; rc == MPS_OK && k < nnz; ++k)
-        if (col[k] < 0 || col[k] >= n_rows) rc = fail(MPS_ERR_FORMAT, "%s: col_idx[%lld] = %d outside [0, %lld)", path, (long long)k, col[k], (long long)n_rows);
+    int32_t width = (int32_t)n_rows;
+    if (rc == MPS_OK) {
+        const long long bad_row = mps::first_decreasing_row(rp, n_rows, n_threads);
+        if (bad_row >= 0) rc = fail(MPS_ERR_FORMAT, "%s: row_ptr decreases at row %lld", path, bad_row);
+    }
+    if (rc == MPS_OK && n_cols) {
+        const int32_t top = mps::max_column(col, nnz, n_threads);
+        if (top >= width) width = top == INT32_MAX ? top : top + 1;
+    }
+    if (rc == MPS_OK) {
+        const long long bad = mps::first_bad_column(col, nnz, width, n_threads);
+        if (bad >= 0) rc = fail(MPS_ERR_FORMAT, "%s: col_idx[%lld] = %d outside [0, %d)", path, bad, col[bad], width);
+    }
     if (rc != MPS_OK) { free(rp); free(col); return rc; }
+    if (n_cols) *n_cols = width;
     out->n_rows = (int32_t)n_rows;
     out->nnz = (int32_t)nnz;
     out->row_ptr = rp;
     out->col_idx = col;
     return MPS_OK;
+}
+
+extern "C" int mps_csr_load(const char *path, int n_threads, mps_csr *out) { return load_text(path, n_threads, out, nullptr); }
+
+extern "C" int mps_csr_load_rect(const char *path, int n_threads, mps_csr *out, int32_t *n_cols) {
+    if (!n_cols) return fail(MPS_ERR_ARG, "mps_csr_load_rect: n_cols is NULL");
+    return load_text(path, n_threads, out, n_cols);
 }
 
 namespace {
@@ -300,6 +320,16 @@ extern "C" int mps_csr_load_bin(const char *path, mps_csr *out, void **val, int 
     fclose(f);
     if (ok && (rp[0] != 0 || rp[h.n_rows] != h.nnz)) ok = false;
     if (!ok) { free(rp); free(col); free(v); return fail(MPS_ERR_FORMAT, "%s: truncated or inconsistent sidecar", path); }
+    // the same checks the text loader applies: a damaged sidecar must not hand the kernels an index they would follow
+    const long long bad_row = mps::first_decreasing_row(rp, h.n_rows, 0);
+    const long long bad_col = bad_row >= 0 ? -1 : mps::first_bad_column(col, h.nnz, h.n_rows, 0);
+    if (bad_row >= 0 || bad_col >= 0 || (long long)h.n_rows + 1 + h.nnz >= 1ll << 31) {
+        int rc = bad_row >= 0 ? fail(MPS_ERR_FORMAT, "%s: row_ptr decreases at row %lld", path, bad_row)
+               : bad_col >= 0 ? fail(MPS_ERR_FORMAT, "%s: col_idx[%lld] = %d outside [0, %d)", path, bad_col, col[bad_col], h.n_rows)
+                              : fail(MPS_ERR_UNSUPPORTED, "%s: N+1+nnz does not fit 31 bits", path);
+        free(rp); free(col); free(v);
+        return rc;
+    }
     out->n_rows = h.n_rows; out->nnz = h.nnz; out->row_ptr = rp; out->col_idx = col;
     if (val) *val = v;
     if (val_bytes) *val_bytes = v ? h.val_bytes : 0;

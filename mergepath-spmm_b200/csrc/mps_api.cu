@@ -8,8 +8,10 @@
 #include <cstdio>
 #include <cstring>
 #include <initializer_list>
+#include <atomic>
 #include <new>
 #include <string>
+#include <thread>
 
 #include "mps_internal.h"
 #include "mps_kernels.cuh"
@@ -110,6 +112,8 @@ static const int kUnitItems = 272;           // merge items one lane group walks
 static const int kTileItemsPerThread = 17;          // merge items per tile the automatic layout aims for
 static const int kSmemLimit = 200 * 1024;
 
+static const int kSmemSplitAbove = 48 * 1024;  // a whole-chunk tile beyond this is cut into sub-chunk units instead
+
 static int plan_layout(mps_plan *p) {
     const int elem = p->dtype == MPS_F16 ? 2 : 4;
     if (!p->user_block) p->block = 64;  // small blocks wait least at the three block barriers of a tile; 12 of them fit an SM
@@ -118,7 +122,17 @@ static int plan_layout(mps_plan *p) {
     const int kSmemTarget = kSmemTargetPer256 * p->block / 256, kTileItems = kTileItemsPerThread * p->block;
     if (!p->user_unroll) p->unroll = 8;
     if (p->vec == 1) p->unroll = 4;
-    if (!p->user_cpu) {
+    auto smem_of = [&](long long unit) -> long long {  // shared memory of a tile whose units hold `unit` merge items (64-bit: no wrap)
+        const long long items = (long long)gpc * unit;
+        if (items > (1ll << 24)) return 1ll << 40;
+        return TileSmem(gpc, (int)items, p->slab_cols, elem).bytes;
+    };
+    const long long total = (long long)p->n_rows + 1 + p->nnz;
+    long long unit;
+    p->sub_chunk = 1;
+    if (p->user_cpu) {
+        unit = (long long)p->cpu * p->ipt;
+    } else {
         // about kTileItems merge items per tile, fewer when the whole problem would otherwise leave SMs without
         // a tile (at least kTilesPerSm tiles per SM), as long as the windows fit the shared-memory target
         if (p->sm_count <= 0) {
@@ -126,21 +140,33 @@ static int plan_layout(mps_plan *p) {
             if (cudaGetDevice(&dev) == cudaSuccess && cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess) p->sm_count = sms;
             if (p->sm_count <= 0) p->sm_count = 148;
         }
-        const long long total = (long long)p->n_rows + 1 + p->nnz;
         long long items = total / ((long long)p->sm_count * kTilesPerSm);
         if (items > kTileItems) items = kTileItems;
         if (items > (long long)gpc * kUnitItems) items = (long long)gpc * kUnitItems;  // wide rows: few units, keep each walk short
         int cpu = (int)(items / ((long long)gpc * p->ipt));
         if (cpu < 1) cpu = 1;
         if (cpu > 64) cpu = 64;
-        while (cpu > 1 && TileSmem(gpc, gpc * cpu * p->ipt, p->slab_cols, elem).bytes > kSmemTarget) --cpu;
+        while (cpu > 1 && smem_of((long long)cpu * p->ipt) > kSmemTarget) --cpu;
         p->cpu = cpu;
+        unit = (long long)cpu * p->ipt;
+        if (cpu == 1 && smem_of(unit) > (kSmemTarget > kSmemSplitAbove ? kSmemTarget : kSmemSplitAbove)) {
+            // `cost` asks for chunks longer than a tile can stage: a unit becomes the k-th part of a chunk (the merge
+            // path is cut at multiples of ceil(ipt / k) instead of ipt; the partition search takes any step)
+            long long k = 2;
+            while ((p->ipt + k - 1) / k > 1 && smem_of((p->ipt + k - 1) / k) > kSmemTarget) ++k;
+            unit = (p->ipt + k - 1) / k;
+            p->sub_chunk = (int)k;
+        }
     }
+    if (smem_of(unit) > kSmemLimit)
+        return fail(MPS_ERR_UNSUPPORTED, "a tile of %d units x %lld merge items needs %lld bytes of shared memory (chunks_per_unit %d x %d items per chunk)",
+                    gpc, unit, smem_of(unit), p->cpu, p->ipt);
+    p->unit_items = (int)unit;
+    p->tile_items = (int)(gpc * unit);
     p->nch = gpc * p->cpu;
-    p->smem_bytes = TileSmem(gpc, p->nch * p->ipt, p->slab_cols, elem).bytes;
-    if (p->smem_bytes > kSmemLimit)
-        return fail(MPS_ERR_UNSUPPORTED, "tile of %d chunks x %d items needs %d bytes of shared memory", p->nch, p->ipt, p->smem_bytes);
-    p->n_tiles = (p->n_chunks + p->nch - 1) / p->nch;
+    p->smem_bytes = (int)smem_of(unit);
+    const long long tiles = (total + p->tile_items - 1) / p->tile_items;
+    p->n_tiles = (int)(tiles < 1 ? 1 : tiles);
     if (!p->user_fused) p->fused = (long long)p->n_tiles * p->n_col_slabs <= kFuseMaxTiles ? 1 : 0;
     // a tile block sums chains of any realistic length itself; a lone lane group of fixup_kernel should not:
     // there every strand-order chain goes to a whole block of fixup_kernel (512 threads per row)
@@ -211,7 +237,10 @@ extern "C" int mps_plan_create(int32_t n_rows, int32_t nnz, int32_t dim, int dty
     mps_plan *p = new (std::nothrow) mps_plan();
     if (!p) return fail(MPS_ERR_NOMEM, "mps_plan_create: out of host memory");
     plan_init_shape(p, n_rows, nnz, dim, dtype, cost, threads_per_warp);
-    MPS_CUDA(cudaGetDevice(&p->device));
+    if (cudaError_t e = cudaGetDevice(&p->device)) {
+        delete p;
+        return fail(MPS_ERR_CUDA, "cudaGetDevice: %s", cudaGetErrorString(e));
+    }
     int rc = plan_layout(p);
     if (rc == MPS_OK) rc = plan_alloc_scratch(p);
     if (rc != MPS_OK) { plan_free_scratch(p); delete p; return rc; }
@@ -257,7 +286,7 @@ extern "C" int mps_plan_partition(mps_plan *p, const int32_t *d_row_ptr, void *s
     cudaStream_t st = (cudaStream_t)stream;
     const long long total = (long long)p->n_rows + 1 + p->nnz;
     const int count = p->n_tiles + 1;
-    partition_kernel<<<(count + 255) / 256, 256, 0, st>>>(d_row_ptr, p->n_rows, p->nnz, (long long)p->ipt * p->nch, total, count,
+    partition_kernel<<<(count + 255) / 256, 256, 0, st>>>(d_row_ptr, p->n_rows, p->nnz, (long long)p->tile_items, total, count,
                                                          p->d_tile_xy);
     MPS_CUDA(cudaGetLastError());
     MPS_CUDA(cudaMemsetAsync(p->d_long_count, 0, sizeof(int), st));
@@ -298,7 +327,7 @@ static int spmm_launch(mps_plan *p, const int32_t *d_row_ptr, const int32_t *d_c
     tp.consumer = p->d_consumer; tp.need = p->d_need; tp.cnt = p->d_cnt; tp.long_chain = p->long_chain; tp.very_long = p->very_long; tp.fused = p->fused;
     tp.total = (long long)p->n_rows + 1 + p->nnz;
     tp.n_rows = p->n_rows; tp.nnz = p->nnz; tp.dim = p->dim;
-    tp.ipt = p->ipt; tp.nch = p->nch; tp.cpu = p->cpu; tp.n_tiles = p->n_tiles;
+    tp.unit_items = p->unit_items; tp.tile_items = p->tile_items; tp.n_tiles = p->n_tiles;
     const bool aligned16 = !((uintptr_t)d_row_ptr % 16) && !((uintptr_t)d_col_idx % 16) && !((uintptr_t)d_val % 16);
     tp.bulk = (p->bulk && aligned16) ? 1 : 0;
     cudaStream_t st = (cudaStream_t)stream;
@@ -368,6 +397,25 @@ extern "C" int mps_plan_info(const mps_plan *p, int64_t what[16]) {
     return MPS_OK;
 }
 
+extern "C" int mps_plan_layout(const mps_plan *p, int64_t what[8]) {
+    if (!p || !what) return fail(MPS_ERR_ARG, "mps_plan_layout: NULL argument");
+    what[0] = p->unit_items; what[1] = p->block / p->gl; what[2] = p->tile_items; what[3] = p->n_tiles;
+    what[4] = p->sub_chunk; what[5] = p->smem_bytes; what[6] = p->n_col_slabs; what[7] = p->fused;
+    return MPS_OK;
+}
+
+extern "C" int mps_layout_query(int32_t n_rows, int32_t nnz, int32_t dim, int dtype, int32_t cost, int64_t what[8]) {
+    if (!what) return fail(MPS_ERR_ARG, "mps_layout_query: what is NULL");
+    if (dim < 1 || cost < 1) return fail(MPS_ERR_ARG, "mps_layout_query: dim and cost must be >= 1 (dim=%d cost=%d)", dim, cost);
+    if (dtype != MPS_F32 && dtype != MPS_F16) return fail(MPS_ERR_ARG, "mps_layout_query: unknown dtype %d", dtype);
+    if (int rc = check_shape(n_rows, nnz)) return rc;
+    mps_plan plan;
+    plan_init_shape(&plan, n_rows, nnz, dim, dtype, cost, 1);
+    plan.sm_count = 148;  // the layout of a B200, whatever machine asks
+    if (int rc = plan_layout(&plan)) return rc;
+    return mps_plan_layout(&plan, what);
+}
+
 // ------------------------------------------------------------------------------------- host-buffer call
 //
 // The call is cut into row slabs (equal nnz + 4*rows) so that PCIe runs in both directions at once:
@@ -426,13 +474,26 @@ static int ws_reserve(int i, size_t bytes) {
 
 extern "C" void mps_host_workspace_release(void) { g_ws.release(); }
 
+// The scan of col_idx (every index inside [0, n_cols)) on background host threads: started before the first CUDA
+// call, joined before the first kernel that gathers by col_idx is launched, so it runs beside the upload of B.
+struct ColumnScan {
+    std::thread worker;
+    long long bad = -1;
+    void start(const int32_t *col, long long nnz, int32_t n_cols) {
+        if (!col || nnz <= 0) return;
+        if (nnz < (1 << 16)) { bad = first_bad_column(col, nnz, n_cols, 1); return; }
+        worker = std::thread([this, col, nnz, n_cols] { bad = first_bad_column(col, nnz, n_cols, 0); });
+    }
+    long long finish() {
+        if (worker.joinable()) worker.join();
+        return bad;
+    }
+    ~ColumnScan() { finish(); }
+};
+
 static int host_call(int32_t n_rows, int32_t n_cols, int32_t nnz, int32_t dim, int dtype, int32_t cost, int32_t threads_per_warp,
-                     const int32_t *row_ptr, const int32_t *col_idx, const void *val, const void *B, void *C) {
-    if (!row_ptr || !B || !C || (!col_idx && nnz > 0)) return fail(MPS_ERR_ARG, "mps_spmm_host: NULL argument");
-    if (dim < 1 || cost < 1 || n_cols < 0) return fail(MPS_ERR_ARG, "mps_spmm_host: dim and cost must be >= 1, n_cols >= 0");
-    if (dtype != MPS_F32 && dtype != MPS_F16) return fail(MPS_ERR_ARG, "mps_spmm_host: unknown dtype %d", dtype);
-    if (int rc = check_shape(n_rows, nnz)) return rc;
-    if (row_ptr[0] != 0 || row_ptr[n_rows] != nnz) return fail(MPS_ERR_ARG, "mps_spmm_host: row_ptr[0] must be 0 and row_ptr[n_rows] == nnz");
+                     const int32_t *row_ptr, const int32_t *col_idx, const void *val, const void *B, bool b_on_device, cudaStream_t b_stream,
+                     void *C, ColumnScan &scan) {
     int dev = 0;
     MPS_CUDA(cudaGetDevice(&dev));
     if (g_ws.device != dev) { g_ws.release(); g_ws.device = dev; }
@@ -465,7 +526,7 @@ static int host_call(int32_t n_rows, int32_t n_cols, int32_t nnz, int32_t dim, i
     }
     const size_t rp_slab_cap = ((size_t)n_rows + 1 + 8 * (size_t)n_slabs + 8);
     const size_t bytes[6] = {4 * ((size_t)n_rows + 1), 4 * (off[n_slabs] + 8), val ? elem * (off[n_slabs] + 8) : 0,
-                             elem * (size_t)n_cols * dim, elem * (size_t)n_rows * dim, 4 * rp_slab_cap};
+                             b_on_device ? 0 : elem * (size_t)n_cols * dim, elem * (size_t)n_rows * dim, 4 * rp_slab_cap};
     for (int i = 0; i < 6; ++i)
         if (int rc = ws_reserve(i, bytes[i])) return rc;
     int32_t *d_rp = (int32_t *)g_ws.buf[0], *d_col = (int32_t *)g_ws.buf[1], *d_rps = (int32_t *)g_ws.buf[5];
@@ -474,8 +535,15 @@ static int host_call(int32_t n_rows, int32_t n_cols, int32_t nnz, int32_t dim, i
     cudaStream_t s_in = g_ws.s_in, s_up = g_ws.s_b, s_work = g_ws.s_work, s_out = g_ws.s_out;
     // row_ptr first (small; the partitions need it), then B at once; rebasing and the partitions run beside B
     MPS_CUDA(cudaMemcpyAsync(d_rp, row_ptr, bytes[0], cudaMemcpyHostToDevice, s_in));
-    MPS_CUDA(cudaMemcpyAsync(g_ws.buf[3], B, bytes[3], cudaMemcpyHostToDevice, s_up));
-    MPS_CUDA(cudaEventRecord(g_ws.ev_b, s_up));
+    // B: uploaded at once on the upload stream, or already on the device and complete when the work queued so far
+    // on the caller's stream has run (another GPU's share of it may still be arriving over NVLink meanwhile)
+    const void *d_B = b_on_device ? B : g_ws.buf[3];
+    if (b_on_device) {
+        MPS_CUDA(cudaEventRecord(g_ws.ev_b, b_stream));
+    } else {
+        MPS_CUDA(cudaMemcpyAsync(g_ws.buf[3], B, bytes[3], cudaMemcpyHostToDevice, s_up));
+        MPS_CUDA(cudaEventRecord(g_ws.ev_b, s_up));
+    }
     size_t rps_off[kMaxHostSlabs];
     size_t at = 0;
     for (int s = 0; s < n_slabs; ++s) {
@@ -496,6 +564,7 @@ static int host_call(int32_t n_rows, int32_t n_cols, int32_t nnz, int32_t dim, i
     for (int s = n_slabs; s < kMaxHostSlabs; ++s) { mps_plan_destroy(g_ws.plan[s]); g_ws.plan[s] = nullptr; }
 
     MPS_CUDA(cudaStreamWaitEvent(s_work, g_ws.ev_b, 0));
+    bool scanned = false;
     // slabs with many rows first: their share of C is the largest download and should overlap the most uploads
     int order[kMaxHostSlabs];
     for (int s = 0; s < n_slabs; ++s) order[s] = s;
@@ -513,9 +582,14 @@ static int host_call(int32_t n_rows, int32_t n_cols, int32_t nnz, int32_t dim, i
         }
         MPS_CUDA(cudaEventRecord(g_ws.ev_slab[s], s_up));  // behind B on the same stream: B is whole when this fires
         MPS_CUDA(cudaStreamWaitEvent(s_work, g_ws.ev_slab[s], 0));
+        if (!scanned) {  // no kernel that gathers by col_idx is launched before every index has been checked
+            scanned = true;
+            const long long bad = scan.finish();
+            if (bad >= 0) return fail(MPS_ERR_ARG, "mps_spmm_host: col_idx[%lld] = %d outside [0, %d)", bad, col_idx[bad], n_cols);
+        }
         char *c_slab = d_C + elem * (size_t)r0 * dim;
         if (int rc = mps_spmm(g_ws.plan[s], d_rps + rps_off[s], d_col + off[s], val ? (const void *)(d_val + elem * off[s]) : nullptr,
-                              g_ws.buf[3], c_slab, s_work))
+                              d_B, c_slab, s_work))
             return rc;
         MPS_CUDA(cudaEventRecord(g_ws.ev_done[s], s_work));
         MPS_CUDA(cudaStreamWaitEvent(s_out, g_ws.ev_done[s], 0));
@@ -529,16 +603,43 @@ static int host_call(int32_t n_rows, int32_t n_cols, int32_t nnz, int32_t dim, i
     return MPS_OK;
 }
 
-extern "C" int mps_spmm_host(int32_t n_rows, int32_t n_cols, int32_t nnz, int32_t dim, int dtype, int32_t cost, int32_t threads_per_warp,
-                             const int32_t *row_ptr, const int32_t *col_idx, const void *val, const void *B, void *C) {
-    const int rc = host_call(n_rows, n_cols, nnz, dim, dtype, cost, threads_per_warp, row_ptr, col_idx, val, B, C);
-    if (rc != MPS_OK) {
+static int host_entry(const char *who, int32_t n_rows, int32_t n_cols, int32_t nnz, int32_t dim, int dtype, int32_t cost, int32_t threads_per_warp,
+                      const int32_t *row_ptr, const int32_t *col_idx, const void *val, const void *B, bool b_on_device, void *b_stream, void *C) {
+    if (!row_ptr || !B || !C || (!col_idx && nnz > 0)) return fail(MPS_ERR_ARG, "%s: NULL argument", who);
+    if (dim < 1 || cost < 1 || n_cols < 0) return fail(MPS_ERR_ARG, "%s: dim and cost must be >= 1, n_cols >= 0", who);
+    if (dtype != MPS_F32 && dtype != MPS_F16) return fail(MPS_ERR_ARG, "%s: unknown dtype %d", who, dtype);
+    if (int rc = check_shape(n_rows, nnz)) return rc;
+    if (row_ptr[n_rows] != nnz) return fail(MPS_ERR_ARG, "%s: row_ptr[n_rows] is %d, nnz is %d", who, row_ptr[n_rows], nnz);
+    // the caller's arrays are checked on the host before any kernel can index by them: row_ptr here (small), col_idx
+    // on background threads while the uploads start; a bad index is reported in preference to any later failure
+    if (int rc = check_csr_host(who, n_rows, n_cols, row_ptr, nullptr, 0)) return rc;
+    ColumnScan scan;
+    scan.start(col_idx, nnz, n_cols);
+    int rc = host_call(n_rows, n_cols, nnz, dim, dtype, cost, threads_per_warp, row_ptr, col_idx, val, B, b_on_device, (cudaStream_t)b_stream, C, scan);
+    const long long bad = scan.finish();
+    if (rc != MPS_OK || bad >= 0) {
         // a step failed with copies possibly still queued on the caller's buffers: let them drain before the caller
         // may free those buffers (the message of the failure stays the one reported)
+        const std::string kept = g_error;
         for (cudaStream_t st : {g_ws.s_in, g_ws.s_b, g_ws.s_work, g_ws.s_out})
             if (st) cudaStreamSynchronize(st);
+        for (mps_plan *&p : g_ws.plan) { mps_plan_destroy(p); p = nullptr; }  // a half-built set of slab plans is not reused
+        g_error = kept;
+        if (bad >= 0) rc = fail(MPS_ERR_ARG, "%s: col_idx[%lld] = %d outside [0, %d)", who, bad, col_idx[bad], n_cols);
     }
     return rc;
+}
+
+extern "C" int mps_spmm_host(int32_t n_rows, int32_t n_cols, int32_t nnz, int32_t dim, int dtype, int32_t cost, int32_t threads_per_warp,
+                             const int32_t *row_ptr, const int32_t *col_idx, const void *val, const void *B, void *C) {
+    return host_entry("mps_spmm_host", n_rows, n_cols, nnz, dim, dtype, cost, threads_per_warp, row_ptr, col_idx, val, B, false, nullptr, C);
+}
+
+extern "C" int mps_spmm_host_resident_b(int32_t n_rows, int32_t n_cols, int32_t nnz, int32_t dim, int dtype, int32_t cost,
+                                        int32_t threads_per_warp, const int32_t *row_ptr, const int32_t *col_idx, const void *val,
+                                        const void *d_B, void *b_ready_stream, void *C) {
+    return host_entry("mps_spmm_host_resident_b", n_rows, n_cols, nnz, dim, dtype, cost, threads_per_warp, row_ptr, col_idx, val, d_B, true,
+                      b_ready_stream, C);
 }
 
 // ------------------------------------------------------------------------------------- slabs (host)

@@ -53,7 +53,7 @@ struct TileParams {
     int fused;  // 1: the tile kernel signals and performs the cross-tile fix-up itself; 0: fixup_kernel follows
     long long total;  // N + 1 + nnz
     int n_rows, nnz, dim;
-    int ipt, nch, cpu, n_tiles;  // items per chunk, chunks per tile, chunks per unit
+    int unit_items, tile_items, n_tiles;  // merge items per unit, per tile (= units per tile x unit_items)
     int bulk;  // 1: bulk async staging (needs 16-byte aligned rp/col/val)
 };
 
@@ -383,7 +383,7 @@ __global__ void __launch_bounds__(BLOCK, kWarpsPerSm * 32 / BLOCK) spmm_tile_ker
     constexpr int GPC = kBlock / GL;   // units (lane groups) per block
     constexpr int SLAB = GL * VEC;     // columns covered by one block
     extern __shared__ __align__(128) unsigned char smem[];
-    const TileSmem L(GPC, p.nch * p.ipt, SLAB, (int)sizeof(T));
+    const TileSmem L(GPC, p.tile_items, SLAB, (int)sizeof(T));
     uint64_t *s_bar = reinterpret_cast<uint64_t *>(smem);
     int *s_fx = reinterpret_cast<int *>(smem + L.off_fx);
     int *s_fy = reinterpret_cast<int *>(smem + L.off_fy);
@@ -412,6 +412,7 @@ __global__ void __launch_bounds__(BLOCK, kWarpsPerSm * 32 / BLOCK) spmm_tile_ker
     const int y_base = Y0 & ~(kAlign - 1);
 
     // ---- stage the tile's windows ----
+    bool staged = false;
     if (p.bulk) {
         const uint32_t bar = smem_u32(s_bar);
         if (tid == 0) mbar_init(bar, 1);
@@ -435,13 +436,15 @@ __global__ void __launch_bounds__(BLOCK, kWarpsPerSm * 32 / BLOCK) spmm_tile_ker
         bool ok = true;
         if (tid < 32) {
             ok = mbar_wait_bounded(bar, 0);
-            if (!ok) {
-                if (tid == 0) atomicExch(p.status, (int)kDevStageTimeout);
-                ok = mbar_wait_bounded(bar, 0);  // give copies in flight one more bounded chance to land
-            }
+            if (!ok && tid == 0) atomicExch(p.status, (int)kDevStageTimeout);
         }
-        if (__syncthreads_or(!ok)) return;
-    } else {
+        // A wait that ran out marks the call as failed (the host reads the status word) but the block does not
+        // leave: it fetches the same windows with plain loads below and carries on, so that its counters and its
+        // rows of C are complete and its shared memory stays its own for as long as a late copy could still land
+        // (a late copy writes the very bytes the plain loads wrote).
+        staged = !__syncthreads_or(!ok);
+    }
+    if (!staged) {
         for (int i = rp_base + tid; i < X1; i += kBlock) s_rp[i - rp_base] = p.rp[i];
         for (int i = y_base + tid; i < Y1; i += kBlock) s_col[i - y_base] = p.col[i];
         if (has_val)
@@ -458,7 +461,7 @@ __global__ void __launch_bounds__(BLOCK, kWarpsPerSm * 32 / BLOCK) spmm_tile_ker
         if (tid == 0) r = c0;
         else if (tid == GPC) r = c1;
         else {
-            long long d = (long long)p.ipt * ((long long)t * p.nch + (long long)tid * p.cpu);
+            long long d = (long long)t * p.tile_items + (long long)tid * p.unit_items;
             if (d > p.total) d = p.total;
             long long lo = d - Y1 > X0 ? d - Y1 : X0;
             long long hi = d - Y0 < X1 ? d - Y0 : X1;

@@ -12,6 +12,7 @@
 #include <dlfcn.h>
 #include <nccl.h>
 
+#include <algorithm>
 #include <cstring>
 #include <new>
 #include <vector>
@@ -35,6 +36,7 @@ struct NcclApi {
     ncclResult_t (*GroupStart)() = nullptr;
     ncclResult_t (*GroupEnd)() = nullptr;
     ncclResult_t (*Broadcast)(const void *, void *, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*AllGather)(const void *, void *, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
     const char *(*GetErrorString)(ncclResult_t) = nullptr;
     bool load() {
         if (handle) return true;
@@ -46,8 +48,9 @@ struct NcclApi {
         GroupStart = (decltype(GroupStart))dlsym(handle, "ncclGroupStart");
         GroupEnd = (decltype(GroupEnd))dlsym(handle, "ncclGroupEnd");
         Broadcast = (decltype(Broadcast))dlsym(handle, "ncclBroadcast");
+        AllGather = (decltype(AllGather))dlsym(handle, "ncclAllGather");
         GetErrorString = (decltype(GetErrorString))dlsym(handle, "ncclGetErrorString");
-        return CommInitAll && CommDestroy && GroupStart && GroupEnd && Broadcast && GetErrorString;
+        return CommInitAll && CommDestroy && GroupStart && GroupEnd && Broadcast && AllGather && GetErrorString;
     }
 };
 NcclApi g_nccl;
@@ -66,6 +69,8 @@ struct Slab {
 struct mps_multi {
     int n_gpus = 0, n_rows = 0, n_cols = 0, nnz = 0, dim = 0, dtype = 0;
     bool has_val = false, have_b = false;
+    bool distinct = true;     // every slab on a device of its own (what a communicator needs)
+    size_t b_block_rows = 0;  // rows of B per device block: ceil(n_cols / n_gpus); every d_B holds n_gpus such blocks
     std::vector<Slab> slab;
     std::vector<ncclComm_t> comm;  // empty until the first gather
 };
@@ -95,6 +100,11 @@ extern "C" int mps_multi_create(int32_t n_gpus, const int32_t *devices, int32_t 
     if (n_gpus < 1 || n_gpus > 64 || !row_ptr || n_rows < 0 || n_cols < 0 || dim < 1 || cost < 1)
         return fail(MPS_ERR_ARG, "mps_multi_create: bad argument");
     if (dtype != MPS_F32 && dtype != MPS_F16) return fail(MPS_ERR_ARG, "mps_multi_create: unknown dtype %d", dtype);
+    if (row_ptr[n_rows] < 0 || (row_ptr[n_rows] > 0 && !col_idx)) return fail(MPS_ERR_ARG, "mps_multi_create: bad nnz / col_idx");
+    if ((long long)n_rows + 1 + row_ptr[n_rows] >= 1ll << 31) return fail(MPS_ERR_UNSUPPORTED, "mps_multi_create: N+1+nnz does not fit 31 bits");
+    // the caller's arrays are checked on the host before anything is uploaded: a bad index must not become a gather
+    // outside B on some device
+    if (int rc = mps::check_csr_host("mps_multi_create", n_rows, n_cols, row_ptr, col_idx, 0)) return rc;
     int visible = 0;
     MM_CUDA(cudaGetDeviceCount(&visible));
     for (int g = 0; g < n_gpus; ++g) {
@@ -102,11 +112,14 @@ extern "C" int mps_multi_create(int32_t n_gpus, const int32_t *devices, int32_t 
         if (d < 0 || d >= visible) return fail(MPS_ERR_ARG, "mps_multi_create: device %d of %d requested, %d visible", d, n_gpus, visible);
     }
     const int nnz = row_ptr[n_rows];
-    if (nnz < 0 || (nnz > 0 && !col_idx)) return fail(MPS_ERR_ARG, "mps_multi_create: bad nnz / col_idx");
     mps_multi *m = new (std::nothrow) mps_multi();
     if (!m) return fail(MPS_ERR_NOMEM, "mps_multi_create: out of host memory");
     m->n_gpus = n_gpus; m->n_rows = n_rows; m->n_cols = n_cols; m->nnz = nnz; m->dim = dim; m->dtype = dtype; m->has_val = val != nullptr;
     m->slab.resize((size_t)n_gpus);
+    m->b_block_rows = ((size_t)n_cols + (size_t)n_gpus - 1) / (size_t)n_gpus;
+    for (int g = 0; g < n_gpus; ++g)
+        for (int h = 0; h < g; ++h)
+            if ((devices ? devices[g] : g) == (devices ? devices[h] : h)) m->distinct = false;
     std::vector<int32_t> bounds((size_t)n_gpus + 1);
     int rc = mps_slab_bounds_items(row_ptr, n_rows, n_gpus, 4, bounds.data());
     const size_t es = elem_bytes(dtype);
@@ -128,7 +141,7 @@ extern "C" int mps_multi_create(int32_t n_gpus, const int32_t *devices, int32_t 
         if (e == cudaSuccess) e = cudaMalloc(&s.d_rp, 4 * ((size_t)rows + 1));
         if (e == cudaSuccess) e = cudaMalloc(&s.d_col, 4 * (size_t)(s.nnz ? s.nnz : 4));
         if (e == cudaSuccess && val) e = cudaMalloc(&s.d_val, es * (size_t)(s.nnz ? s.nnz : 8));
-        if (e == cudaSuccess) e = cudaMalloc(&s.d_B, es * (size_t)n_cols * dim + 16);
+        if (e == cudaSuccess) e = cudaMalloc(&s.d_B, es * m->b_block_rows * (size_t)n_gpus * dim + 16);
         if (e == cudaSuccess) e = cudaMalloc(&s.d_C, es * (size_t)n_rows * dim + 16);
         if (e == cudaSuccess) e = cudaMemcpy(s.d_rp, rp.data(), 4 * ((size_t)rows + 1), cudaMemcpyHostToDevice);
         if (e == cudaSuccess && s.nnz) e = cudaMemcpy(s.d_col, col_idx + k0, 4 * (size_t)s.nnz, cudaMemcpyHostToDevice);
@@ -154,30 +167,11 @@ extern "C" int mps_multi_slab(const mps_multi *m, int32_t g, int32_t *device, in
     return MPS_OK;
 }
 
-extern "C" int mps_multi_set_b(mps_multi *m, const void *host_B) {
-    if (!m || !host_B) return fail(MPS_ERR_ARG, "mps_multi_set_b: NULL argument");
-    const size_t bytes = elem_bytes(m->dtype) * (size_t)m->n_cols * m->dim;
-    int prev = 0;
-    cudaGetDevice(&prev);
-    for (Slab &s : m->slab) {
-        cudaError_t e = cudaSetDevice(s.device);
-        if (e == cudaSuccess) e = cudaMemcpyAsync(s.d_B, host_B, bytes, cudaMemcpyHostToDevice, s.stream);
-        if (e != cudaSuccess) { cudaSetDevice(prev); return fail(MPS_ERR_CUDA, "mps_multi_set_b: device %d: %s", s.device, cudaGetErrorString(e)); }
-    }
-    for (Slab &s : m->slab) {
-        cudaSetDevice(s.device);
-        cudaError_t e = cudaStreamSynchronize(s.stream);
-        if (e != cudaSuccess) { cudaSetDevice(prev); return fail(MPS_ERR_CUDA, "mps_multi_set_b: device %d: %s", s.device, cudaGetErrorString(e)); }
-    }
-    cudaSetDevice(prev);
-    m->have_b = true;
-    return MPS_OK;
-}
-
 // Communicators are created once, outside any timed region.
 static int multi_init_comm(mps_multi *m) {
     if (m->n_gpus > 1 && m->comm.empty()) {
-        if (!g_nccl.load()) return fail(MPS_ERR_UNSUPPORTED, "mps_multi_spmm: a replicated C needs NCCL (libnccl.so.2 not found: %s)", dlerror());
+        if (!m->distinct) return fail(MPS_ERR_UNSUPPORTED, "a communicator needs every slab on a device of its own");
+        if (!g_nccl.load()) return fail(MPS_ERR_UNSUPPORTED, "NCCL is needed (libnccl.so.2 not found: %s)", dlerror());
         std::vector<int> devs;
         for (const Slab &s : m->slab) devs.push_back(s.device);
         m->comm.assign((size_t)m->n_gpus, nullptr);
@@ -185,6 +179,50 @@ static int multi_init_comm(mps_multi *m) {
         if (r != ncclSuccess) { m->comm.clear(); return fail(MPS_ERR_CUDA, "ncclCommInitAll: %s", g_nccl.GetErrorString(r)); }
     }
     return MPS_OK;
+}
+
+// B reaches every device once over PCIe in total, not once per device: device g uploads block g of B's rows
+// (ceil(n_cols / n_gpus) rows each) into its place of its own full-size buffer, then one in-place NCCL
+// all-gather of equal blocks over NVLink completes every copy.  Without NCCL, with one device, or with several
+// slabs on one device (no communicator possible) every device uploads all of B itself.
+extern "C" int mps_multi_set_b(mps_multi *m, const void *host_B) {
+    if (!m || !host_B) return fail(MPS_ERR_ARG, "mps_multi_set_b: NULL argument");
+    const size_t es = elem_bytes(m->dtype), row_bytes = es * (size_t)m->dim;
+    int prev = 0;
+    cudaGetDevice(&prev);
+    bool over_nvlink = m->n_gpus > 1 && m->distinct && multi_init_comm(m) == MPS_OK;
+    int rc = MPS_OK;
+    for (int g = 0; g < m->n_gpus && rc == MPS_OK; ++g) {
+        Slab &s = m->slab[(size_t)g];
+        size_t row0 = 0, rows = (size_t)m->n_cols;
+        if (over_nvlink) {
+            row0 = std::min((size_t)g * m->b_block_rows, (size_t)m->n_cols);
+            rows = std::min(m->b_block_rows, (size_t)m->n_cols - row0);
+        }
+        cudaError_t e = cudaSetDevice(s.device);
+        if (e == cudaSuccess && rows)
+            e = cudaMemcpyAsync((char *)s.d_B + row0 * row_bytes, (const char *)host_B + row0 * row_bytes, rows * row_bytes, cudaMemcpyHostToDevice, s.stream);
+        if (e != cudaSuccess) rc = fail(MPS_ERR_CUDA, "mps_multi_set_b: device %d: %s", s.device, cudaGetErrorString(e));
+    }
+    if (rc == MPS_OK && over_nvlink) {
+        const size_t count = m->b_block_rows * (size_t)m->dim;
+        const ncclDataType_t dt = m->dtype == MPS_F16 ? ncclFloat16 : ncclFloat32;
+        ncclResult_t r = g_nccl.GroupStart();
+        for (int g = 0; g < m->n_gpus && r == ncclSuccess; ++g) {
+            Slab &s = m->slab[(size_t)g];
+            r = g_nccl.AllGather((const char *)s.d_B + (size_t)g * count * es, s.d_B, count, dt, m->comm[(size_t)g], s.stream);
+        }
+        ncclResult_t r2 = g_nccl.GroupEnd();
+        if (r != ncclSuccess || r2 != ncclSuccess) rc = fail(MPS_ERR_CUDA, "ncclAllGather: %s", g_nccl.GetErrorString(r != ncclSuccess ? r : r2));
+    }
+    for (Slab &s : m->slab) {  // drain every device, also after a failure: the caller may free host_B next
+        cudaSetDevice(s.device);
+        cudaError_t e = cudaStreamSynchronize(s.stream);
+        if (e != cudaSuccess && rc == MPS_OK) rc = fail(MPS_ERR_CUDA, "mps_multi_set_b: device %d: %s", s.device, cudaGetErrorString(e));
+    }
+    cudaSetDevice(prev);
+    if (rc == MPS_OK) m->have_b = true;
+    return rc;
 }
 
 static int multi_gather(mps_multi *m) {
@@ -228,9 +266,10 @@ extern "C" int mps_multi_spmm(mps_multi *m, int32_t repeat, int32_t gather_c, fl
         cudaSetDevice(s.device);
         cudaEventRecord(s.ev1, s.stream);
     }
-    for (Slab &s : m->slab) {
+    for (Slab &s : m->slab) {  // every device is drained, also after a failed launch: nothing of this call stays in flight
         cudaSetDevice(s.device);
         if (rc == MPS_OK) rc = mps_plan_sync_check(s.plan, s.stream);
+        else cudaStreamSynchronize(s.stream);
         float ms = 0.0f;
         if (rc == MPS_OK && cudaEventElapsedTime(&ms, s.ev0, s.ev1) == cudaSuccess && ms > worst) worst = ms;
     }

@@ -10,7 +10,9 @@ struct mps_plan {
     int n_chunks, ipt;
     int vec, gl, unroll, slab_cols, n_col_slabs;
     int block;                          // threads per tile block (64, 128 or 256)
-    int nch, cpu, n_tiles, smem_bytes;  // chunks per tile, chunks per unit
+    int nch, cpu, n_tiles, smem_bytes;  // chunks per tile, chunks per unit (whole-chunk layouts; 1 unit = 1 "chunk" otherwise)
+    int unit_items, tile_items;         // merge items one lane group walks, merge items per tile (= units per tile x unit_items)
+    int sub_chunk;                      // units per reference chunk when a chunk is too long for one unit (1 = whole chunks)
     int bulk;
     int long_chain, very_long, n_long, long_capacity;  // chain lengths (tiles): strand order above long_chain, own kernel above very_long
     int device, sm_count;

@@ -281,9 +281,11 @@ ORC_API int orc_spmm_f32_omp(const int *row_ptr, const int *col, const float *va
  * equal it bit for bit.
  *
  *   chunk  c : merge items [ipt*c, ipt*(c+1)), one reference chunk
- *   unit     : cpu consecutive chunks, walked in order by one lane group with
- *              one running accumulator, acc = fmaf(a, b, acc)
- *   tile   t : nch consecutive chunks = nch/cpu units
+ *   unit     : unit_items consecutive merge items (cpu whole chunks, or the k-th
+ *              part of a chunk when `cost` asks for chunks longer than a tile),
+ *              walked in order by one lane group with one running accumulator,
+ *              acc = fmaf(a, b, acc)
+ *   tile   t : nu consecutive units; tiles cover [0, N+1+nnz) and no more
  *   a row that ends inside a unit is stored directly unless it began in an
  *   earlier unit, in which case the unit's share is its "head"; what is left
  *   at the unit's end is its "carry".
@@ -323,105 +325,139 @@ static inline void model_store(const model_io *io, int row, const float *v_in) {
     else memcpy((float *)io->C + at, v, sizeof(float) * io->dim);
 }
 
-static int tile_model_impl(const int *row_ptr, const int *col, const void *val, const float *row_scale, const float *col_scale,
-                           const void *B, void *C, int n_rows, int nnz, int dim, int is_half, int cost, int nch, int cpu,
-                           int long_chain) {
-    if (cost < 1 || nch < 1 || cpu < 1 || nch % cpu != 0 || dim < 1 || dim > 1024) return -1;
+/* unit_items: merge items per unit; nu: units per tile.  The tiles are independent until the cross-tile fix-up,
+ * so they are walked by all host threads (every thread owns its scratch; each row of C, each tcarry / thead row is
+ * written by exactly one tile), which lets the model check a full-size product in seconds. */
+static int tile_model_items(const int *row_ptr, const int *col, const void *val, const float *row_scale, const float *col_scale,
+                            const void *B, void *C, int n_rows, int nnz, int dim, int is_half, int64_t unit_items, int nu,
+                            int long_chain) {
+    if (unit_items < 1 || nu < 1 || dim < 1 || dim > 1024) return -1;
     model_io io = {row_ptr, col, val, B, C, dim, is_half, row_scale, col_scale};
-    const int nu = nch / cpu; /* units per tile */
     const int64_t total = (int64_t)n_rows + 1 + nnz;
-    const int P = orc_chunk_count(n_rows, nnz, cost);
-    const int64_t ipt = orc_items_per_chunk(n_rows, nnz, P);
-    const int T = (P + nch - 1) / nch;
-    int *tx = malloc(sizeof(int) * (T + 1)), *ty = malloc(sizeof(int) * (T + 1));
+    const int64_t tile_items = unit_items * nu;
+    int64_t T64 = (total + tile_items - 1) / tile_items;
+    if (T64 < 1) T64 = 1;
+    if (T64 > 0x7fffffff) return -1;
+    const int T = (int)T64;
+    int *tx = malloc(sizeof(int) * ((size_t)T + 1)), *ty = malloc(sizeof(int) * ((size_t)T + 1));
     float *tcarry = calloc((size_t)T * dim, sizeof(float));
     float *thead = calloc((size_t)T * dim, sizeof(float));
-    int *fx = malloc(sizeof(int) * (nu + 1)), *fy = malloc(sizeof(int) * (nu + 1));
-    float *carry = malloc(sizeof(float) * (size_t)nu * dim);
-    float *head = malloc(sizeof(float) * (size_t)nu * dim);
-    char *has_head = malloc(nu);
-    float *acc = malloc(sizeof(float) * dim), *sum = malloc(sizeof(float) * dim);
-    float *strand = malloc(sizeof(float) * 16 * dim);
+    if (!tx || !ty || !tcarry || !thead) { free(tx); free(ty); free(tcarry); free(thead); return -1; }
 
+#pragma omp parallel for schedule(static)
     for (int t = 0; t <= T; ++t)
-        orc_merge_path_search(lmin(ipt * nch * (int64_t)t, total), row_ptr, n_rows + 1, nnz, &tx[t], &ty[t]);
+        orc_merge_path_search(lmin(tile_items * (int64_t)t, total), row_ptr, n_rows + 1, nnz, &tx[t], &ty[t]);
 
-    for (int t = 0; t < T; ++t) {
-        for (int u = 0; u <= nu; ++u)
-            orc_merge_path_search(lmin(ipt * ((int64_t)t * nch + (int64_t)u * cpu), total), row_ptr, n_rows + 1, nnz, &fx[u], &fy[u]);
-        for (int u = 0; u < nu; ++u) {
-            const int x0 = fx[u], y0 = fy[u], x1 = fx[u + 1], y1 = fy[u + 1];
-            const int cont = x0 >= 1 && y0 > row_ptr[x0 - 1];
-            int x = x0, first = 1;
-            has_head[u] = 0;
-            for (int j = 0; j < dim; ++j) acc[j] = 0.0f;
-            for (int k = y0; k <= y1; ++k) {
-                /* consume every marker that precedes non-zero k (all that are left when k == y1) */
-                while (x < x1 && (k == y1 || row_ptr[x] <= k)) {
-                    if (x >= 1) {
-                        if (first && cont) { memcpy(head + (size_t)u * dim, acc, sizeof(float) * dim); has_head[u] = 1; }
-                        else model_store(&io, x - 1, acc);
-                        first = 0;
-                        for (int j = 0; j < dim; ++j) acc[j] = 0.0f;
+#pragma omp parallel
+    {
+        int *fx = malloc(sizeof(int) * (nu + 1)), *fy = malloc(sizeof(int) * (nu + 1));
+        float *carry = malloc(sizeof(float) * (size_t)nu * dim);
+        float *head = malloc(sizeof(float) * (size_t)nu * dim);
+        char *has_head = malloc(nu);
+        float *acc = malloc(sizeof(float) * dim), *sum = malloc(sizeof(float) * dim);
+#pragma omp for schedule(dynamic, 64)
+        for (int t = 0; t < T; ++t) {
+            for (int u = 0; u <= nu; ++u)
+                orc_merge_path_search(lmin(tile_items * (int64_t)t + unit_items * (int64_t)u, total), row_ptr, n_rows + 1, nnz, &fx[u], &fy[u]);
+            for (int u = 0; u < nu; ++u) {
+                const int x0 = fx[u], y0 = fy[u], x1 = fx[u + 1], y1 = fy[u + 1];
+                const int cont = x0 >= 1 && y0 > row_ptr[x0 - 1];
+                int x = x0, first = 1;
+                has_head[u] = 0;
+                for (int j = 0; j < dim; ++j) acc[j] = 0.0f;
+                for (int k = y0; k <= y1; ++k) {
+                    /* consume every marker that precedes non-zero k (all that are left when k == y1) */
+                    while (x < x1 && (k == y1 || row_ptr[x] <= k)) {
+                        if (x >= 1) {
+                            if (first && cont) { memcpy(head + (size_t)u * dim, acc, sizeof(float) * dim); has_head[u] = 1; }
+                            else model_store(&io, x - 1, acc);
+                            first = 0;
+                            for (int j = 0; j < dim; ++j) acc[j] = 0.0f;
+                        }
+                        ++x;
                     }
-                    ++x;
+                    if (k == y1) break;
+                    const float a = model_val(&io, k);
+                    const int cc = col[k];
+                    if (!is_half) { /* same fused multiply-adds, read straight from the fp32 row */
+                        const float *restrict b = (const float *)B + (size_t)cc * dim;
+#pragma omp simd
+                        for (int j = 0; j < dim; ++j) acc[j] = fmaf(a, b[j], acc[j]);
+                    } else {
+                        for (int j = 0; j < dim; ++j) acc[j] = fmaf(a, model_b(&io, cc, j), acc[j]);
+                    }
                 }
-                if (k == y1) break;
-                const float a = model_val(&io, k);
-                const int cc = col[k];
-                for (int j = 0; j < dim; ++j) acc[j] = fmaf(a, model_b(&io, cc, j), acc[j]);
+                memcpy(carry + (size_t)u * dim, acc, sizeof(float) * dim);
             }
-            memcpy(carry + (size_t)u * dim, acc, sizeof(float) * dim);
+            /* in-tile fix-up */
+            for (int u = 0; u < nu; ++u) {
+                if (!has_head[u]) continue;
+                int s = u;
+                while (s > 0 && fx[s] == fx[u]) --s;
+                const int from_prev = fx[0] == fx[u] && ty[t] > row_ptr[tx[t] - 1];
+                for (int j = 0; j < dim; ++j) sum[j] = 0.0f;
+                for (int q = s; q < u; ++q) for (int j = 0; j < dim; ++j) sum[j] += carry[(size_t)q * dim + j];
+                for (int j = 0; j < dim; ++j) sum[j] += head[(size_t)u * dim + j];
+                if (from_prev) memcpy(thead + (size_t)t * dim, sum, sizeof(float) * dim);
+                else model_store(&io, fx[u] - 1, sum);
+            }
+            {
+                int s = nu;
+                while (s > 0 && fx[s] == fx[nu]) --s;
+                for (int j = 0; j < dim; ++j) sum[j] = 0.0f;
+                for (int q = s; q < nu; ++q) for (int j = 0; j < dim; ++j) sum[j] += carry[(size_t)q * dim + j];
+                memcpy(tcarry + (size_t)t * dim, sum, sizeof(float) * dim);
+            }
         }
-        /* in-tile fix-up */
-        for (int u = 0; u < nu; ++u) {
-            if (!has_head[u]) continue;
-            int s = u;
-            while (s > 0 && fx[s] == fx[u]) --s;
-            const int from_prev = fx[0] == fx[u] && ty[t] > row_ptr[tx[t] - 1];
-            for (int j = 0; j < dim; ++j) sum[j] = 0.0f;
-            for (int q = s; q < u; ++q) for (int j = 0; j < dim; ++j) sum[j] += carry[(size_t)q * dim + j];
-            for (int j = 0; j < dim; ++j) sum[j] += head[(size_t)u * dim + j];
-            if (from_prev) memcpy(thead + (size_t)t * dim, sum, sizeof(float) * dim);
-            else model_store(&io, fx[u] - 1, sum);
-        }
-        {
-            int s = nu;
-            while (s > 0 && fx[s] == fx[nu]) --s;
-            for (int j = 0; j < dim; ++j) sum[j] = 0.0f;
-            for (int q = s; q < nu; ++q) for (int j = 0; j < dim; ++j) sum[j] += carry[(size_t)q * dim + j];
-            memcpy(tcarry + (size_t)t * dim, sum, sizeof(float) * dim);
-        }
+        free(fx); free(fy); free(carry); free(head); free(has_head); free(acc); free(sum);
     }
     /* cross-tile fix-up */
-    for (int t = 1; t < T; ++t) {
-        if (!(tx[t] >= 1 && tx[t + 1] > tx[t] && ty[t] > row_ptr[tx[t] - 1])) continue;
-        int f = t;
-        while (f > 0 && tx[f - 1] == tx[t]) --f; /* first tile that starts in this row */
-        const int s = f - 1, len = t - s;
-        for (int j = 0; j < dim; ++j) sum[j] = 0.0f;
-        if (len > long_chain) {
-            for (int g = 0; g < 16; ++g) {
-                float *sg = strand + (size_t)g * dim;
-                for (int j = 0; j < dim; ++j) sg[j] = 0.0f;
-                for (int q = s + g; q < t; q += 16) for (int j = 0; j < dim; ++j) sg[j] += tcarry[(size_t)q * dim + j];
+#pragma omp parallel
+    {
+        float *sum = malloc(sizeof(float) * dim);
+        float *strand = malloc(sizeof(float) * 16 * dim);
+#pragma omp for schedule(dynamic, 256)
+        for (int t = 1; t < T; ++t) {
+            if (!(tx[t] >= 1 && tx[t + 1] > tx[t] && ty[t] > row_ptr[tx[t] - 1])) continue;
+            int f = t;
+            while (f > 0 && tx[f - 1] == tx[t]) --f; /* first tile that starts in this row */
+            const int s = f - 1, len = t - s;
+            for (int j = 0; j < dim; ++j) sum[j] = 0.0f;
+            if (len > long_chain) {
+                for (int g = 0; g < 16; ++g) {
+                    float *sg = strand + (size_t)g * dim;
+                    for (int j = 0; j < dim; ++j) sg[j] = 0.0f;
+                    for (int q = s + g; q < t; q += 16) for (int j = 0; j < dim; ++j) sg[j] += tcarry[(size_t)q * dim + j];
+                }
+                for (int g = 0; g < 16; ++g) for (int j = 0; j < dim; ++j) sum[j] += strand[(size_t)g * dim + j];
+            } else {
+                for (int q = s; q < t; ++q) for (int j = 0; j < dim; ++j) sum[j] += tcarry[(size_t)q * dim + j];
             }
-            for (int g = 0; g < 16; ++g) for (int j = 0; j < dim; ++j) sum[j] += strand[(size_t)g * dim + j];
-        } else {
-            for (int q = s; q < t; ++q) for (int j = 0; j < dim; ++j) sum[j] += tcarry[(size_t)q * dim + j];
+            for (int j = 0; j < dim; ++j) sum[j] += thead[(size_t)t * dim + j];
+            model_store(&io, tx[t] - 1, sum);
         }
-        for (int j = 0; j < dim; ++j) sum[j] += thead[(size_t)t * dim + j];
-        model_store(&io, tx[t] - 1, sum);
+        free(sum); free(strand);
     }
-    free(tx); free(ty); free(tcarry); free(thead); free(fx); free(fy); free(carry); free(head);
-    free(has_head); free(acc); free(sum); free(strand);
+    free(tx); free(ty); free(tcarry); free(thead);
     return 0;
+}
+
+/* Layout given the way a whole-chunk plan reports it: nch chunks per tile, cpu chunks per unit, ipt from `cost`;
+ * unit_items > 0 overrides cpu * ipt (sub-chunk units: a unit is a part of one chunk). */
+static int tile_model_impl(const int *row_ptr, const int *col, const void *val, const float *row_scale, const float *col_scale,
+                           const void *B, void *C, int n_rows, int nnz, int dim, int is_half, int cost, int nch, int cpu,
+                           int long_chain, int64_t unit_items) {
+    if (cost < 1 || nch < 1 || cpu < 1 || nch % cpu != 0) return -1;
+    const int P = orc_chunk_count(n_rows, nnz, cost);
+    const int64_t ipt = orc_items_per_chunk(n_rows, nnz, P);
+    if (unit_items <= 0) unit_items = ipt * cpu;
+    return tile_model_items(row_ptr, col, val, row_scale, col_scale, B, C, n_rows, nnz, dim, is_half, unit_items, nch / cpu, long_chain);
 }
 
 ORC_API int orc_tile_model(const int *row_ptr, const int *col, const void *val, const void *B,
                            void *C, int n_rows, int nnz, int dim, int is_half, int cost,
-                           int nch, int cpu, int long_chain) {
-    return tile_model_impl(row_ptr, col, val, NULL, NULL, B, C, n_rows, nnz, dim, is_half, cost, nch, cpu, long_chain);
+                           int nch, int cpu, int long_chain, int64_t unit_items) {
+    return tile_model_impl(row_ptr, col, val, NULL, NULL, B, C, n_rows, nnz, dim, is_half, cost, nch, cpu, long_chain, unit_items);
 }
 
 /* The scaled variant (fp32): value(i,j) = row_scale[i] * col_scale[j]; the column factor enters each fused
@@ -429,8 +465,8 @@ ORC_API int orc_tile_model(const int *row_ptr, const int *col, const void *val, 
  * at src/MergePathSpMM.cu:436-441. */
 ORC_API int orc_tile_model_scaled(const int *row_ptr, const int *col, const float *row_scale, const float *col_scale,
                                   const float *B, float *C, int n_rows, int nnz, int dim, int cost, int nch, int cpu,
-                                  int long_chain) {
-    return tile_model_impl(row_ptr, col, NULL, row_scale, col_scale, B, C, n_rows, nnz, dim, 0, cost, nch, cpu, long_chain);
+                                  int long_chain, int64_t unit_items) {
+    return tile_model_impl(row_ptr, col, NULL, row_scale, col_scale, B, C, n_rows, nnz, dim, 0, cost, nch, cpu, long_chain, unit_items);
 }
 
 /* Nnz-balanced row slabs for G devices: bounds[g] = first row whose start

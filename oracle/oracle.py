@@ -59,9 +59,9 @@ def lib():
         L.orc_spmm_f32_omp.restype = C.c_int
         L.orc_spmm_f32_omp.argtypes = [_i32p, _i32p, vp, vp, vp, C.c_int, C.c_int, C.c_int]
         L.orc_tile_model.restype = C.c_int
-        L.orc_tile_model.argtypes = [_i32p, _i32p, vp, vp, vp] + [C.c_int] * 8
+        L.orc_tile_model.argtypes = [_i32p, _i32p, vp, vp, vp] + [C.c_int] * 8 + [C.c_int64]
         L.orc_tile_model_scaled.restype = C.c_int
-        L.orc_tile_model_scaled.argtypes = [_i32p, _i32p, vp, vp, vp, vp] + [C.c_int] * 7
+        L.orc_tile_model_scaled.argtypes = [_i32p, _i32p, vp, vp, vp, vp] + [C.c_int] * 7 + [C.c_int64]
         L.orc_slab_bounds.restype = None
         L.orc_slab_bounds.argtypes = [_i32p, C.c_int, C.c_int, _i32p]
         _lib = L
@@ -154,27 +154,28 @@ def spmm_f32_omp(row_ptr, col, val, B, out=None, threads: int = 0):
     return out, used
 
 
-def tile_model(row_ptr, col, val, B, cost: int, nch: int, cpu: int, long_chain: int, is_half: bool = False) -> np.ndarray:
-    """nch = chunks per tile, cpu = chunks per unit (nch % cpu == 0)."""
+def tile_model(row_ptr, col, val, B, cost: int, nch: int, cpu: int, long_chain: int, is_half: bool = False, unit_items: int = 0) -> np.ndarray:
+    """nch = chunks per tile, cpu = chunks per unit (nch % cpu == 0); a unit holds cpu * items_per_chunk(cost) merge
+    items unless unit_items > 0 names another count (sub-chunk units).  A tile is nch // cpu units."""
     rp, ci = _i32(row_ptr), _i32(col)
     v, Bm = _store(val, is_half), _store(B, is_half)
     n, dim = len(rp) - 1, Bm.shape[1]
     out = np.zeros((n, dim), np.float16 if is_half else np.float32)
     rc = lib().orc_tile_model(rp, ci, _ptr(v), _ptr(Bm), _ptr(out), n, int(rp[-1]), dim, int(is_half),
-                              cost, nch, cpu, long_chain)
+                              cost, nch, cpu, long_chain, unit_items)
     if rc != 0:
         raise ValueError("orc_tile_model: bad arguments")
     return out
 
 
-def tile_model_scaled(row_ptr, col, row_scale, col_scale, B, cost: int, nch: int, cpu: int, long_chain: int) -> np.ndarray:
+def tile_model_scaled(row_ptr, col, row_scale, col_scale, B, cost: int, nch: int, cpu: int, long_chain: int, unit_items: int = 0) -> np.ndarray:
     """Model of mps_spmm_scaled: value(i, j) = row_scale[i] * col_scale[j], row factor applied to the finished row;
     a scale given as None is all ones."""
     rp, ci = _i32(row_ptr), _i32(col)
     rs, cs, Bm = (None if a is None else np.ascontiguousarray(a, np.float32) for a in (row_scale, col_scale, B))
     n, dim = len(rp) - 1, Bm.shape[1]
     out = np.zeros((n, dim), np.float32)
-    rc = lib().orc_tile_model_scaled(rp, ci, _ptr(rs), _ptr(cs), _ptr(Bm), _ptr(out), n, int(rp[-1]), dim, cost, nch, cpu, long_chain)
+    rc = lib().orc_tile_model_scaled(rp, ci, _ptr(rs), _ptr(cs), _ptr(Bm), _ptr(out), n, int(rp[-1]), dim, cost, nch, cpu, long_chain, unit_items)
     if rc != 0:
         raise ValueError("orc_tile_model_scaled: bad arguments")
     return out

@@ -138,7 +138,7 @@ def test_backward_product_through_the_transpose(mps, orc, cuda):
     plan.sync_check()
     info = plan.info()
     h_rp, h_col, h_val = (t.cpu().numpy() for t in (rp_t, col_t, val_t))
-    model = orc.tile_model(h_rp, h_col, h_val, dC, 8, info["chunks_per_tile"], info["chunks_per_unit"], info["long_chain"])
+    model = orc.tile_model(h_rp, h_col, h_val, dC, 8, info["chunks_per_tile"], info["chunks_per_unit"], info["long_chain"], unit_items=info["unit_items"])
     assert np.array_equal(got.view(np.uint32), model.view(np.uint32))
     # against the definition, without using the transposed arrays: dB[j] = sum over (i, j) of a_ij * dC[i]
     want = np.zeros((n_cols, dim), np.float64)

@@ -28,6 +28,7 @@ def test_reads_the_writers_format(tmp_path, mps):
     "0,2,3,3,5\n1,2,0,0,3",        # no trailing commas
     "0,2,3,3,5,\n1,2,0,0,3,\n",    # final newline
     " 0, 2,\t3,3, 5,\n 1,2, 0,0,3,\nignored third line",  # blanks before numbers, extra line
+    "0 ,2\t,3,3,5 ,\n1,2 ,0,0,3 ",                        # blanks after numbers (stoi stops at them)
     "+0,2,3,3,5,\n1,2,0,0,3,",
 ])
 def test_accepted_variants(tmp_path, mps, text):
@@ -126,3 +127,43 @@ def test_binary_sidecar_round_trip(tmp_path, mps, graphs):
         f.truncate(100)
     with pytest.raises(mps.MpsError):
         mps.load_csr_bin(p)
+
+
+def test_columns_beyond_the_rows_need_the_rect_loader(tmp_path, mps):
+    """scripts/npz_to_csr.py builds its matrix without a shape: a destination above every source gives columns >= N."""
+    p = str(tmp_path / "wide.csr")
+    _write(p, "0,2,3,\n1,7,0,")
+    with pytest.raises(mps.MpsError) as e:
+        mps.load_csr(p)
+    assert e.value.code == mps.capi.ERR_FORMAT
+    rp, col, n_cols = mps.load_csr_rect(p)
+    assert rp.tolist() == [0, 2, 3] and col.tolist() == [1, 7, 0] and n_cols == 8
+    _write(p, "0,2,3,\n1,-7,0,")
+    with pytest.raises(mps.MpsError):
+        mps.load_csr_rect(p)
+    q = str(tmp_path / "square.csr")
+    _write(q, "0,2,3,\n1,0,0,")
+    assert mps.load_csr_rect(q)[2] == 2
+
+
+def test_a_damaged_sidecar_is_rejected_like_a_damaged_text_file(tmp_path, mps):
+    rp = np.array([0, 2, 3, 3, 5], np.int32)
+    col = np.array([1, 2, 0, 0, 3], np.int32)
+    p = str(tmp_path / "g.bin")
+    mps.save_csr_bin(p, rp, col)
+    raw = bytearray(open(p, "rb").read())
+    good = bytes(raw)
+    at_col = 32 + 4 * len(rp)
+    raw[at_col + 4: at_col + 8] = np.int32(4).tobytes()            # col_idx[1] = 4 with 4 rows
+    open(p, "wb").write(raw)
+    with pytest.raises(mps.MpsError) as e:
+        mps.load_csr_bin(p)
+    assert e.value.code == mps.capi.ERR_FORMAT and "col_idx[1]" in str(e.value)
+    raw = bytearray(good)
+    raw[32 + 8: 32 + 12] = np.int32(1).tobytes()                   # row_ptr = 0,2,1,...
+    open(p, "wb").write(raw)
+    with pytest.raises(mps.MpsError) as e:
+        mps.load_csr_bin(p)
+    assert e.value.code == mps.capi.ERR_FORMAT and "row_ptr decreases" in str(e.value)
+    open(p, "wb").write(good)
+    assert mps.load_csr_bin(p)[0].tolist() == rp.tolist()

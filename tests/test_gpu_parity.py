@@ -47,7 +47,7 @@ def _run(mps, cuda, rp, col, val, B, cost, tune=None, tpw=1):
 
 def _check(orc, rp, col, val, B, got, info, cost, tol):
     half = B.dtype == np.float16
-    model = orc.tile_model(rp, col, val, B, cost, info["chunks_per_tile"], info["chunks_per_unit"], info["long_chain"], is_half=half)
+    model = orc.tile_model(rp, col, val, B, cost, info["chunks_per_tile"], info["chunks_per_unit"], info["long_chain"], is_half=half, unit_items=info["unit_items"])
     assert not np.isnan(got.astype(np.float32)).any(), "some element of C was never written"
     same = _bits(got) == _bits(model)
     assert same.all(), f"{(~same).sum()} elements differ from the CPU model (first at {np.argwhere(~same)[0]})"
@@ -360,7 +360,7 @@ def test_scaled_product_bit_exact_with_its_model(mps, orc, graphs, cuda, dim, tu
     plan.sync_check()
     info = plan.info()
     got = out.cpu().numpy()
-    model = orc.tile_model_scaled(rp, col, rs, cs, B, 8, info["chunks_per_tile"], info["chunks_per_unit"], info["long_chain"])
+    model = orc.tile_model_scaled(rp, col, rs, cs, B, 8, info["chunks_per_tile"], info["chunks_per_unit"], info["long_chain"], unit_items=info["unit_items"])
     assert np.array_equal(_bits(got), _bits(model))
     rows = np.repeat(np.arange(n), np.diff(rp))
     val = (rs.astype(np.float64)[rows] * cs.astype(np.float64)[col]).astype(np.float32)
@@ -368,7 +368,7 @@ def test_scaled_product_bit_exact_with_its_model(mps, orc, graphs, cuda, dim, tu
     assert (np.abs(got.astype(np.float64) - orc.spmm_f64(rp, col, val, B)) <= 2e-6 + 2e-5 * scale).all()
     # the unscaled entry point still works on the same plan afterwards
     plain = plan.spmm(d_rp, d_col, None, d_B).cpu().numpy()
-    assert np.array_equal(_bits(plain), _bits(orc.tile_model(rp, col, None, B, 8, info["chunks_per_tile"], info["chunks_per_unit"], info["long_chain"])))
+    assert np.array_equal(_bits(plain), _bits(orc.tile_model(rp, col, None, B, 8, info["chunks_per_tile"], info["chunks_per_unit"], info["long_chain"], unit_items=info["unit_items"])))
     plan.close()
     with pytest.raises(mps.MpsError) as e:
         ph = mps.Plan(n, nnz, 16, mps.F16, 8, device=cuda)
@@ -392,7 +392,7 @@ def test_scaled_product_on_long_rows(mps, orc, cuda):
         got = plan.spmm_scaled(*d).cpu().numpy()
         plan.sync_check()
         info = plan.info()
-        model = orc.tile_model_scaled(rp, col, rs, cs, B, 1, info["chunks_per_tile"], info["chunks_per_unit"], info["long_chain"])
+        model = orc.tile_model_scaled(rp, col, rs, cs, B, 1, info["chunks_per_tile"], info["chunks_per_unit"], info["long_chain"], unit_items=info["unit_items"])
         assert np.array_equal(_bits(got), _bits(model)), tune
         plan.close()
 
@@ -410,7 +410,7 @@ def test_scaled_product_with_one_factor_only(mps, orc, graphs, cuda):
     d_rp, d_col, d_rs, d_cs, d_B = (_dev(a, cuda) for a in (rp, col, rs, cs, B))
     plan.partition(d_rp)
     info = plan.info()
-    shape = (8, info["chunks_per_tile"], info["chunks_per_unit"], info["long_chain"])
+    shape = (8, info["chunks_per_tile"], info["chunks_per_unit"], info["long_chain"], info["unit_items"])
     for r, c, dr, dc in ((rs, None, d_rs, None), (None, cs, None, d_cs)):
         got = plan.spmm_scaled(d_rp, d_col, dr, dc, d_B).cpu().numpy()
         plan.sync_check()
@@ -442,7 +442,7 @@ def test_row_slabs_are_bit_identical_to_their_own_model_and_close_to_the_whole(m
             srp = mps.slab_rebase(rp, r0, r1)
             scol, sval = col[rp[r0]:rp[r1]], val[rp[r0]:rp[r1]]
             got, info = _run(mps, cuda, srp, scol, sval, B, 8)
-            model = orc.tile_model(srp, scol, sval, B, 8, info["chunks_per_tile"], info["chunks_per_unit"], info["long_chain"])
+            model = orc.tile_model(srp, scol, sval, B, 8, info["chunks_per_tile"], info["chunks_per_unit"], info["long_chain"], unit_items=info["unit_items"])
             assert np.array_equal(_bits(got), _bits(model))
             parts.append(got)
         cat = np.concatenate(parts)

@@ -1,5 +1,5 @@
-"""The N > 1 host logic on CPU ranks (gloo, world sizes 2 and 3): slab bounds, rebasing, the padded
-all-gather of C.  The multiply itself is the GPU's job; here each rank fills its slab with the
+"""The N > 1 host logic on CPU ranks (gloo, world sizes 2 and 3): slab bounds, rebasing, B completed from
+per-rank blocks, the unpadded gather of C.  The multiply itself is the GPU's job; here each rank fills its slab with the
 oracle's fp64 loop (as the checker's stand-in) so that the plumbing can be verified without a GPU."""
 import os
 import socket
@@ -44,6 +44,11 @@ def _worker(rank, world, port, out_dir):
     full = multi.gather_c(c_slab, bounds)
     want = orc.spmm_f64(rp, col, val, B).astype(np.float32)
     ok = bool(np.array_equal(full.numpy(), want))
+    # B from per-rank blocks: every rank contributes rows [b0, b1) only and ends with all of B
+    b0, b1, blk = multi.b_block(n, rank, world)
+    assert blk * world >= n and (rank < world - 1 or b1 == n)
+    whole = multi.replicate_b(torch.from_numpy(B[b0:b1].copy()), n)
+    ok = ok and whole.shape == (n, 8) and bool(np.array_equal(whole.numpy(), B))
     # torch tensors take the same path as numpy arrays
     r0t, r1t, srp_t, scol_t, sval_t = multi.slab_of(torch.from_numpy(rp), torch.from_numpy(col), torch.from_numpy(val), rank, world)
     ok = ok and (r0t, r1t) == (r0, r1) and np.array_equal(srp_t.numpy(), srp) and np.array_equal(scol_t.numpy(), scol)
