@@ -28,7 +28,7 @@ def test_host_arm_line():
 
 @pytest.mark.gpu
 def test_default_arm_line_on_a_small_graph(cuda):
-    out = _run("--steps", "5", "--warmup", "3", "--scale", "15", "--e2e-steps", "1")
+    out = _run("--steps", "5", "--warmup", "3", "--scale", "15", "--e2e-steps", "1", "--c5-scale", "14", "--c5-degree", "16", "--c5-steps", "3")
     for key in ("metric", "value", "unit", "n_gpus", "steps", "warmup", "ms_per_step", "higher_is_better", "scaling", "vs_baseline",
                 "dtype", "data", "config", "roofline", "e2e", "gpu_launches", "clocks", "cpu_baseline"):
         assert key in out, key
@@ -38,3 +38,12 @@ def test_default_arm_line_on_a_small_graph(cuda):
     assert out["e2e"]["h2d_bytes_per_step"] > 0 and out["e2e"]["d2h_bytes_per_step"] > 0 and out["e2e"]["value"] < out["value"]
     assert out["gpu_launches"] >= 5 and "workload" in out["config"]
     assert out["cpu_baseline"]["kind"] == "port" and out["cpu_baseline"]["value"] > 0
+    # the line looks at what it timed, and carries bounds that are fractions of a peak
+    assert out["check"]["ok"] is True and out["check"]["rows"] >= 4000 and out["check"]["max_scaled_err"] <= 1.0
+    assert out["e2e"]["check"]["ok"] is True
+    r = out["roofline"]
+    assert 0 < r["compulsory_frac"] < 1.5 and r["l2_peak_gbs"] > r["hbm_gather_gbs"] > 0 and 0 < r["l2_frac"] < 1.5
+    assert r["nearest_bound"] in ("hbm_compulsory", "l2_gather", "hbm_measured_traffic")
+    c5 = out["c5_strong"]
+    assert c5["scaling"] == "strong" and c5["check"]["ok"] is True and c5["ms_per_step"] > 0 and c5["n_gpus"] == 1
+    assert out["reference_gpu"].get("best", {}).get("cost") in (8, 32) or "unavailable" in out["reference_gpu"]

@@ -426,6 +426,69 @@ def test_scaled_product_with_one_factor_only(mps, orc, graphs, cuda):
     plan.close()
 
 
+def test_mid_size_graph_unfused_by_size_is_bit_exact_with_the_cpu_model(mps, orc, graphs, cuda):
+    """Above 2048 tiles the cross-tile fix-up is the separate fixup_kernel (four columns per lane, its first blocks for
+    the rows that span more than 32 tiles) - the form every large multiply takes.  R-MAT 2^17 reaches it by size alone."""
+    rp, col = graphs.rmat_csr(17, 32, seed=9)
+    val = graphs.gcn_values(rp, col)
+    n = len(rp) - 1
+    for dim, half in ((32, False), (64, False), (16, False), (128, True), (20, False)):
+        if half:
+            B, v = graphs.dense_normal_f16(n, dim, seed=6), val.astype(np.float16)
+        else:
+            B, v = graphs.dense_uniform(n, dim, seed=6), val
+        got, info = _run(mps, cuda, rp, col, v, B, 16)
+        assert info["n_tiles"] > 2048 and info["fused_fixup"] == 0 and info["kernels_per_call"] == 2, info
+        _check(orc, rp, col, v, B, got, info, 16, 1e-2 if half else 1e-5)
+    assert info["long_rows"] >= 0
+
+
+@pytest.mark.parametrize("dim", [4, 16, 64, 128])
+@pytest.mark.parametrize("cost", [1000, 10000, 10**7])
+def test_costs_beyond_one_tile_are_cut_into_sub_chunk_units(mps, orc, graphs, cuda, dim, cost):
+    """The reference's command line takes any cost; a chunk longer than a tile can stage is walked as several units."""
+    rp, col = graphs.rmat_csr(17, 16, seed=4)
+    val = graphs.gcn_values(rp, col)
+    B = graphs.dense_uniform(len(rp) - 1, dim, seed=5)
+    got, info = _run(mps, cuda, rp, col, val, B, cost)
+    assert info["shared_bytes_per_block"] <= 64 * 1024
+    if cost >= 10000:
+        assert info["units_per_chunk"] > 1
+    _check(orc, rp, col, val, B, got, info, cost, 1e-5)
+
+
+def test_host_call_with_b_already_on_the_device(mps, graphs, cuda):
+    """mps_spmm_host_resident_b: A and C are host buffers, B is a device buffer that another stream is still
+    completing when the call starts; the result equals the all-host call bit for bit."""
+    rp, col = graphs.rmat_csr(19, 32, seed=3)
+    val = graphs.gcn_values(rp, col)
+    n = len(rp) - 1
+    B = graphs.dense_uniform(n, 32, seed=4)
+    want = mps.spmm_host(rp, col, val, B, cost=16)
+    side = torch.cuda.Stream(device=cuda)
+    d_B = torch.empty((n, 32), dtype=torch.float32, device=cuda)
+    hB = torch.from_numpy(B).pin_memory()
+    pinned = [torch.from_numpy(a).pin_memory() for a in (rp, col, val)]
+    out = torch.full((n, 32), float("nan"), dtype=torch.float32).pin_memory()
+    for _ in range(2):
+        d_B.zero_()
+        torch.cuda.synchronize()
+        with torch.cuda.stream(side):
+            d_B.copy_(hB, non_blocking=True)       # B arrives on another stream while A uploads
+            mps.spmm_host_resident_b(*pinned, d_B, out, cost=16, stream=side)
+        assert np.array_equal(_bits(out.numpy()), _bits(want))
+        out.fill_(float("nan"))
+    mps.capi.lib().mps_host_workspace_release()
+
+
+def test_gather_probe_reports_a_plausible_rate(mps, cuda):
+    small = torch.zeros(32 << 20, dtype=torch.uint8, device=cuda)     # inside the L2
+    rate = mps.gather_probe(small, 256, 1 << 24)
+    assert 1000.0 < rate < 100000.0, rate                              # GB/s
+    with pytest.raises(mps.MpsError):
+        mps.gather_probe(small, 100, 1 << 20)
+
+
 # ------------------------------------------------------------------ slabs
 
 def test_row_slabs_are_bit_identical_to_their_own_model_and_close_to_the_whole(mps, orc, graphs, cuda):

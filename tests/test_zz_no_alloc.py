@@ -74,6 +74,29 @@ def test_noalloc_unit_values_and_other_cost(mps, graphs, cuda):
         assert torch.equal(out, want)
 
 
+def test_noalloc_mid_size_runs_the_separate_fixup_on_the_static_array(mps, graphs, cuda):
+    """Between 2,049 and 32,768 tiles the cross-tile fix-up is a kernel of its own that reads the tile carries, the
+    per-tile counts and the long-row list out of the static array; twice in a row, with a small problem in between
+    that overwrites the front of the array."""
+    rp, col = graphs.rmat_csr(17, 32, seed=9)
+    val = graphs.gcn_values(rp, col)
+    B = graphs.dense_uniform(len(rp) - 1, 32, seed=6)
+    big = [torch.from_numpy(np.ascontiguousarray(a)).to(cuda) for a in (rp, col, val, B)]
+    lay = mps.layout_query(len(rp) - 1, len(col), 32, mps.F32, 16)
+    assert 2048 < lay["n_tiles"] <= 32768 and lay["fused_fixup"] == 0
+    want = _with_plan(mps, cuda, *big, cost=16)
+    small = _problem(graphs, cuda, "rmat_f32")
+    want_small = _with_plan(mps, cuda, *small, cost=8)
+    out = torch.empty_like(want)
+    out_small = torch.empty_like(want_small)
+    for _ in range(2):
+        out.fill_(float("nan"))
+        mps.spmm_noalloc(*big, out=out, cost=16)
+        assert torch.equal(out, want)
+        mps.spmm_noalloc(*small, out=out_small, cost=8)
+        assert torch.equal(out_small, want_small)
+
+
 def test_noalloc_refuses_what_does_not_fit(mps, cuda):
     """The shape is refused before any pointer is used.  It is chosen so that it cannot fit under any
     tile layout: 2*10^9 merge items need more than 32,768 tiles even if a tile filled all of an SM's
