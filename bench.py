@@ -68,6 +68,8 @@ def parse_args():
     ap.add_argument("--c5-degree", type=int, default=64)
     ap.add_argument("--c5-dim", type=int, default=32)
     ap.add_argument("--c5-steps", type=int, default=20)
+    ap.add_argument("--hot-mb", type=float, default=-1.0, help="MB of B rows marked to stay in the L2 (mps_plan_mark_hot_columns); 0 = off, -1 = automatic")
+    ap.add_argument("--slab", default="", help="R/N: on one GPU, the workload of rank R of an N-GPU run (graph of 2^scale * N nodes, slab R of N) - for profiling")
     ap.add_argument("--no-probe", action="store_true", help="leave out the gather-rate probe (roofline.l2_peak_gbs)")
     return ap.parse_args()
 
@@ -186,7 +188,7 @@ def check_product(rp, col, val, B, C_out, half, seed=0, n_random=4096, n_long=32
     lens = (rp[1:] - rp[:-1]).long()
     g = torch.Generator(device="cpu")
     g.manual_seed(seed)
-    rows = torch.unique(torch.cat([torch.randint(0, max(n, 1), (n_random,), generator=g).to(dev), torch.topk(lens, min(n_long, n)).indices,
+    rows = torch.unique(torch.cat([torch.randperm(max(n, 1), generator=g)[:n_random].to(dev), torch.topk(lens, min(n_long, n)).indices,
                                    torch.tensor([0, n - 1], device=dev)]))
     l = lens[rows]
     total = int(l.sum().item())
@@ -236,13 +238,17 @@ def build_workload(args, world, rank, dev):
     from mergepath_spmm_b200 import graphs
     mps = entry.load_package()
     scale = total_scale(args, world)
+    cut, piece = world, rank
+    if args.slab and world == 1:  # one rank's share of a larger run, alone on this GPU
+        piece, cut = (int(v) for v in args.slab.split("/"))
+        scale = total_scale(args, cut)
     rp, col = graphs.rmat_csr(scale, args.avg_degree, args.seed, device=dev)
     n, nnz = rp.numel() - 1, col.numel()
     half = args.dtype == "f16"
     val = graphs.gcn_values(rp, col, "f16" if half else "f32")
-    if world > 1:
-        bounds = mps.slab_bounds(rp.cpu().numpy(), world, args.balance, args.row_weight)
-        r0, r1 = int(bounds[rank]), int(bounds[rank + 1])
+    if cut > 1:
+        bounds = mps.slab_bounds(rp.cpu().numpy(), cut, args.balance, args.row_weight)
+        r0, r1 = int(bounds[piece]), int(bounds[piece + 1])
         k0, k1 = int(rp[r0].item()), int(rp[r1].item())
         s_rp = (rp[r0:r1 + 1] - k0).contiguous()
         s_col, s_val = col[k0:k1].clone(), val[k0:k1].clone()
@@ -266,6 +272,9 @@ def total_scale(args, world):
 
 
 def workload_name(args, world):
+    if args.slab and world == 1:
+        piece, cut = (int(v) for v in args.slab.split("/"))
+        return f"rmat{total_scale(args, cut)}_deg{args.avg_degree}_gcn_{args.dtype}_dim{args.dim}_slab{piece}of{cut}"
     return f"rmat{total_scale(args, world)}_deg{args.avg_degree}_gcn_{args.dtype}_dim{args.dim}"
 
 
@@ -384,7 +393,8 @@ def e2e_through_host_call(mps, args, w, world, rank, dev, cost, dt, n_slab, nnz_
     ok = bool(min_over_ranks(1.0 if chk["ok"] else 0.0, world) > 0.5)
     mps.capi.lib().mps_host_workspace_release()
     host = {k: (h[k].numpy() if h[k] is not None else None) for k in h} if world == 1 else None
-    return {"value": round(2.0 * w["nnz"] * args.dim / e2e_s / 1e9, 2), "unit": "GFLOP/s", "h2d_bytes_per_step": int(sum_over_ranks(h2d, world)),
+    flop_nnz = nnz_slab if (args.slab and world == 1) else w["nnz"]
+    return {"value": round(2.0 * flop_nnz * args.dim / e2e_s / 1e9, 2), "unit": "GFLOP/s", "h2d_bytes_per_step": int(sum_over_ranks(h2d, world)),
             "d2h_bytes_per_step": int(sum_over_ranks(d2h, world)), "ms_per_step": round(e2e_s * 1e3, 3), "steps": steps,
             "b_replication": "each rank uploads 1/N of B, NCCL all-gather over NVLink" if world > 1 else "one upload",
             "check": {"ok": ok, "max_scaled_err": max_over_ranks(chk["max_scaled_err"], world), "rows": int(sum_over_ranks(chk["rows"], world))}}, host
@@ -481,7 +491,7 @@ def run_ours(args):
     per_rank_ms = all_ranks(ms_mine / args.steps, world)
     plan.sync_check()
     ms_step = ms_total / args.steps
-    flops = 2.0 * w["nnz"] * args.dim
+    flops = 2.0 * (nnz_slab if (args.slab and world == 1) else w["nnz"]) * args.dim
     value = flops / (ms_step * 1e-3) / 1e9
 
     # ---- a look at what was timed (outside the timed region), every rank ----

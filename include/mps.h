@@ -193,6 +193,18 @@ MPS_API int mps_spmm(mps_plan *plan, const int32_t *d_row_ptr, const int32_t *d_
 MPS_API int mps_spmm_scaled(mps_plan *plan, const int32_t *d_row_ptr, const int32_t *d_col_idx,
                     const float *d_row_scale, const float *d_col_scale, const void *d_B, void *d_C, void *stream);
 
+/* Optional, after mps_plan_create (no reference counterpart): tells the multiply which rows of B the L2 should keep.
+ * Counts the occurrences of every column in d_col_idx (the col_idx that mps_spmm will be given; n_cols = rows of B),
+ * marks the most frequent columns until their rows of B fill `budget_bytes` (something like half of the 126 MB L2), and
+ * keeps a marked copy of col_idx inside the plan (4 bytes per non-zero).  From then on mps_spmm on this plan gathers
+ * marked rows with an L2 evict-last policy and the others with evict-first, and reads the plan's copy instead of the
+ * caller's col_idx - so call this again if the indices change.  Pays when B is many times the L2 (a rank of a
+ * multi-GPU job keeps all of B); budget_bytes <= 0 removes the marking.  Results are bit-identical either way.
+ * *hot_columns / *hot_nnz (may be NULL): how many columns were marked and how many non-zeros refer to them.
+ * Allocates, synchronises the stream. */
+MPS_API int mps_plan_mark_hot_columns(mps_plan *plan, const int32_t *d_col_idx, int32_t n_cols, int64_t budget_bytes,
+                              void *stream, int64_t *hot_columns, int64_t *hot_nnz);
+
 /* Waits for the stream and returns MPS_ERR_DEVICE if any kernel of this plan gave up a wait (a tile block whose
  * staged window did not arrive in time fetches it again with plain loads and finishes its rows, but the call
  * counts as failed: treat C as undefined until this returns MPS_OK). */
@@ -210,11 +222,23 @@ MPS_API int mps_plan_info(const mps_plan *plan, int64_t what[16]);
  * what[4]=units per reference chunk (1 unless `cost` asks for chunks longer than a tile can stage: then a
  * unit is the what[4]-th part of a chunk and what[0] = ceil(items_per_chunk / what[4]); any `cost` the
  * reference's command line accepts is therefore accepted here), what[5]=shared bytes per block,
- * what[6]=column slabs, what[7]=1 when the tile kernel performs the cross-tile fix-up itself.
+ * what[6]=column slabs, what[7]=1 when the tile kernel performs the cross-tile fix-up itself,
+ * what[8]=lane groups that share a unit (1, or 32 / lanes_per_chunk when a whole warp walks a unit, see
+ * mps_plan_set_walk), what[9..11]=0 (reserved).
  * mps_layout_query gives the same numbers for a shape without a plan or a CUDA device (the automatic
  * layout for 148 SMs). */
-MPS_API int mps_plan_layout(const mps_plan *plan, int64_t what[8]);
-MPS_API int mps_layout_query(int32_t n_rows, int32_t nnz, int32_t dim, int dtype, int32_t cost, int64_t what[8]);
+MPS_API int mps_plan_layout(const mps_plan *plan, int64_t what[12]);
+MPS_API int mps_layout_query(int32_t n_rows, int32_t nnz, int32_t dim, int dtype, int32_t cost, int64_t what[12]);
+
+/* How a unit is walked (no reference counterpart in form; in substance this is the reference's choice of
+ * threads_per_warp, src/MergePathSpMM.cu:224-243: how many chunks a warp takes at once).  0: every group of
+ * lanes_per_chunk lanes walks a unit of its own (a warp at dim 16 walks eight units side by side).  1: the whole warp
+ * walks one unit - its lane groups take consecutive non-zeros, keep partial sums of the row in progress and combine
+ * them with xor-shuffles in a fixed tree at every row end - so no lane idles where neighbouring units would end
+ * their rows at different places.  -1: automatic.  Full-width lanes (dim a multiple of 4 fp32 / 8 fp16, fewer than 32
+ * lanes per row), 64-thread blocks and unroll 8 only; elsewhere the setting is ignored.  Changes the summation order
+ * (still fixed and reproducible); call before mps_plan_partition. */
+MPS_API int mps_plan_set_walk(mps_plan *plan, int32_t warp_per_unit);
 
 /* Per-kernel timing (no reference counterpart; the reference is timed from outside with nvprof,
  * README.md:41-46): while enabled, every mps_spmm records a CUDA event pair around its tile

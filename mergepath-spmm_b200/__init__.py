@@ -108,6 +108,12 @@ class Plan:
             capi.check(capi.lib().mps_plan_tune(self._h, chunks_per_unit, unroll, int(bulk_staging), block_threads, fused_fixup))
         return self
 
+    def set_walk(self, warp_per_unit: int = -1):
+        """1: a whole warp walks a unit (lane groups combined with shuffles at row ends); 0: a lane group per unit; -1: automatic."""
+        with torch.cuda.device(self.device):
+            capi.check(capi.lib().mps_plan_set_walk(self._h, warp_per_unit))
+        return self
+
     def partition(self, row_ptr, stream=None):
         _need_cuda(row_ptr)
         with torch.cuda.device(self.device):
@@ -134,6 +140,14 @@ class Plan:
                                                   _dev_ptr(B), _dev_ptr(out), _stream_ptr(stream)))
         return out
 
+    def mark_hot_columns(self, col_idx, n_cols: int, budget_bytes: int, stream=None) -> tuple[int, int]:
+        """Rows of B that the L2 should keep (mps_plan_mark_hot_columns); returns (columns marked, non-zeros that hit them)."""
+        _need_cuda(col_idx)
+        a, b = C.c_int64(), C.c_int64()
+        with torch.cuda.device(self.device):
+            capi.check(capi.lib().mps_plan_mark_hot_columns(self._h, _dev_ptr(col_idx), n_cols, budget_bytes, _stream_ptr(stream), C.byref(a), C.byref(b)))
+        return a.value, b.value
+
     def sync_check(self, stream=None):
         with torch.cuda.device(self.device):
             capi.check(capi.lib().mps_plan_sync_check(self._h, _stream_ptr(stream)))
@@ -153,18 +167,18 @@ class Plan:
         arr = (C.c_int64 * 16)()
         capi.check(capi.lib().mps_plan_info(self._h, arr))
         out = dict(zip(self.INFO, [int(v) for v in arr]))
-        lay = (C.c_int64 * 8)()
+        lay = (C.c_int64 * 12)()
         capi.check(capi.lib().mps_plan_layout(self._h, lay))
         out.update(zip(LAYOUT, [int(v) for v in lay]))
         return out
 
 
-LAYOUT = ("unit_items", "units_per_tile", "tile_items", "n_tiles", "units_per_chunk", "shared_bytes_per_block", "column_slabs", "fused_fixup")
+LAYOUT = ("unit_items", "units_per_tile", "tile_items", "n_tiles", "units_per_chunk", "shared_bytes_per_block", "column_slabs", "fused_fixup", "groups_per_unit")
 
 
 def layout_query(n_rows: int, nnz: int, dim: int, dtype=F32, cost: int = 8) -> dict:
     """The automatic tile layout for a shape (mps_layout_query): no plan, no CUDA device needed."""
-    lay = (C.c_int64 * 8)()
+    lay = (C.c_int64 * 12)()
     capi.check(capi.lib().mps_layout_query(n_rows, nnz, dim, dtype, cost, lay))
     return dict(zip(LAYOUT, [int(v) for v in lay]))
 

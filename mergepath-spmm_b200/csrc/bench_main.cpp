@@ -10,6 +10,8 @@
 // Installed under a name that ends in "_fp16" (the build links MergePathSpMM_fp16 to the same program) it is the
 // twin of the reference's fp16 program: the same argv, fp16 storage unless --dtype says otherwise.
 //
+// <input_file> may also be the binary sidecar that mps_csr_save_bin writes (a 10^9-edge graph is ~10 GB of text).
+//
 // Options (all optional, after the positionals):
 //   --dtype=f32|f16   --values=unit|gcn   --check   --device=K
 //   --gpus=G          row slabs of equal (nnz + 4*rows) over G devices of this node (mps_multi_*)
@@ -79,7 +81,13 @@ int main(int argc, char *argv[]) {
         if (!parse_option(argv[i], o)) { fprintf(stderr, "unknown or malformed option %s\n", argv[i]); return 2; }
 
     mps_csr g;
-    if (mps_csr_load(argv[1], 0, &g) != MPS_OK) { fprintf(stderr, "error: %s\n", mps_last_error()); return 1; }
+    {   // the reference's text file, or this library's binary sidecar of the same graph (recognised by its first bytes)
+        char magic[8] = {0};
+        if (FILE *f = fopen(argv[1], "rb")) { if (fread(magic, 1, 8, f) != 8) magic[0] = 0; fclose(f); }
+        const bool sidecar = memcmp(magic, "MPSCSR01", 8) == 0;
+        const int rc = sidecar ? mps_csr_load_bin(argv[1], &g, nullptr, nullptr) : mps_csr_load(argv[1], 0, &g);
+        if (rc != MPS_OK) { fprintf(stderr, "error: %s\n", mps_last_error()); return 1; }
+    }
     std::cout << "Total number of rows: " << g.n_rows << " and non-zeros: " << g.nnz << std::endl;
     if (dim < 1 || cost < 1) { fprintf(stderr, "error: dimension and cost must be >= 1\n"); return 2; }
     if (dim <= 32 && tpw > 32 / dim)
@@ -123,7 +131,10 @@ int main(int argc, char *argv[]) {
     MPS_OK_OR_DIE(mps_multi_create(o.gpus, devices.data(), g.n_rows, g.n_rows, dim, half ? MPS_F16 : MPS_F32, cost, tpw, g.row_ptr, g.col_idx,
                                    val_ptr, &m));
     const double setup_ms = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
+    MPS_OK_OR_DIE(mps_multi_set_b(m, hB.data()));  // the first call also creates the communicator
+    t0 = std::chrono::steady_clock::now();
     MPS_OK_OR_DIE(mps_multi_set_b(m, hB.data()));
+    const double set_b_ms = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
     float ms = 0, ms_gather = 0;
     MPS_OK_OR_DIE(mps_multi_spmm(m, 3, 0, &ms, nullptr));  // warm-up
     if (repeat > 0) MPS_OK_OR_DIE(mps_multi_spmm(m, repeat, o.gather_c ? 1 : 0, &ms, &ms_gather));
@@ -152,6 +163,8 @@ int main(int argc, char *argv[]) {
         printf("  device %d: rows [%d, %d)  nnz %d\n", dev, r0, r1, nz);
     }
     printf("upload + partition: %.3f ms (once)\n", setup_ms);
+    printf("B to every device: %.3f ms (%.1f MB; %s)\n", set_b_ms, (double)(cells * es) / 1e6,
+           o.gpus > 1 ? "each device uploads 1/gpus of the rows, NCCL all-gather completes them" : "one upload");
     if (repeat > 0)
         printf("time per SpMM: %.4f ms  %.1f GFLOP/s  %.1f GB/s algorithmic (max over devices)\n", ms, flops / ms / 1e6, bytes / ms / 1e6);
     if (o.gather_c) printf("all-gather of C over NCCL: %.4f ms\n", ms_gather);

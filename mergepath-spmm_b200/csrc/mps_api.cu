@@ -112,13 +112,20 @@ static const int kUnitItems = 272;           // merge items one lane group walks
 static const int kTileItemsPerThread = 17;          // merge items per tile the automatic layout aims for
 static const int kSmemLimit = 200 * 1024;
 
+static const int kWalkWarpMaxLanes = 0;  // lanes per group up to which a whole warp walks a unit by default (0: never)
 static const int kSmemSplitAbove = 48 * 1024;  // a whole-chunk tile beyond this is cut into sub-chunk units instead
 
 static int plan_layout(mps_plan *p) {
     const int elem = p->dtype == MPS_F16 ? 2 : 4;
     if (!p->user_block) p->block = 64;  // small blocks wait least at the three block barriers of a tile; 12 of them fit an SM
     if (p->block < p->gl) p->block = p->gl;
-    const int gpc = p->block / p->gl;  // units per tile
+    // a warp per unit exists for full-width lanes, 64-thread blocks and batches of eight; it pays where a warp holds
+    // several lane groups (see kWalkWarpMaxLanes)
+    const bool can_spread = p->vec > 1 && p->gl < 32 && p->block == 64 && (!p->user_unroll || p->unroll == 8);
+    if (!p->user_walk) p->walk = (can_spread && p->gl <= kWalkWarpMaxLanes) ? 1 : 0;
+    if (!can_spread) p->walk = 0;
+    const int groups = p->walk ? 32 / p->gl : 1;          // lane groups that share a unit
+    const int gpc = p->block / (p->gl * groups);          // units per tile
     const int kSmemTarget = kSmemTargetPer256 * p->block / 256, kTileItems = kTileItemsPerThread * p->block;
     if (!p->user_unroll) p->unroll = 8;
     if (p->vec == 1) p->unroll = 4;
@@ -142,7 +149,7 @@ static int plan_layout(mps_plan *p) {
         }
         long long items = total / ((long long)p->sm_count * kTilesPerSm);
         if (items > kTileItems) items = kTileItems;
-        if (items > (long long)gpc * kUnitItems) items = (long long)gpc * kUnitItems;  // wide rows: few units, keep each walk short
+        if (items > (long long)gpc * groups * kUnitItems) items = (long long)gpc * groups * kUnitItems;  // wide rows: few units, keep each walk short
         int cpu = (int)(items / ((long long)gpc * p->ipt));
         if (cpu < 1) cpu = 1;
         if (cpu > 64) cpu = 64;
@@ -205,6 +212,8 @@ static void plan_free_scratch(mps_plan *p) {
     cudaFree(p->d_tile_xy); cudaFree(p->d_tcarry); cudaFree(p->d_thead);
     cudaFree(p->d_status); cudaFree(p->d_long_list); cudaFree(p->d_long_count);
     cudaFree(p->d_consumer); cudaFree(p->d_need); cudaFree(p->d_cnt);
+    cudaFree(p->d_col_hot);
+    p->d_col_hot = nullptr;
     p->d_tile_xy = nullptr; p->d_tcarry = p->d_thead = nullptr;
     p->d_status = p->d_long_list = p->d_long_count = nullptr;
     p->d_consumer = p->d_need = p->d_cnt = nullptr;
@@ -275,6 +284,18 @@ extern "C" int mps_plan_tune(mps_plan *p, int32_t chunks_per_unit, int32_t unrol
     p->user_unroll = unroll != 0;
     if (p->user_unroll) p->unroll = unroll;
     p->bulk = bulk_staging ? 1 : 0;
+    if (int rc = plan_layout(p)) return rc;
+    p->partitioned = false;
+    if (p->n_tiles != old_tiles) return plan_alloc_scratch(p);
+    return MPS_OK;
+}
+
+extern "C" int mps_plan_set_walk(mps_plan *p, int32_t warp_per_unit) {
+    if (!p) return fail(MPS_ERR_ARG, "mps_plan_set_walk: plan is NULL");
+    if (warp_per_unit < -1 || warp_per_unit > 1) return fail(MPS_ERR_ARG, "mps_plan_set_walk: -1 (automatic), 0 or 1");
+    const int old_tiles = p->n_tiles;
+    p->user_walk = warp_per_unit >= 0;
+    if (p->user_walk) p->walk = warp_per_unit;
     if (int rc = plan_layout(p)) return rc;
     p->partitioned = false;
     if (p->n_tiles != old_tiles) return plan_alloc_scratch(p);
@@ -393,18 +414,20 @@ extern "C" int mps_plan_info(const mps_plan *p, int64_t what[16]) {
     what[4] = p->gl; what[5] = p->vec; what[6] = p->unroll; what[7] = p->smem_bytes;
     what[8] = p->n_long; what[9] = p->tpw_effective;
     what[10] = 1 + (((!p->fused && p->n_tiles > 1) || p->n_long > 0) ? 1 : 0);
-    what[11] = p->long_chain; what[12] = p->cpu; what[13] = p->block / p->gl; what[14] = p->block; what[15] = p->very_long;
+    what[11] = p->long_chain; what[12] = p->cpu; what[13] = p->tile_items / p->unit_items; what[14] = p->block; what[15] = p->very_long;
     return MPS_OK;
 }
 
-extern "C" int mps_plan_layout(const mps_plan *p, int64_t what[8]) {
+extern "C" int mps_plan_layout(const mps_plan *p, int64_t what[12]) {
     if (!p || !what) return fail(MPS_ERR_ARG, "mps_plan_layout: NULL argument");
-    what[0] = p->unit_items; what[1] = p->block / p->gl; what[2] = p->tile_items; what[3] = p->n_tiles;
+    for (int i = 0; i < 12; ++i) what[i] = 0;
+    what[0] = p->unit_items; what[1] = p->tile_items / p->unit_items; what[2] = p->tile_items; what[3] = p->n_tiles;
     what[4] = p->sub_chunk; what[5] = p->smem_bytes; what[6] = p->n_col_slabs; what[7] = p->fused;
+    what[8] = p->walk ? 32 / p->gl : 1;
     return MPS_OK;
 }
 
-extern "C" int mps_layout_query(int32_t n_rows, int32_t nnz, int32_t dim, int dtype, int32_t cost, int64_t what[8]) {
+extern "C" int mps_layout_query(int32_t n_rows, int32_t nnz, int32_t dim, int dtype, int32_t cost, int64_t what[12]) {
     if (!what) return fail(MPS_ERR_ARG, "mps_layout_query: what is NULL");
     if (dim < 1 || cost < 1) return fail(MPS_ERR_ARG, "mps_layout_query: dim and cost must be >= 1 (dim=%d cost=%d)", dim, cost);
     if (dtype != MPS_F32 && dtype != MPS_F16) return fail(MPS_ERR_ARG, "mps_layout_query: unknown dtype %d", dtype);
@@ -478,22 +501,64 @@ extern "C" void mps_host_workspace_release(void) { g_ws.release(); }
 // call, joined before the first kernel that gathers by col_idx is launched, so it runs beside the upload of B.
 struct ColumnScan {
     std::thread worker;
-    long long bad = -1;
-    void start(const int32_t *col, long long nnz, int32_t n_cols) {
-        if (!col || nnz <= 0) return;
-        if (nnz < (1 << 16)) { bad = first_bad_column(col, nnz, n_cols, 1); return; }
-        worker = std::thread([this, col, nnz, n_cols] { bad = first_bad_column(col, nnz, n_cols, 0); });
+    std::atomic<int> done{0};          // ranges checked so far
+    std::atomic<long long> bad{-1};    // position of the first index outside [0, n_cols), or -1
+    long long lo[kMaxHostSlabs], hi[kMaxHostSlabs];
+    // ranges [begin[i], end[i]) of col are checked one after the other, in this order
+    void start(const int32_t *col, int32_t n_cols, int n, const long long *begin, const long long *end) {
+        long long total = 0;
+        for (int i = 0; i < n; ++i) { lo[i] = begin[i]; hi[i] = end[i]; total += end[i] - begin[i]; }
+        auto run = [this, col, n_cols, n](int threads) {
+            for (int i = 0; i < n; ++i) {
+                if (bad.load() < 0 && hi[i] > lo[i]) {
+                    const long long at = first_bad_column(col + lo[i], hi[i] - lo[i], n_cols, threads);
+                    if (at >= 0) bad.store(lo[i] + at);
+                }
+                done.store(i + 1, std::memory_order_release);
+            }
+        };
+        if (!col || total <= 0) { done.store(n); return; }
+        if (total < (1 << 16)) { run(1); return; }
+        worker = std::thread(run, 8);  // a few threads are enough to stay ahead of the upload and leave the host's memory to the DMA
+    }
+    // waits until range i has been checked; returns the first bad position found so far, or -1
+    long long wait_range(int i) {
+        while (done.load(std::memory_order_acquire) <= i) std::this_thread::yield();
+        return bad.load();
     }
     long long finish() {
         if (worker.joinable()) worker.join();
-        return bad;
+        return bad.load();
     }
     ~ColumnScan() { finish(); }
 };
 
+// The row slabs of one host-buffer call and the order in which they are uploaded and multiplied.
+struct HostSlabs {
+    int n = 1;
+    int32_t bounds[kMaxHostSlabs + 1];
+    int order[kMaxHostSlabs];
+};
+
+static int host_slabs(int32_t n_rows, int32_t nnz, const int32_t *row_ptr, HostSlabs *hs) {
+    const long long items = (long long)n_rows + nnz;
+    int n_slabs = (int)(items / kHostSlabMinItems);
+    if (n_slabs < 1) n_slabs = 1;
+    if (n_slabs > kMaxHostSlabs) n_slabs = kMaxHostSlabs;
+    hs->n = n_slabs;
+    if (int rc = mps_slab_bounds_items(row_ptr, n_rows, n_slabs, 4, hs->bounds)) return rc;
+    // slabs with many rows first: their share of C is the largest download and should overlap the most uploads
+    for (int s = 0; s < n_slabs; ++s) hs->order[s] = s;
+    for (int i = 1; i < n_slabs; ++i)
+        for (int j = i; j > 0 && hs->bounds[hs->order[j] + 1] - hs->bounds[hs->order[j]] > hs->bounds[hs->order[j - 1] + 1] - hs->bounds[hs->order[j - 1]]; --j) {
+            const int t = hs->order[j]; hs->order[j] = hs->order[j - 1]; hs->order[j - 1] = t;
+        }
+    return MPS_OK;
+}
+
 static int host_call(int32_t n_rows, int32_t n_cols, int32_t nnz, int32_t dim, int dtype, int32_t cost, int32_t threads_per_warp,
                      const int32_t *row_ptr, const int32_t *col_idx, const void *val, const void *B, bool b_on_device, cudaStream_t b_stream,
-                     void *C, ColumnScan &scan) {
+                     void *C, const HostSlabs &hs, ColumnScan &scan) {
     int dev = 0;
     MPS_CUDA(cudaGetDevice(&dev));
     if (g_ws.device != dev) { g_ws.release(); g_ws.device = dev; }
@@ -509,12 +574,9 @@ static int host_call(int32_t n_rows, int32_t n_cols, int32_t nnz, int32_t dim, i
         }
     }
     const size_t elem = dtype == MPS_F16 ? 2 : 4;
-    const long long items = (long long)n_rows + nnz;
-    int n_slabs = (int)(items / kHostSlabMinItems);
-    if (n_slabs < 1) n_slabs = 1;
-    if (n_slabs > kMaxHostSlabs) n_slabs = kMaxHostSlabs;
-    int32_t bounds[kMaxHostSlabs + 1];
-    if (int rc = mps_slab_bounds_items(row_ptr, n_rows, n_slabs, 4, bounds)) return rc;
+    const int n_slabs = hs.n;
+    const int32_t *bounds = hs.bounds;
+    const int *order = hs.order;
 
     // device layout: slab s of col_idx/val starts at an offset that is a multiple of 8 elements, so its
     // base stays 16-byte aligned and the tile kernel can stage it with bulk copies
@@ -564,29 +626,25 @@ static int host_call(int32_t n_rows, int32_t n_cols, int32_t nnz, int32_t dim, i
     for (int s = n_slabs; s < kMaxHostSlabs; ++s) { mps_plan_destroy(g_ws.plan[s]); g_ws.plan[s] = nullptr; }
 
     MPS_CUDA(cudaStreamWaitEvent(s_work, g_ws.ev_b, 0));
-    bool scanned = false;
-    // slabs with many rows first: their share of C is the largest download and should overlap the most uploads
-    int order[kMaxHostSlabs];
-    for (int s = 0; s < n_slabs; ++s) order[s] = s;
-    for (int i = 1; i < n_slabs; ++i)
-        for (int j = i; j > 0 && bounds[order[j] + 1] - bounds[order[j]] > bounds[order[j - 1] + 1] - bounds[order[j - 1]]; --j) {
-            const int t = order[j]; order[j] = order[j - 1]; order[j - 1] = t;
-        }
+    // every upload is queued at once, in slab order, behind B on the upload stream ...
     for (int i = 0; i < n_slabs; ++i) {
         const int s = order[i];
-        const int r0 = bounds[s], rows = bounds[s + 1] - bounds[s];
+        const int r0 = bounds[s];
         const size_t k0 = (size_t)row_ptr[r0], len = (size_t)(row_ptr[bounds[s + 1]] - row_ptr[r0]);
         if (len) {
             MPS_CUDA(cudaMemcpyAsync(d_col + off[s], col_idx + k0, 4 * len, cudaMemcpyHostToDevice, s_up));
             if (val) MPS_CUDA(cudaMemcpyAsync(d_val + elem * off[s], (const char *)val + elem * k0, elem * len, cudaMemcpyHostToDevice, s_up));
         }
         MPS_CUDA(cudaEventRecord(g_ws.ev_slab[s], s_up));  // behind B on the same stream: B is whole when this fires
+    }
+    // ... and a slab's multiply is queued once the host has checked that slab's column indices (the scan runs in the
+    // same order on background threads and stays ahead of the link): no kernel gathers by an index that was not checked
+    for (int i = 0; i < n_slabs; ++i) {
+        const int s = order[i];
+        const int r0 = bounds[s], rows = bounds[s + 1] - bounds[s];
+        const long long bad = scan.wait_range(i);
+        if (bad >= 0) return fail(MPS_ERR_ARG, "mps_spmm_host: col_idx[%lld] = %d outside [0, %d)", bad, col_idx[bad], n_cols);
         MPS_CUDA(cudaStreamWaitEvent(s_work, g_ws.ev_slab[s], 0));
-        if (!scanned) {  // no kernel that gathers by col_idx is launched before every index has been checked
-            scanned = true;
-            const long long bad = scan.finish();
-            if (bad >= 0) return fail(MPS_ERR_ARG, "mps_spmm_host: col_idx[%lld] = %d outside [0, %d)", bad, col_idx[bad], n_cols);
-        }
         char *c_slab = d_C + elem * (size_t)r0 * dim;
         if (int rc = mps_spmm(g_ws.plan[s], d_rps + rps_off[s], d_col + off[s], val ? (const void *)(d_val + elem * off[s]) : nullptr,
                               d_B, c_slab, s_work))
@@ -613,9 +671,16 @@ static int host_entry(const char *who, int32_t n_rows, int32_t n_cols, int32_t n
     // the caller's arrays are checked on the host before any kernel can index by them: row_ptr here (small), col_idx
     // on background threads while the uploads start; a bad index is reported in preference to any later failure
     if (int rc = check_csr_host(who, n_rows, n_cols, row_ptr, nullptr, 0)) return rc;
+    HostSlabs hs;
+    if (int rc = host_slabs(n_rows, nnz, row_ptr, &hs)) return rc;
+    long long begin[kMaxHostSlabs], end[kMaxHostSlabs];
+    for (int i = 0; i < hs.n; ++i) {
+        begin[i] = row_ptr[hs.bounds[hs.order[i]]];
+        end[i] = row_ptr[hs.bounds[hs.order[i] + 1]];
+    }
     ColumnScan scan;
-    scan.start(col_idx, nnz, n_cols);
-    int rc = host_call(n_rows, n_cols, nnz, dim, dtype, cost, threads_per_warp, row_ptr, col_idx, val, B, b_on_device, (cudaStream_t)b_stream, C, scan);
+    scan.start(col_idx, n_cols, hs.n, begin, end);
+    int rc = host_call(n_rows, n_cols, nnz, dim, dtype, cost, threads_per_warp, row_ptr, col_idx, val, B, b_on_device, (cudaStream_t)b_stream, C, hs, scan);
     const long long bad = scan.finish();
     if (rc != MPS_OK || bad >= 0) {
         // a step failed with copies possibly still queued on the caller's buffers: let them drain before the caller

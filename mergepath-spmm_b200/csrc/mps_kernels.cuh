@@ -134,6 +134,11 @@ __device__ __forceinline__ uint64_t l2_evict_first_policy() {
     asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
     return policy;
 }
+__device__ __forceinline__ uint64_t l2_evict_last_policy() {
+    uint64_t policy;
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(policy));
+    return policy;
+}
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar, uint64_t policy) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(dst),
                  "l"(src), "r"(bytes), "r"(bar), "l"(policy)
@@ -186,6 +191,11 @@ struct Lane<float, 4> {
     static __device__ __forceinline__ scalar from_float(float v) { return v; }
     static __device__ __forceinline__ scalar one() { return 1.0f; }
     static __device__ __forceinline__ raw load(const float *p) { return __ldg(reinterpret_cast<const float4 *>(p)); }
+    static __device__ __forceinline__ raw load_hint(const float *p, uint64_t policy) {
+        float4 v;
+        asm("ld.global.nc.L2::cache_hint.v4.f32 {%0, %1, %2, %3}, [%4], %5;" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p), "l"(policy));
+        return v;
+    }
     static __device__ __forceinline__ void fma(float (&acc)[4], float a, const raw &b) {
         acc[0] = fmaf(a, b.x, acc[0]); acc[1] = fmaf(a, b.y, acc[1]);
         acc[2] = fmaf(a, b.z, acc[2]); acc[3] = fmaf(a, b.w, acc[3]);
@@ -202,6 +212,7 @@ struct Lane<float, 1> {
     static __device__ __forceinline__ scalar from_float(float v) { return v; }
     static __device__ __forceinline__ scalar one() { return 1.0f; }
     static __device__ __forceinline__ raw load(const float *p) { return __ldg(p); }
+    static __device__ __forceinline__ raw load_hint(const float *p, uint64_t) { return __ldg(p); }
     static __device__ __forceinline__ void fma(float (&acc)[1], float a, const raw &b) { acc[0] = fmaf(a, b, acc[0]); }
     static __device__ __forceinline__ void store(float *p, const float (&v)[1]) { __stcs(p, v[0]); }
 };
@@ -213,6 +224,11 @@ struct Lane<__half, 8> {
     static __device__ __forceinline__ scalar from_float(float) { return (unsigned short)0x3C00; }  // scaled products are fp32-only
     static __device__ __forceinline__ scalar one() { return (unsigned short)0x3C00; }
     static __device__ __forceinline__ raw load(const __half *p) { return __ldg(reinterpret_cast<const uint4 *>(p)); }
+    static __device__ __forceinline__ raw load_hint(const __half *p, uint64_t policy) {
+        uint4 v;
+        asm("ld.global.nc.L2::cache_hint.v4.u32 {%0, %1, %2, %3}, [%4], %5;" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p), "l"(policy));
+        return v;
+    }
     static __device__ __forceinline__ void fma(float (&acc)[8], scalar a, const raw &b) {
         fma_f32_f16x2(acc[0], acc[1], a, b.x);
         fma_f32_f16x2(acc[2], acc[3], a, b.y);
@@ -235,6 +251,7 @@ struct Lane<__half, 1> {
     static __device__ __forceinline__ scalar from_float(float v) { return v; }
     static __device__ __forceinline__ scalar one() { return 1.0f; }
     static __device__ __forceinline__ raw load(const __half *p) { return __ldg(p); }
+    static __device__ __forceinline__ raw load_hint(const __half *p, uint64_t) { return __ldg(p); }
     static __device__ __forceinline__ void fma(float (&acc)[1], float a, const raw &b) { acc[0] = fmaf(a, __half2float(b), acc[0]); }
     static __device__ __forceinline__ void store(__half *p, const float (&v)[1]) { *p = __float2half_rn(v[0]); }
 };
@@ -377,11 +394,22 @@ __device__ __forceinline__ void block_fixup(const TileParams &p, int e, int chai
 // lanes with the accumulator kept in registers across the chunk boundaries inside the unit.
 // SCALED: the value of non-zero (i, j) is row_scale[i] * col_scale[j] instead of a stored value (a kernel of
 // its own so that the plain product carries none of its selects).
-template <typename T, int VEC, int GL, int U, int BLOCK, bool SCALED>
+// HOT: bit 31 of a staged column index marks a column whose row of B should stay in the L2 (set by
+// mps_plan_mark_hot_columns in the plan's own copy of col_idx); such rows are gathered with an evict-last policy,
+// all others with evict-first, so that the rows with the most reuse are the ones the L2 keeps.
+// SPREAD: a unit is walked by a whole warp instead of one lane group.  The warp's 32/GL lane groups take consecutive
+// non-zeros of the unit (group s the non-zeros at offset s, s + 32/GL, .. from the unit's start), each keeping a partial
+// sum of the row in progress; at every row end the partial sums are combined with xor-shuffles in a fixed tree and the
+// first group stores the row.  All lanes of a warp then follow the same rows, so none is masked off where the units of
+// neighbouring groups would end their rows at different places - which is what costs at small dim, where a warp holds
+// eight groups.
+template <typename T, int VEC, int GL, int U, int BLOCK, bool SCALED, bool HOT = false, bool SPREAD = false>
 __global__ void __launch_bounds__(BLOCK, kWarpsPerSm * 32 / BLOCK) spmm_tile_kernel(const TileParams p) {
     constexpr int kBlock = BLOCK;
-    constexpr int GPC = kBlock / GL;   // units (lane groups) per block
-    constexpr int SLAB = GL * VEC;     // columns covered by one block
+    constexpr int UL = SPREAD ? 32 : GL;   // lanes that walk one unit
+    constexpr int G = UL / GL;             // lane groups per unit (1 unless SPREAD)
+    constexpr int GPC = kBlock / UL;       // units per block
+    constexpr int SLAB = GL * VEC;         // columns covered by one block
     extern __shared__ __align__(128) unsigned char smem[];
     const TileSmem L(GPC, p.tile_items, SLAB, (int)sizeof(T));
     uint64_t *s_bar = reinterpret_cast<uint64_t *>(smem);
@@ -394,7 +422,8 @@ __global__ void __launch_bounds__(BLOCK, kWarpsPerSm * 32 / BLOCK) spmm_tile_ker
     float *s_head = reinterpret_cast<float *>(smem + L.off_head);
 
     const int tid = threadIdx.x;
-    const int g = tid / GL, l = tid % GL;
+    const int g = tid / UL, l = tid % GL;   // unit of this thread, lane inside its group
+    [[maybe_unused]] const int sg = (tid % UL) / GL;  // group inside the unit (SPREAD), else 0
     const int t = blockIdx.x;
     const int coff = blockIdx.y * SLAB + l * VEC;  // first column of this lane
     const bool active = coff < p.dim;
@@ -403,6 +432,27 @@ __global__ void __launch_bounds__(BLOCK, kWarpsPerSm * 32 / BLOCK) spmm_tile_ker
     const T *__restrict__ Bl = static_cast<const T *>(p.B) + coff;  // this lane's columns of B
     T *__restrict__ Cl = static_cast<T *>(p.C) + coff;
     const unsigned dim = (unsigned)p.dim;
+    [[maybe_unused]] uint64_t keep = 0, pass = 0;
+    if constexpr (HOT) {
+        keep = l2_evict_last_policy(); pass = l2_evict_first_policy();
+#if defined(MPS_AB_COLD) && MPS_AB_COLD == 1
+        asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(pass));
+#elif defined(MPS_AB_COLD) && MPS_AB_COLD == 2
+        asm volatile("createpolicy.fractional.L2::evict_unchanged.b64 %0, 1.0;" : "=l"(pass));
+#endif
+#if defined(MPS_AB_HOT_NORMAL)
+        asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(keep));
+#endif
+    }
+    // one gathered row of B (this lane's columns); HOT strips the mark and picks the policy
+    auto gather = [&](unsigned ci) -> typename Lane<T, VEC>::raw {
+        if constexpr (HOT) {
+            const uint64_t pol = (ci >> 31) ? keep : pass;
+            return Lane<T, VEC>::load_hint(Bl + (size_t)(ci & 0x7fffffffu) * dim, pol);
+        } else {
+            return Lane<T, VEC>::load(Bl + (size_t)ci * dim);
+        }
+    };
 
     const int2 c0 = __ldg(p.tile_xy + t), c1 = __ldg(p.tile_xy + t + 1);
     const int X0 = c0.x, Y0 = c0.y, X1 = c1.x, Y1 = c1.y;
@@ -478,7 +528,7 @@ __global__ void __launch_bounds__(BLOCK, kWarpsPerSm * 32 / BLOCK) spmm_tile_ker
     __syncthreads();
 
     // ---- walk this group's unit ----
-    {
+    if constexpr (!SPREAD) {
         const int x0 = s_fx[g], y0 = s_fy[g], x1 = s_fx[g + 1], y1 = s_fy[g + 1];
         bool head_pending = x0 >= 1 && y0 > w_rp[x0 - 1];  // first row began before this unit
         int x = x0;
@@ -518,7 +568,7 @@ __global__ void __launch_bounds__(BLOCK, kWarpsPerSm * 32 / BLOCK) spmm_tile_ker
                 const unsigned ci = (unsigned)w_col[k + u];
                 if constexpr (SCALED) a[u] = cs ? Lane<T, VEC>::from_float(__ldg(cs + ci)) : Lane<T, VEC>::one();
                 else a[u] = has_val ? Lane<T, VEC>::value(w_val[k + u]) : Lane<T, VEC>::one();
-                if (active) b[u] = Lane<T, VEC>::load(Bl + (size_t)ci * dim);
+                if (active) b[u] = gather(ci);
             }
             while (next_mark <= k) end_row();
             if (next_mark >= k + U) {  // no row ends inside the batch
@@ -544,7 +594,7 @@ __global__ void __launch_bounds__(BLOCK, kWarpsPerSm * 32 / BLOCK) spmm_tile_ker
                     const unsigned ci = (unsigned)w_col[k + u];
                     if constexpr (SCALED) a[u] = cs ? Lane<T, VEC>::from_float(__ldg(cs + ci)) : Lane<T, VEC>::one();
                 else a[u] = has_val ? Lane<T, VEC>::value(w_val[k + u]) : Lane<T, VEC>::one();
-                    if (active) b[u] = Lane<T, VEC>::load(Bl + (size_t)ci * dim);
+                    if (active) b[u] = gather(ci);
                 }
             }
 #pragma unroll
@@ -557,13 +607,103 @@ __global__ void __launch_bounds__(BLOCK, kWarpsPerSm * 32 / BLOCK) spmm_tile_ker
         }
         while (x < x1) end_row();
         smem_put<VEC>(s_carry + g * SLAB + l * VEC, acc);
+    } else {
+        // ---- the warp walks its unit: group sg takes the non-zeros y0 + sg, y0 + sg + G, .. ----
+        const int x0 = s_fx[g], y0 = s_fy[g], x1 = s_fx[g + 1], y1 = s_fy[g + 1];
+        bool head_pending = x0 >= 1 && y0 > w_rp[x0 - 1];
+        int x = x0;
+        int next_mark = x < x1 ? w_rp[x] : 0x7fffffff;
+        float acc[VEC];
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) acc[i] = 0.0f;
+        // partial sums of the groups -> every lane holds the row: level by level, partner group sg ^ 1, ^ 2, ^ 4
+        auto combine = [&]() {
+#pragma unroll
+            for (int off = GL; off < 32; off <<= 1) {
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], off);
+            }
+        };
+        auto end_row = [&]() {  // warp-uniform: every lane of the warp sees the same x and next_mark
+            if (x >= 1) {
+                combine();
+                if (head_pending) {
+                    if (sg == 0) smem_put<VEC>(s_head + g * SLAB + l * VEC, acc);
+                    head_pending = false;
+                } else if (active && sg == 0) {
+                    Lane<T, VEC>::store(Cl + (size_t)(x - 1) * dim, acc);
+                }
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) acc[i] = 0.0f;
+            }
+            ++x;
+            next_mark = x < x1 ? w_rp[x] : 0x7fffffff;
+        };
+        // one slice = the G consecutive non-zeros [base, base + G), one per group; `mine` says whether this group's
+        // non-zero exists (remainder) - its operands a, b are already in registers
+        auto fold_slice = [&](int base, bool mine, typename Lane<T, VEC>::scalar a, const typename Lane<T, VEC>::raw &b) {
+            while (next_mark <= base) end_row();
+            const int j = base + sg;
+            if (next_mark >= base + G) {  // no row ends inside the slice
+                if (active && mine) Lane<T, VEC>::fma(acc, a, b);
+            } else {
+                int lo = base;
+                while (next_mark < base + G) {  // rows that end inside the slice, one after the other
+                    if (active && mine && j >= lo && j < next_mark) Lane<T, VEC>::fma(acc, a, b);
+                    lo = next_mark;
+                    end_row();
+                }
+                if (active && mine && j >= lo) Lane<T, VEC>::fma(acc, a, b);
+            }
+        };
+        constexpr int NB = G * U;  // non-zeros per batch of the warp
+        int k = y0;
+        for (; k + NB <= y1; k += NB) {
+            typename Lane<T, VEC>::raw b[U];
+            typename Lane<T, VEC>::scalar a[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int j = k + u * G + sg;
+                const unsigned ci = (unsigned)w_col[j];
+                a[u] = has_val ? Lane<T, VEC>::value(w_val[j]) : Lane<T, VEC>::one();
+                if (active) b[u] = gather(ci);
+            }
+            if (next_mark >= k + NB) {  // no row ends inside the batch
+                if (active) {
+#pragma unroll
+                    for (int u = 0; u < U; ++u) Lane<T, VEC>::fma(acc, a[u], b[u]);
+                }
+            } else {
+#pragma unroll
+                for (int u = 0; u < U; ++u) fold_slice(k + u * G, true, a[u], b[u]);
+            }
+        }
+        if (k < y1) {  // remainder: fewer than NB non-zeros
+            typename Lane<T, VEC>::raw b[U];
+            typename Lane<T, VEC>::scalar a[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int j = k + u * G + sg;
+                if (j < y1) {
+                    const unsigned ci = (unsigned)w_col[j];
+                    a[u] = has_val ? Lane<T, VEC>::value(w_val[j]) : Lane<T, VEC>::one();
+                    if (active) b[u] = gather(ci);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u)
+                if (k + u * G < y1) fold_slice(k + u * G, k + u * G + sg < y1, a[u], b[u]);
+        }
+        while (x < x1) end_row();
+        combine();
+        if (sg == 0) smem_put<VEC>(s_carry + g * SLAB + l * VEC, acc);
     }
     __syncthreads();
 
     // ---- in-tile fix-up: the group finishes the row its unit ended first, if it began earlier ----
     {
         const int x0 = s_fx[g], x1 = s_fx[g + 1], y0 = s_fy[g];
-        if (x0 >= 1 && x1 > x0 && y0 > w_rp[x0 - 1]) {
+        if (sg == 0 && x0 >= 1 && x1 > x0 && y0 > w_rp[x0 - 1]) {
             int s = g;
             while (s > 0 && s_fx[s] == x0) --s;
             const bool from_prev = s_fx[0] == x0 && Y0 > w_rp[X0 - 1];  // row began before this tile
@@ -582,7 +722,7 @@ __global__ void __launch_bounds__(BLOCK, kWarpsPerSm * 32 / BLOCK) spmm_tile_ker
         }
     }
     // ---- tile carry: everything after the last marker of the tile ----
-    if (g == GPC - 1) {
+    if (g == GPC - 1 && sg == 0) {
         const int xe = s_fx[GPC];
         int s = GPC;
         while (s > 0 && s_fx[s] == xe) --s;

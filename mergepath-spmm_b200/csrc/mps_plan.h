@@ -16,13 +16,16 @@ struct mps_plan {
     int bulk;
     int long_chain, very_long, n_long, long_capacity;  // chain lengths (tiles): strand order above long_chain, own kernel above very_long
     int device, sm_count;
-    bool user_cpu, user_unroll, user_block, user_fused;
+    bool user_cpu, user_unroll, user_block, user_fused, user_walk;
+    int walk;  // 0: one lane group walks a unit; 1: a whole warp walks a unit, its groups combined with shuffles at row ends
     int fused;  // cross-tile fix-up inside the tile kernel (small problems) or as a kernel of its own
     bool partitioned;
     int2 *d_tile_xy;
     float *d_tcarry, *d_thead;
     int *d_status, *d_long_list, *d_long_count;
     int *d_consumer, *d_need, *d_cnt;  // per tile: who ends my carry's row, contributions awaited, arrivals (x column slabs)
+    int *d_col_hot;    // the plan's own copy of col_idx with bit 31 set on hot columns (mps_plan_mark_hot_columns), or nullptr
+    long long hot_columns, hot_nnz;
     bool profiling;
     int prof_used;
     cudaEvent_t prof_ev[2 * kProfSlots];

@@ -325,13 +325,24 @@ static inline void model_store(const model_io *io, int row, const float *v_in) {
     else memcpy((float *)io->C + at, v, sizeof(float) * io->dim);
 }
 
+/* acc <- part[0..groups) added pairwise, level by level (distance 1, 2, 4, ..) */
+#define MODEL_TREE(dst)                                                                                  \
+    do {                                                                                                 \
+        memcpy(tree, part, sizeof(float) * (size_t)groups * dim);                                        \
+        for (int off_ = 1; off_ < groups; off_ <<= 1)                                                    \
+            for (int s_ = 0; s_ < groups; s_ += 2 * off_)                                                \
+                for (int j_ = 0; j_ < dim; ++j_) tree[(size_t)s_ * dim + j_] += tree[(size_t)(s_ + off_) * dim + j_]; \
+        memcpy(dst, tree, sizeof(float) * dim);                                                          \
+    } while (0)
+
 /* unit_items: merge items per unit; nu: units per tile.  The tiles are independent until the cross-tile fix-up,
  * so they are walked by all host threads (every thread owns its scratch; each row of C, each tcarry / thead row is
  * written by exactly one tile), which lets the model check a full-size product in seconds. */
 static int tile_model_items(const int *row_ptr, const int *col, const void *val, const float *row_scale, const float *col_scale,
                             const void *B, void *C, int n_rows, int nnz, int dim, int is_half, int64_t unit_items, int nu,
-                            int long_chain) {
+                            int long_chain, int groups) {
     if (unit_items < 1 || nu < 1 || dim < 1 || dim > 1024) return -1;
+    if (!(groups == 1 || groups == 2 || groups == 4 || groups == 8 || groups == 16)) return -1;
     model_io io = {row_ptr, col, val, B, C, dim, is_half, row_scale, col_scale};
     const int64_t total = (int64_t)n_rows + 1 + nnz;
     const int64_t tile_items = unit_items * nu;
@@ -355,6 +366,7 @@ static int tile_model_items(const int *row_ptr, const int *col, const void *val,
         float *head = malloc(sizeof(float) * (size_t)nu * dim);
         char *has_head = malloc(nu);
         float *acc = malloc(sizeof(float) * dim), *sum = malloc(sizeof(float) * dim);
+        float *part = malloc(sizeof(float) * (size_t)groups * dim), *tree = malloc(sizeof(float) * (size_t)groups * dim);
 #pragma omp for schedule(dynamic, 64)
         for (int t = 0; t < T; ++t) {
             for (int u = 0; u <= nu; ++u)
@@ -364,29 +376,36 @@ static int tile_model_items(const int *row_ptr, const int *col, const void *val,
                 const int cont = x0 >= 1 && y0 > row_ptr[x0 - 1];
                 int x = x0, first = 1;
                 has_head[u] = 0;
-                for (int j = 0; j < dim; ++j) acc[j] = 0.0f;
+                /* `groups` lane groups share the unit: group s folds the non-zeros y0 + s, y0 + s + groups, .. of the
+                 * row in progress into part[s]; at a row end the partial sums are added in a fixed tree (neighbours
+                 * first: s with s ^ 1, then ^ 2, ..), which is what the kernel's xor-shuffles compute.  groups == 1 is
+                 * the plain walk: one running sum. */
+                for (int j = 0; j < groups * dim; ++j) part[j] = 0.0f;
                 for (int k = y0; k <= y1; ++k) {
                     /* consume every marker that precedes non-zero k (all that are left when k == y1) */
                     while (x < x1 && (k == y1 || row_ptr[x] <= k)) {
                         if (x >= 1) {
+                            MODEL_TREE(acc);
                             if (first && cont) { memcpy(head + (size_t)u * dim, acc, sizeof(float) * dim); has_head[u] = 1; }
                             else model_store(&io, x - 1, acc);
                             first = 0;
-                            for (int j = 0; j < dim; ++j) acc[j] = 0.0f;
+                            for (int j = 0; j < groups * dim; ++j) part[j] = 0.0f;
                         }
                         ++x;
                     }
                     if (k == y1) break;
                     const float a = model_val(&io, k);
                     const int cc = col[k];
+                    float *restrict pacc = part + (size_t)((k - y0) % groups) * dim;
                     if (!is_half) { /* same fused multiply-adds, read straight from the fp32 row */
                         const float *restrict b = (const float *)B + (size_t)cc * dim;
 #pragma omp simd
-                        for (int j = 0; j < dim; ++j) acc[j] = fmaf(a, b[j], acc[j]);
+                        for (int j = 0; j < dim; ++j) pacc[j] = fmaf(a, b[j], pacc[j]);
                     } else {
-                        for (int j = 0; j < dim; ++j) acc[j] = fmaf(a, model_b(&io, cc, j), acc[j]);
+                        for (int j = 0; j < dim; ++j) pacc[j] = fmaf(a, model_b(&io, cc, j), pacc[j]);
                     }
                 }
+                MODEL_TREE(acc);
                 memcpy(carry + (size_t)u * dim, acc, sizeof(float) * dim);
             }
             /* in-tile fix-up */
@@ -409,7 +428,7 @@ static int tile_model_items(const int *row_ptr, const int *col, const void *val,
                 memcpy(tcarry + (size_t)t * dim, sum, sizeof(float) * dim);
             }
         }
-        free(fx); free(fy); free(carry); free(head); free(has_head); free(acc); free(sum);
+        free(fx); free(fy); free(carry); free(head); free(has_head); free(acc); free(sum); free(part); free(tree);
     }
     /* cross-tile fix-up */
 #pragma omp parallel
@@ -446,18 +465,18 @@ static int tile_model_items(const int *row_ptr, const int *col, const void *val,
  * unit_items > 0 overrides cpu * ipt (sub-chunk units: a unit is a part of one chunk). */
 static int tile_model_impl(const int *row_ptr, const int *col, const void *val, const float *row_scale, const float *col_scale,
                            const void *B, void *C, int n_rows, int nnz, int dim, int is_half, int cost, int nch, int cpu,
-                           int long_chain, int64_t unit_items) {
+                           int long_chain, int64_t unit_items, int groups) {
     if (cost < 1 || nch < 1 || cpu < 1 || nch % cpu != 0) return -1;
     const int P = orc_chunk_count(n_rows, nnz, cost);
     const int64_t ipt = orc_items_per_chunk(n_rows, nnz, P);
     if (unit_items <= 0) unit_items = ipt * cpu;
-    return tile_model_items(row_ptr, col, val, row_scale, col_scale, B, C, n_rows, nnz, dim, is_half, unit_items, nch / cpu, long_chain);
+    return tile_model_items(row_ptr, col, val, row_scale, col_scale, B, C, n_rows, nnz, dim, is_half, unit_items, nch / cpu, long_chain, groups);
 }
 
 ORC_API int orc_tile_model(const int *row_ptr, const int *col, const void *val, const void *B,
                            void *C, int n_rows, int nnz, int dim, int is_half, int cost,
-                           int nch, int cpu, int long_chain, int64_t unit_items) {
-    return tile_model_impl(row_ptr, col, val, NULL, NULL, B, C, n_rows, nnz, dim, is_half, cost, nch, cpu, long_chain, unit_items);
+                           int nch, int cpu, int long_chain, int64_t unit_items, int groups) {
+    return tile_model_impl(row_ptr, col, val, NULL, NULL, B, C, n_rows, nnz, dim, is_half, cost, nch, cpu, long_chain, unit_items, groups);
 }
 
 /* The scaled variant (fp32): value(i,j) = row_scale[i] * col_scale[j]; the column factor enters each fused
@@ -466,7 +485,7 @@ ORC_API int orc_tile_model(const int *row_ptr, const int *col, const void *val, 
 ORC_API int orc_tile_model_scaled(const int *row_ptr, const int *col, const float *row_scale, const float *col_scale,
                                   const float *B, float *C, int n_rows, int nnz, int dim, int cost, int nch, int cpu,
                                   int long_chain, int64_t unit_items) {
-    return tile_model_impl(row_ptr, col, NULL, row_scale, col_scale, B, C, n_rows, nnz, dim, 0, cost, nch, cpu, long_chain, unit_items);
+    return tile_model_impl(row_ptr, col, NULL, row_scale, col_scale, B, C, n_rows, nnz, dim, 0, cost, nch, cpu, long_chain, unit_items, 1);
 }
 
 /* Nnz-balanced row slabs for G devices: bounds[g] = first row whose start

@@ -59,7 +59,7 @@ def lib():
         L.orc_spmm_f32_omp.restype = C.c_int
         L.orc_spmm_f32_omp.argtypes = [_i32p, _i32p, vp, vp, vp, C.c_int, C.c_int, C.c_int]
         L.orc_tile_model.restype = C.c_int
-        L.orc_tile_model.argtypes = [_i32p, _i32p, vp, vp, vp] + [C.c_int] * 8 + [C.c_int64]
+        L.orc_tile_model.argtypes = [_i32p, _i32p, vp, vp, vp] + [C.c_int] * 8 + [C.c_int64, C.c_int]
         L.orc_tile_model_scaled.restype = C.c_int
         L.orc_tile_model_scaled.argtypes = [_i32p, _i32p, vp, vp, vp, vp] + [C.c_int] * 7 + [C.c_int64]
         L.orc_slab_bounds.restype = None
@@ -154,15 +154,16 @@ def spmm_f32_omp(row_ptr, col, val, B, out=None, threads: int = 0):
     return out, used
 
 
-def tile_model(row_ptr, col, val, B, cost: int, nch: int, cpu: int, long_chain: int, is_half: bool = False, unit_items: int = 0) -> np.ndarray:
+def tile_model(row_ptr, col, val, B, cost: int, nch: int, cpu: int, long_chain: int, is_half: bool = False, unit_items: int = 0, groups: int = 1) -> np.ndarray:
     """nch = chunks per tile, cpu = chunks per unit (nch % cpu == 0); a unit holds cpu * items_per_chunk(cost) merge
-    items unless unit_items > 0 names another count (sub-chunk units).  A tile is nch // cpu units."""
+    items unless unit_items > 0 names another count (sub-chunk units).  A tile is nch // cpu units.  groups > 1: that
+    many lane groups share a unit (a warp walks it) and their partial sums are added in a fixed tree at row ends."""
     rp, ci = _i32(row_ptr), _i32(col)
     v, Bm = _store(val, is_half), _store(B, is_half)
     n, dim = len(rp) - 1, Bm.shape[1]
     out = np.zeros((n, dim), np.float16 if is_half else np.float32)
     rc = lib().orc_tile_model(rp, ci, _ptr(v), _ptr(Bm), _ptr(out), n, int(rp[-1]), dim, int(is_half),
-                              cost, nch, cpu, long_chain, unit_items)
+                              cost, nch, cpu, long_chain, unit_items, groups)
     if rc != 0:
         raise ValueError("orc_tile_model: bad arguments")
     return out

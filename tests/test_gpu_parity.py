@@ -29,12 +29,14 @@ def _bits(a):
     return a.view(np.uint16 if a.dtype == np.float16 else np.uint32)
 
 
-def _run(mps, cuda, rp, col, val, B, cost, tune=None, tpw=1):
+def _run(mps, cuda, rp, col, val, B, cost, tune=None, tpw=1, walk=None):
     n, nnz, dim = len(rp) - 1, len(col), B.shape[1]
     half = B.dtype == np.float16
     plan = mps.Plan(n, nnz, dim, mps.F16 if half else mps.F32, cost, tpw, device=cuda)
     if tune:
         plan.tune(**tune)
+    if walk is not None:
+        plan.set_walk(walk)
     d_rp, d_col, d_val, d_B = _dev(rp, cuda), _dev(col, cuda), _dev(val, cuda), _dev(B, cuda)
     plan.partition(d_rp)
     out = torch.full((n, dim), float("nan"), dtype=d_B.dtype, device=cuda)  # every element must be overwritten
@@ -47,7 +49,8 @@ def _run(mps, cuda, rp, col, val, B, cost, tune=None, tpw=1):
 
 def _check(orc, rp, col, val, B, got, info, cost, tol):
     half = B.dtype == np.float16
-    model = orc.tile_model(rp, col, val, B, cost, info["chunks_per_tile"], info["chunks_per_unit"], info["long_chain"], is_half=half, unit_items=info["unit_items"])
+    model = orc.tile_model(rp, col, val, B, cost, info["chunks_per_tile"], info["chunks_per_unit"], info["long_chain"], is_half=half, unit_items=info["unit_items"],
+                           groups=info["groups_per_unit"])
     assert not np.isnan(got.astype(np.float32)).any(), "some element of C was never written"
     same = _bits(got) == _bits(model)
     assert same.all(), f"{(~same).sum()} elements differ from the CPU model (first at {np.argwhere(~same)[0]})"
@@ -479,6 +482,72 @@ def test_host_call_with_b_already_on_the_device(mps, graphs, cuda):
         assert np.array_equal(_bits(out.numpy()), _bits(want))
         out.fill_(float("nan"))
     mps.capi.lib().mps_host_workspace_release()
+
+
+@pytest.mark.parametrize("dim,half", [(16, False), (32, False), (64, False), (8, False), (12, False), (24, False), (32, True), (64, True), (128, True), (16, True)])
+def test_warp_per_unit_walk_is_bit_exact_with_its_model(mps, orc, graphs, cuda, dim, half):
+    """mps_plan_set_walk(1): a warp walks one unit, its 32/lanes groups take consecutive non-zeros and their partial sums
+    are combined with shuffles in a fixed tree at row ends.  Power-law graph (fused and unfused fix-up), the structured
+    graph of short rows, and every edge-case shape."""
+    def operands(n_cols, seed):
+        if half:
+            return graphs.dense_normal_f16(n_cols, dim, seed=seed)
+        return graphs.dense_uniform(n_cols, dim, seed=seed)
+    for rp, col in (cases.c1_rmat(), cases.c2_batched(400)):
+        val = graphs.gcn_values(rp, col, "f16" if half else "f32")
+        B = operands(len(rp) - 1, 1)
+        for tune in (None, dict(fused_fixup=0), dict(chunks_per_unit=3)):
+            got, info = _run(mps, cuda, rp, col, val, B, 8, tune, walk=1)
+            assert info["groups_per_unit"] == 32 // info["lanes_per_chunk"] > 1 and info["units_per_tile"] == 2
+            _check(orc, rp, col, val, B, got, info, 8, 1e-2 if half else 1e-5)
+    rng = np.random.default_rng(3)
+    for name, (rp, col) in sorted(cases.edge_cases().items()):
+        n_cols = max(int(col.max()) + 1 if len(col) else 1, len(rp) - 1)
+        val = rng.uniform(-1, 1, len(col)).astype(np.float16 if half else np.float32)
+        B = operands(n_cols, 2)
+        for cost in (1, 8):
+            got, info = _run(mps, cuda, rp, col, val, B, cost, walk=1)
+            _check(orc, rp, col, val, B, got, info, cost, 1e-2 if half else 1e-5)
+
+
+def test_warp_per_unit_walk_on_a_mid_size_graph_and_where_it_does_not_apply(mps, orc, graphs, cuda):
+    rp, col = graphs.rmat_csr(17, 32, seed=9)
+    val = graphs.gcn_values(rp, col)
+    B = graphs.dense_uniform(len(rp) - 1, 16, seed=6)
+    got, info = _run(mps, cuda, rp, col, val, B, 16, walk=1)
+    assert info["groups_per_unit"] == 8 and info["fused_fixup"] == 0
+    _check(orc, rp, col, val, B, got, info, 16, 1e-5)
+    # 32 lanes per row, generic dims and other block sizes keep the lane-group walk whatever is asked
+    for dim, tune in ((128, None), (20, None), (16, dict(block_threads=128))):
+        Bx = graphs.dense_uniform(len(rp) - 1, dim, seed=6)
+        got, info = _run(mps, cuda, rp, col, val, Bx, 16, tune, walk=1)
+        assert info["groups_per_unit"] == (1 if dim != 20 else info["groups_per_unit"])
+        _check(orc, rp, col, val, Bx, got, info, 16, 1e-5)
+
+
+def test_hot_column_marking_changes_cache_policy_not_results(mps, graphs, cuda):
+    """mps_plan_mark_hot_columns: the most frequent columns' rows of B are gathered with an L2 evict-last policy, the
+    others with evict-first; the plan reads its own marked copy of col_idx.  Same bits as without marking."""
+    rp, col = graphs.rmat_csr(16, 32, seed=5)
+    val = graphs.gcn_values(rp, col)
+    n, nnz = len(rp) - 1, len(col)
+    d_rp, d_col, d_val = _dev(rp, cuda), _dev(col, cuda), _dev(val, cuda)
+    for dim, half in ((64, False), (16, False), (128, True)):
+        B = graphs.dense_normal_f16(n, dim, seed=6) if half else graphs.dense_uniform(n, dim, seed=6)
+        v = d_val.to(torch.float16) if half else d_val
+        d_B = _dev(B, cuda)
+        plan = mps.Plan(n, nnz, dim, mps.F16 if half else mps.F32, 16, device=cuda)
+        plan.partition(d_rp)
+        plain = plan.spmm(d_rp, d_col, v, d_B).clone()
+        cols, hits = plan.mark_hot_columns(d_col, n, 2 << 20)           # 2 MB of rows
+        assert 0 < cols <= (2 << 20) // (dim * B.itemsize) and hits > cols
+        marked = plan.spmm(d_rp, d_col, v, d_B)
+        plan.sync_check()
+        assert torch.equal(plain, marked)
+        assert plan.mark_hot_columns(d_col, n, 0) == (0, 0)             # switched off again
+        assert torch.equal(plain, plan.spmm(d_rp, d_col, v, d_B))
+        plan.sync_check()
+        plan.close()
 
 
 def test_gather_probe_reports_a_plausible_rate(mps, cuda):
