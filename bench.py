@@ -68,7 +68,6 @@ def parse_args():
     ap.add_argument("--c5-degree", type=int, default=64)
     ap.add_argument("--c5-dim", type=int, default=32)
     ap.add_argument("--c5-steps", type=int, default=20)
-    ap.add_argument("--hot-mb", type=float, default=-1.0, help="MB of B rows marked to stay in the L2 (mps_plan_mark_hot_columns); 0 = off, -1 = automatic")
     ap.add_argument("--slab", default="", help="R/N: on one GPU, the workload of rank R of an N-GPU run (graph of 2^scale * N nodes, slab R of N) - for profiling")
     ap.add_argument("--no-probe", action="store_true", help="leave out the gather-rate probe (roofline.l2_peak_gbs)")
     return ap.parse_args()

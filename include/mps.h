@@ -193,18 +193,6 @@ MPS_API int mps_spmm(mps_plan *plan, const int32_t *d_row_ptr, const int32_t *d_
 MPS_API int mps_spmm_scaled(mps_plan *plan, const int32_t *d_row_ptr, const int32_t *d_col_idx,
                     const float *d_row_scale, const float *d_col_scale, const void *d_B, void *d_C, void *stream);
 
-/* Optional, after mps_plan_create (no reference counterpart): tells the multiply which rows of B the L2 should keep.
- * Counts the occurrences of every column in d_col_idx (the col_idx that mps_spmm will be given; n_cols = rows of B),
- * marks the most frequent columns until their rows of B fill `budget_bytes` (something like half of the 126 MB L2), and
- * keeps a marked copy of col_idx inside the plan (4 bytes per non-zero).  From then on mps_spmm on this plan gathers
- * marked rows with an L2 evict-last policy and the others with evict-first, and reads the plan's copy instead of the
- * caller's col_idx - so call this again if the indices change.  Pays when B is many times the L2 (a rank of a
- * multi-GPU job keeps all of B); budget_bytes <= 0 removes the marking.  Results are bit-identical either way.
- * *hot_columns / *hot_nnz (may be NULL): how many columns were marked and how many non-zeros refer to them.
- * Allocates, synchronises the stream. */
-MPS_API int mps_plan_mark_hot_columns(mps_plan *plan, const int32_t *d_col_idx, int32_t n_cols, int64_t budget_bytes,
-                              void *stream, int64_t *hot_columns, int64_t *hot_nnz);
-
 /* Waits for the stream and returns MPS_ERR_DEVICE if any kernel of this plan gave up a wait (a tile block whose
  * staged window did not arrive in time fetches it again with plain loads and finishes its rows, but the call
  * counts as failed: treat C as undefined until this returns MPS_OK). */
@@ -271,9 +259,11 @@ MPS_API int mps_gather_probe(const void *d_table, int64_t table_rows, int32_t ro
  * reallocate.  Blocking.
  * The caller's arrays are validated on host threads before any kernel indexes by them (the reference
  * checks nothing, its helper :41-52 is never called): row_ptr[0] == 0, row_ptr non-decreasing,
- * row_ptr[n_rows] == nnz, every col_idx inside [0, n_cols) - else MPS_ERR_ARG naming the position.  The
- * scan of col_idx runs beside the upload of B, and a bad index is reported in preference to any other
- * failure of the call (also on a machine without a device). */
+ * row_ptr[n_rows] == nnz, every col_idx inside [0, n_cols) - else MPS_ERR_ARG naming the position.  row_ptr
+ * is checked on the host; col_idx where each slab of it lands on the device, ahead of the multiply on the
+ * same stream (an index outside B is replaced by 0 in the workspace copy before any kernel gathers by it,
+ * and C is then meaningless), so the check costs the uploads nothing.  A bad index is reported in preference
+ * to any other failure of the call, also on a machine without a device (there the host scans col_idx). */
 MPS_API int mps_spmm_host(int32_t n_rows, int32_t n_cols, int32_t nnz, int32_t dim, int dtype, int32_t cost,
                   int32_t threads_per_warp, const int32_t *row_ptr, const int32_t *col_idx,
                   const void *val, const void *B, void *C);

@@ -140,14 +140,6 @@ class Plan:
                                                   _dev_ptr(B), _dev_ptr(out), _stream_ptr(stream)))
         return out
 
-    def mark_hot_columns(self, col_idx, n_cols: int, budget_bytes: int, stream=None) -> tuple[int, int]:
-        """Rows of B that the L2 should keep (mps_plan_mark_hot_columns); returns (columns marked, non-zeros that hit them)."""
-        _need_cuda(col_idx)
-        a, b = C.c_int64(), C.c_int64()
-        with torch.cuda.device(self.device):
-            capi.check(capi.lib().mps_plan_mark_hot_columns(self._h, _dev_ptr(col_idx), n_cols, budget_bytes, _stream_ptr(stream), C.byref(a), C.byref(b)))
-        return a.value, b.value
-
     def sync_check(self, stream=None):
         with torch.cuda.device(self.device):
             capi.check(capi.lib().mps_plan_sync_check(self._h, _stream_ptr(stream)))

@@ -37,7 +37,7 @@ def _sources(names):
 def build_library(force: bool = False, verbose: bool = False) -> str:
     """Compiles every source to an object (in parallel) and links libmps_b200.so."""
     from concurrent.futures import ThreadPoolExecutor
-    srcs = _sources(["mps_api.cu", "mps_spmm_f32.cu", "mps_spmm_f32_scaled.cu", "mps_spmm_f16.cu", "mps_noalloc.cu", "mps_multi.cu", "mps_probe.cu", "mps_hot.cu", "convert_device.cu", "csr_io.cpp", "convert.cpp", "host_check.cpp", "partition_host.cpp"])
+    srcs = _sources(["mps_api.cu", "mps_spmm_f32.cu", "mps_spmm_f32_scaled.cu", "mps_spmm_f16.cu", "mps_noalloc.cu", "mps_multi.cu", "mps_probe.cu", "convert_device.cu", "csr_io.cpp", "convert.cpp", "host_check.cpp", "partition_host.cpp"])
     deps = srcs + _sources(["mps_kernels.cuh", "mps_dispatch.cuh", "mps_internal.h", "mps_plan.h"]) + [os.path.join(ROOT, "include", "mps.h")]
     if not force and _newer(LIB, deps):
         return LIB

@@ -17,7 +17,7 @@ F32, F16 = 0, 1
 SYMBOLS = [
     "mps_last_error", "mps_version", "mps_csr_load", "mps_csr_load_rect", "mps_csr_free", "mps_csr_save", "mps_csr_save_bin",
     "mps_csr_load_bin", "mps_coo_to_csr", "mps_coo_to_csr_device", "mps_csr_transpose_device", "mps_npz_to_csr", "mps_chunk_count", "mps_partition_device", "mps_schedule_device", "mps_plan_create",
-    "mps_plan_destroy", "mps_plan_tune", "mps_plan_partition", "mps_spmm", "mps_spmm_scaled", "mps_plan_mark_hot_columns", "mps_plan_sync_check", "mps_plan_info", "mps_plan_set_walk", "mps_plan_layout", "mps_layout_query", "mps_plan_profile", "mps_plan_profile_read",
+    "mps_plan_destroy", "mps_plan_tune", "mps_plan_partition", "mps_spmm", "mps_spmm_scaled", "mps_plan_sync_check", "mps_plan_info", "mps_plan_set_walk", "mps_plan_layout", "mps_layout_query", "mps_plan_profile", "mps_plan_profile_read",
     "mps_algorithmic_bytes", "mps_gather_probe", "mps_spmm_host", "mps_spmm_host_resident_b", "mps_partition_host", "mps_schedule_host", "mps_host_workspace_release", "mps_spmm_noalloc", "mps_slab_bounds", "mps_slab_bounds_items", "mps_slab_rebase", "mps_multi_create", "mps_multi_destroy", "mps_multi_slab",
     "mps_multi_set_b", "mps_multi_spmm", "mps_multi_get_c",
 ]
@@ -70,7 +70,6 @@ def lib():
     L.mps_plan_partition.argtypes = [vp, vp, vp]
     L.mps_spmm.argtypes = [vp, vp, vp, vp, vp, vp, vp]
     L.mps_spmm_scaled.argtypes = [vp] * 8
-    L.mps_plan_mark_hot_columns.argtypes = [vp, vp, i32, i64, vp, C.POINTER(i64), C.POINTER(i64)]
     L.mps_plan_sync_check.argtypes = [vp, vp]
     L.mps_plan_info.argtypes = [vp, C.POINTER(i64)]
     L.mps_plan_layout.argtypes = [vp, C.POINTER(i64)]

@@ -8,10 +8,8 @@
 #include <cstdio>
 #include <cstring>
 #include <initializer_list>
-#include <atomic>
 #include <new>
 #include <string>
-#include <thread>
 
 #include "mps_internal.h"
 #include "mps_kernels.cuh"
@@ -212,8 +210,6 @@ static void plan_free_scratch(mps_plan *p) {
     cudaFree(p->d_tile_xy); cudaFree(p->d_tcarry); cudaFree(p->d_thead);
     cudaFree(p->d_status); cudaFree(p->d_long_list); cudaFree(p->d_long_count);
     cudaFree(p->d_consumer); cudaFree(p->d_need); cudaFree(p->d_cnt);
-    cudaFree(p->d_col_hot);
-    p->d_col_hot = nullptr;
     p->d_tile_xy = nullptr; p->d_tcarry = p->d_thead = nullptr;
     p->d_status = p->d_long_list = p->d_long_count = nullptr;
     p->d_consumer = p->d_need = p->d_cnt = nullptr;
@@ -456,6 +452,17 @@ __global__ void rebase_kernel(const int *__restrict__ rp, int row0, int rows, in
     if (i <= rows) out[i] = rp[row0 + i] - rp[row0];
 }
 
+// Column indices of a slab in the workspace copy: an index outside [0, n_cols) is replaced by 0 and the smallest such
+// position recorded, so that the multiply that follows can only gather rows of B that exist; the host turns the record
+// into MPS_ERR_ARG.  Reads 4 bytes per non-zero out of device memory - nothing beside the upload it follows.
+__global__ void clamp_columns_kernel(int *__restrict__ col, long long n, unsigned n_cols, long long base, unsigned long long *__restrict__ first_bad) {
+    for (long long k = (long long)blockIdx.x * blockDim.x + threadIdx.x; k < n; k += (long long)gridDim.x * blockDim.x)
+        if ((unsigned)col[k] >= n_cols) {
+            atomicMin(first_bad, (unsigned long long)(base + k));
+            col[k] = 0;
+        }
+}
+
 namespace {
 const int kMaxHostSlabs = 8;
 const long long kHostSlabMinItems = 4ll << 20;  // below this the call is one slab
@@ -466,8 +473,10 @@ struct HostWorkspace {
     mps_plan *plan[kMaxHostSlabs] = {};
     cudaStream_t s_in = nullptr, s_b = nullptr, s_work = nullptr, s_out = nullptr;  // plan, upload, work, download
     cudaEvent_t ev_b = nullptr, ev_slab[kMaxHostSlabs] = {}, ev_done[kMaxHostSlabs] = {};
+    unsigned long long *d_bad = nullptr;  // smallest position of a column index outside [0, n_cols) seen by this call
     int device = -1;
     void release() {
+        cudaFree(d_bad); d_bad = nullptr;
         for (int i = 0; i < 6; ++i) { cudaFree(buf[i]); buf[i] = nullptr; cap[i] = 0; }
         for (int i = 0; i < kMaxHostSlabs; ++i) {
             mps_plan_destroy(plan[i]); plan[i] = nullptr;
@@ -497,42 +506,6 @@ static int ws_reserve(int i, size_t bytes) {
 
 extern "C" void mps_host_workspace_release(void) { g_ws.release(); }
 
-// The scan of col_idx (every index inside [0, n_cols)) on background host threads: started before the first CUDA
-// call, joined before the first kernel that gathers by col_idx is launched, so it runs beside the upload of B.
-struct ColumnScan {
-    std::thread worker;
-    std::atomic<int> done{0};          // ranges checked so far
-    std::atomic<long long> bad{-1};    // position of the first index outside [0, n_cols), or -1
-    long long lo[kMaxHostSlabs], hi[kMaxHostSlabs];
-    // ranges [begin[i], end[i]) of col are checked one after the other, in this order
-    void start(const int32_t *col, int32_t n_cols, int n, const long long *begin, const long long *end) {
-        long long total = 0;
-        for (int i = 0; i < n; ++i) { lo[i] = begin[i]; hi[i] = end[i]; total += end[i] - begin[i]; }
-        auto run = [this, col, n_cols, n](int threads) {
-            for (int i = 0; i < n; ++i) {
-                if (bad.load() < 0 && hi[i] > lo[i]) {
-                    const long long at = first_bad_column(col + lo[i], hi[i] - lo[i], n_cols, threads);
-                    if (at >= 0) bad.store(lo[i] + at);
-                }
-                done.store(i + 1, std::memory_order_release);
-            }
-        };
-        if (!col || total <= 0) { done.store(n); return; }
-        if (total < (1 << 16)) { run(1); return; }
-        worker = std::thread(run, 8);  // a few threads are enough to stay ahead of the upload and leave the host's memory to the DMA
-    }
-    // waits until range i has been checked; returns the first bad position found so far, or -1
-    long long wait_range(int i) {
-        while (done.load(std::memory_order_acquire) <= i) std::this_thread::yield();
-        return bad.load();
-    }
-    long long finish() {
-        if (worker.joinable()) worker.join();
-        return bad.load();
-    }
-    ~ColumnScan() { finish(); }
-};
-
 // The row slabs of one host-buffer call and the order in which they are uploaded and multiplied.
 struct HostSlabs {
     int n = 1;
@@ -558,7 +531,7 @@ static int host_slabs(int32_t n_rows, int32_t nnz, const int32_t *row_ptr, HostS
 
 static int host_call(int32_t n_rows, int32_t n_cols, int32_t nnz, int32_t dim, int dtype, int32_t cost, int32_t threads_per_warp,
                      const int32_t *row_ptr, const int32_t *col_idx, const void *val, const void *B, bool b_on_device, cudaStream_t b_stream,
-                     void *C, const HostSlabs &hs, ColumnScan &scan) {
+                     void *C, const HostSlabs &hs, long long *bad_column) {
     int dev = 0;
     MPS_CUDA(cudaGetDevice(&dev));
     if (g_ws.device != dev) { g_ws.release(); g_ws.device = dev; }
@@ -572,6 +545,7 @@ static int host_call(int32_t n_rows, int32_t n_cols, int32_t nnz, int32_t dim, i
             MPS_CUDA(cudaEventCreateWithFlags(&g_ws.ev_slab[i], cudaEventDisableTiming));
             MPS_CUDA(cudaEventCreateWithFlags(&g_ws.ev_done[i], cudaEventDisableTiming));
         }
+        MPS_CUDA(cudaMalloc(&g_ws.d_bad, sizeof(unsigned long long)));
     }
     const size_t elem = dtype == MPS_F16 ? 2 : 4;
     const int n_slabs = hs.n;
@@ -626,25 +600,23 @@ static int host_call(int32_t n_rows, int32_t n_cols, int32_t nnz, int32_t dim, i
     for (int s = n_slabs; s < kMaxHostSlabs; ++s) { mps_plan_destroy(g_ws.plan[s]); g_ws.plan[s] = nullptr; }
 
     MPS_CUDA(cudaStreamWaitEvent(s_work, g_ws.ev_b, 0));
-    // every upload is queued at once, in slab order, behind B on the upload stream ...
+    MPS_CUDA(cudaMemsetAsync(g_ws.d_bad, 0xff, sizeof(unsigned long long), s_work));
     for (int i = 0; i < n_slabs; ++i) {
         const int s = order[i];
-        const int r0 = bounds[s];
+        const int r0 = bounds[s], rows = bounds[s + 1] - bounds[s];
         const size_t k0 = (size_t)row_ptr[r0], len = (size_t)(row_ptr[bounds[s + 1]] - row_ptr[r0]);
         if (len) {
             MPS_CUDA(cudaMemcpyAsync(d_col + off[s], col_idx + k0, 4 * len, cudaMemcpyHostToDevice, s_up));
             if (val) MPS_CUDA(cudaMemcpyAsync(d_val + elem * off[s], (const char *)val + elem * k0, elem * len, cudaMemcpyHostToDevice, s_up));
         }
         MPS_CUDA(cudaEventRecord(g_ws.ev_slab[s], s_up));  // behind B on the same stream: B is whole when this fires
-    }
-    // ... and a slab's multiply is queued once the host has checked that slab's column indices (the scan runs in the
-    // same order on background threads and stays ahead of the link): no kernel gathers by an index that was not checked
-    for (int i = 0; i < n_slabs; ++i) {
-        const int s = order[i];
-        const int r0 = bounds[s], rows = bounds[s + 1] - bounds[s];
-        const long long bad = scan.wait_range(i);
-        if (bad >= 0) return fail(MPS_ERR_ARG, "mps_spmm_host: col_idx[%lld] = %d outside [0, %d)", bad, col_idx[bad], n_cols);
         MPS_CUDA(cudaStreamWaitEvent(s_work, g_ws.ev_slab[s], 0));
+        // the caller's column indices are checked where they have just landed, ahead of the multiply on the same stream:
+        // no kernel gathers by an index outside B (the host's memory is left to the uploads)
+        if (len) {
+            clamp_columns_kernel<<<592, 256, 0, s_work>>>(d_col + off[s], (long long)len, (unsigned)n_cols, (long long)k0, g_ws.d_bad);
+            MPS_CUDA(cudaGetLastError());
+        }
         char *c_slab = d_C + elem * (size_t)r0 * dim;
         if (int rc = mps_spmm(g_ws.plan[s], d_rps + rps_off[s], d_col + off[s], val ? (const void *)(d_val + elem * off[s]) : nullptr,
                               d_B, c_slab, s_work))
@@ -653,11 +625,14 @@ static int host_call(int32_t n_rows, int32_t n_cols, int32_t nnz, int32_t dim, i
         MPS_CUDA(cudaStreamWaitEvent(s_out, g_ws.ev_done[s], 0));
         if (rows) MPS_CUDA(cudaMemcpyAsync((char *)C + elem * (size_t)r0 * dim, c_slab, elem * (size_t)rows * dim, cudaMemcpyDeviceToHost, s_out));
     }
+    unsigned long long first_bad = ~0ull;
+    MPS_CUDA(cudaMemcpyAsync(&first_bad, g_ws.d_bad, sizeof first_bad, cudaMemcpyDeviceToHost, s_work));
     MPS_CUDA(cudaStreamSynchronize(s_in));
     MPS_CUDA(cudaStreamSynchronize(s_up));
     MPS_CUDA(cudaStreamSynchronize(s_out));
     for (int s = 0; s < n_slabs; ++s)
         if (int rc = mps_plan_sync_check(g_ws.plan[s], s_work)) return rc;
+    if (first_bad != ~0ull) *bad_column = (long long)first_bad;
     return MPS_OK;
 }
 
@@ -668,20 +643,22 @@ static int host_entry(const char *who, int32_t n_rows, int32_t n_cols, int32_t n
     if (dtype != MPS_F32 && dtype != MPS_F16) return fail(MPS_ERR_ARG, "%s: unknown dtype %d", who, dtype);
     if (int rc = check_shape(n_rows, nnz)) return rc;
     if (row_ptr[n_rows] != nnz) return fail(MPS_ERR_ARG, "%s: row_ptr[n_rows] is %d, nnz is %d", who, row_ptr[n_rows], nnz);
-    // the caller's arrays are checked on the host before any kernel can index by them: row_ptr here (small), col_idx
-    // on background threads while the uploads start; a bad index is reported in preference to any later failure
+    // the caller's arrays are checked before any kernel can index by them: row_ptr here on the host (small, and the slab
+    // bounds are taken from it), col_idx on the device where each slab lands; a bad index is reported in preference to any
+    // other failure of the call
     if (int rc = check_csr_host(who, n_rows, n_cols, row_ptr, nullptr, 0)) return rc;
+    if (n_cols == 0 && nnz > 0) return fail(MPS_ERR_ARG, "%s: col_idx[0] = %d outside [0, 0)", who, col_idx[0]);
     HostSlabs hs;
     if (int rc = host_slabs(n_rows, nnz, row_ptr, &hs)) return rc;
-    long long begin[kMaxHostSlabs], end[kMaxHostSlabs];
-    for (int i = 0; i < hs.n; ++i) {
-        begin[i] = row_ptr[hs.bounds[hs.order[i]]];
-        end[i] = row_ptr[hs.bounds[hs.order[i] + 1]];
+    long long bad = -1;
+    int rc = host_call(n_rows, n_cols, nnz, dim, dtype, cost, threads_per_warp, row_ptr, col_idx, val, B, b_on_device, (cudaStream_t)b_stream, C, hs, &bad);
+    // without a usable device nothing was checked there: the same check on host threads, so that a bad index is
+    // reported in preference to the missing device
+    if (rc == MPS_ERR_CUDA && bad < 0) {
+        const std::string kept = g_error;
+        bad = first_bad_column(col_idx, nnz, n_cols, 0);
+        g_error = kept;
     }
-    ColumnScan scan;
-    scan.start(col_idx, n_cols, hs.n, begin, end);
-    int rc = host_call(n_rows, n_cols, nnz, dim, dtype, cost, threads_per_warp, row_ptr, col_idx, val, B, b_on_device, (cudaStream_t)b_stream, C, hs, scan);
-    const long long bad = scan.finish();
     if (rc != MPS_OK || bad >= 0) {
         // a step failed with copies possibly still queued on the caller's buffers: let them drain before the caller
         // may free those buffers (the message of the failure stays the one reported)

@@ -64,29 +64,25 @@ static int launch_tile_gl(const mps_plan *p, const TileParams &tp, cudaStream_t 
     return fail(MPS_ERR_STATE, "no kernel for %d lanes per chunk", p->gl);
 }
 
-// The variants with per-row L2 policies (columns marked hot in the plan's own col_idx) and / or a warp per unit:
-// one block size (64), one unroll (8).
-template <typename T, int VEC, int GL, bool HOT, bool SPREAD>
-static int launch_tile_x_k(const mps_plan *p, const TileParams &tp, cudaStream_t st) {
-    auto kern = spmm_tile_kernel<T, VEC, GL, 8, 64, false, HOT, SPREAD>;
+// The variant with a warp per unit: one block size (64), one unroll (8).
+template <typename T, int VEC, int GL>
+static int launch_tile_warp_k(const mps_plan *p, const TileParams &tp, cudaStream_t st) {
+    auto kern = spmm_tile_kernel<T, VEC, GL, 8, 64, false, true>;
     if (p->smem_bytes > 48 * 1024) MPS_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, p->smem_bytes));
     dim3 grid((unsigned)p->n_tiles, (unsigned)p->n_col_slabs);
     kern<<<grid, 64, p->smem_bytes, st>>>(tp);
     MPS_CUDA(cudaGetLastError());
     return MPS_OK;
 }
-template <typename T, int VEC, bool HOT, bool SPREAD>
-static int launch_tile_x(const mps_plan *p, const TileParams &tp, cudaStream_t st) {
+template <typename T, int VEC>
+static int launch_tile_warp(const mps_plan *p, const TileParams &tp, cudaStream_t st) {
     switch (p->gl) {
-        case 2: return launch_tile_x_k<T, VEC, 2, HOT, SPREAD>(p, tp, st);
-        case 4: return launch_tile_x_k<T, VEC, 4, HOT, SPREAD>(p, tp, st);
-        case 8: return launch_tile_x_k<T, VEC, 8, HOT, SPREAD>(p, tp, st);
-        case 16: return launch_tile_x_k<T, VEC, 16, HOT, SPREAD>(p, tp, st);
-        case 32:
-            if constexpr (!SPREAD) return launch_tile_x_k<T, VEC, 32, HOT, false>(p, tp, st);
-            break;
+        case 2: return launch_tile_warp_k<T, VEC, 2>(p, tp, st);
+        case 4: return launch_tile_warp_k<T, VEC, 4>(p, tp, st);
+        case 8: return launch_tile_warp_k<T, VEC, 8>(p, tp, st);
+        case 16: return launch_tile_warp_k<T, VEC, 16>(p, tp, st);
     }
-    return fail(MPS_ERR_STATE, "no kernel for %d lanes per chunk", p->gl);
+    return fail(MPS_ERR_STATE, "no warp-per-unit kernel for %d lanes per chunk", p->gl);
 }
 
 template <typename T, int FULLVEC, bool SCALED>
@@ -94,17 +90,10 @@ static int spmm_typed(mps_plan *p, const TileParams &tp, cudaStream_t st) {
     int rc;
     const bool prof = p->profiling && p->prof_used < kProfSlots;
     if (prof) MPS_CUDA(cudaEventRecord(p->prof_ev[2 * p->prof_used], st));
-    bool hot = false;
-    if constexpr (!SCALED) hot = p->d_col_hot != nullptr && p->vec > 1 && p->block == 64 && p->unroll == 8;
     if (p->vec == 1) rc = launch_tile_b<T, 1, 32, 4, SCALED>(p, tp, st);
-    else if (hot || (p->walk && !SCALED)) {
-        if constexpr (!SCALED) {
-            TileParams th = tp;
-            if (hot) th.col = p->d_col_hot;  // same indices as the caller's col_idx, bit 31 set on the marked columns
-            if (hot && p->walk) rc = launch_tile_x<T, FULLVEC, true, true>(p, th, st);
-            else if (hot) rc = launch_tile_x<T, FULLVEC, true, false>(p, th, st);
-            else rc = launch_tile_x<T, FULLVEC, false, true>(p, th, st);
-        } else rc = MPS_ERR_STATE;
+    else if (p->walk && !SCALED) {
+        if constexpr (!SCALED) rc = launch_tile_warp<T, FULLVEC>(p, tp, st);
+        else rc = MPS_ERR_STATE;
     } else rc = launch_tile_gl<T, FULLVEC, SCALED>(p, tp, st);
     if (rc != MPS_OK) return rc;
     if (prof) { MPS_CUDA(cudaEventRecord(p->prof_ev[2 * p->prof_used + 1], st)); ++p->prof_used; }

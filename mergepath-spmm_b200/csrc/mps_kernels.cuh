@@ -134,11 +134,6 @@ __device__ __forceinline__ uint64_t l2_evict_first_policy() {
     asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
     return policy;
 }
-__device__ __forceinline__ uint64_t l2_evict_last_policy() {
-    uint64_t policy;
-    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(policy));
-    return policy;
-}
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar, uint64_t policy) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(dst),
                  "l"(src), "r"(bytes), "r"(bar), "l"(policy)
@@ -191,11 +186,6 @@ struct Lane<float, 4> {
     static __device__ __forceinline__ scalar from_float(float v) { return v; }
     static __device__ __forceinline__ scalar one() { return 1.0f; }
     static __device__ __forceinline__ raw load(const float *p) { return __ldg(reinterpret_cast<const float4 *>(p)); }
-    static __device__ __forceinline__ raw load_hint(const float *p, uint64_t policy) {
-        float4 v;
-        asm("ld.global.nc.L2::cache_hint.v4.f32 {%0, %1, %2, %3}, [%4], %5;" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p), "l"(policy));
-        return v;
-    }
     static __device__ __forceinline__ void fma(float (&acc)[4], float a, const raw &b) {
         acc[0] = fmaf(a, b.x, acc[0]); acc[1] = fmaf(a, b.y, acc[1]);
         acc[2] = fmaf(a, b.z, acc[2]); acc[3] = fmaf(a, b.w, acc[3]);
@@ -212,7 +202,6 @@ struct Lane<float, 1> {
     static __device__ __forceinline__ scalar from_float(float v) { return v; }
     static __device__ __forceinline__ scalar one() { return 1.0f; }
     static __device__ __forceinline__ raw load(const float *p) { return __ldg(p); }
-    static __device__ __forceinline__ raw load_hint(const float *p, uint64_t) { return __ldg(p); }
     static __device__ __forceinline__ void fma(float (&acc)[1], float a, const raw &b) { acc[0] = fmaf(a, b, acc[0]); }
     static __device__ __forceinline__ void store(float *p, const float (&v)[1]) { __stcs(p, v[0]); }
 };
@@ -224,11 +213,6 @@ struct Lane<__half, 8> {
     static __device__ __forceinline__ scalar from_float(float) { return (unsigned short)0x3C00; }  // scaled products are fp32-only
     static __device__ __forceinline__ scalar one() { return (unsigned short)0x3C00; }
     static __device__ __forceinline__ raw load(const __half *p) { return __ldg(reinterpret_cast<const uint4 *>(p)); }
-    static __device__ __forceinline__ raw load_hint(const __half *p, uint64_t policy) {
-        uint4 v;
-        asm("ld.global.nc.L2::cache_hint.v4.u32 {%0, %1, %2, %3}, [%4], %5;" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p), "l"(policy));
-        return v;
-    }
     static __device__ __forceinline__ void fma(float (&acc)[8], scalar a, const raw &b) {
         fma_f32_f16x2(acc[0], acc[1], a, b.x);
         fma_f32_f16x2(acc[2], acc[3], a, b.y);
@@ -251,7 +235,6 @@ struct Lane<__half, 1> {
     static __device__ __forceinline__ scalar from_float(float v) { return v; }
     static __device__ __forceinline__ scalar one() { return 1.0f; }
     static __device__ __forceinline__ raw load(const __half *p) { return __ldg(p); }
-    static __device__ __forceinline__ raw load_hint(const __half *p, uint64_t) { return __ldg(p); }
     static __device__ __forceinline__ void fma(float (&acc)[1], float a, const raw &b) { acc[0] = fmaf(a, __half2float(b), acc[0]); }
     static __device__ __forceinline__ void store(__half *p, const float (&v)[1]) { *p = __float2half_rn(v[0]); }
 };
@@ -394,16 +377,13 @@ __device__ __forceinline__ void block_fixup(const TileParams &p, int e, int chai
 // lanes with the accumulator kept in registers across the chunk boundaries inside the unit.
 // SCALED: the value of non-zero (i, j) is row_scale[i] * col_scale[j] instead of a stored value (a kernel of
 // its own so that the plain product carries none of its selects).
-// HOT: bit 31 of a staged column index marks a column whose row of B should stay in the L2 (set by
-// mps_plan_mark_hot_columns in the plan's own copy of col_idx); such rows are gathered with an evict-last policy,
-// all others with evict-first, so that the rows with the most reuse are the ones the L2 keeps.
 // SPREAD: a unit is walked by a whole warp instead of one lane group.  The warp's 32/GL lane groups take consecutive
 // non-zeros of the unit (group s the non-zeros at offset s, s + 32/GL, .. from the unit's start), each keeping a partial
 // sum of the row in progress; at every row end the partial sums are combined with xor-shuffles in a fixed tree and the
 // first group stores the row.  All lanes of a warp then follow the same rows, so none is masked off where the units of
 // neighbouring groups would end their rows at different places - which is what costs at small dim, where a warp holds
 // eight groups.
-template <typename T, int VEC, int GL, int U, int BLOCK, bool SCALED, bool HOT = false, bool SPREAD = false>
+template <typename T, int VEC, int GL, int U, int BLOCK, bool SCALED, bool SPREAD = false>
 __global__ void __launch_bounds__(BLOCK, kWarpsPerSm * 32 / BLOCK) spmm_tile_kernel(const TileParams p) {
     constexpr int kBlock = BLOCK;
     constexpr int UL = SPREAD ? 32 : GL;   // lanes that walk one unit
@@ -432,27 +412,8 @@ __global__ void __launch_bounds__(BLOCK, kWarpsPerSm * 32 / BLOCK) spmm_tile_ker
     const T *__restrict__ Bl = static_cast<const T *>(p.B) + coff;  // this lane's columns of B
     T *__restrict__ Cl = static_cast<T *>(p.C) + coff;
     const unsigned dim = (unsigned)p.dim;
-    [[maybe_unused]] uint64_t keep = 0, pass = 0;
-    if constexpr (HOT) {
-        keep = l2_evict_last_policy(); pass = l2_evict_first_policy();
-#if defined(MPS_AB_COLD) && MPS_AB_COLD == 1
-        asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(pass));
-#elif defined(MPS_AB_COLD) && MPS_AB_COLD == 2
-        asm volatile("createpolicy.fractional.L2::evict_unchanged.b64 %0, 1.0;" : "=l"(pass));
-#endif
-#if defined(MPS_AB_HOT_NORMAL)
-        asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(keep));
-#endif
-    }
-    // one gathered row of B (this lane's columns); HOT strips the mark and picks the policy
-    auto gather = [&](unsigned ci) -> typename Lane<T, VEC>::raw {
-        if constexpr (HOT) {
-            const uint64_t pol = (ci >> 31) ? keep : pass;
-            return Lane<T, VEC>::load_hint(Bl + (size_t)(ci & 0x7fffffffu) * dim, pol);
-        } else {
-            return Lane<T, VEC>::load(Bl + (size_t)ci * dim);
-        }
-    };
+    // one gathered row of B (this lane's columns)
+    auto gather = [&](unsigned ci) -> typename Lane<T, VEC>::raw { return Lane<T, VEC>::load(Bl + (size_t)ci * dim); };
 
     const int2 c0 = __ldg(p.tile_xy + t), c1 = __ldg(p.tile_xy + t + 1);
     const int X0 = c0.x, Y0 = c0.y, X1 = c1.x, Y1 = c1.y;

@@ -24,8 +24,6 @@ struct mps_plan {
     float *d_tcarry, *d_thead;
     int *d_status, *d_long_list, *d_long_count;
     int *d_consumer, *d_need, *d_cnt;  // per tile: who ends my carry's row, contributions awaited, arrivals (x column slabs)
-    int *d_col_hot;    // the plan's own copy of col_idx with bit 31 set on hot columns (mps_plan_mark_hot_columns), or nullptr
-    long long hot_columns, hot_nnz;
     bool profiling;
     int prof_used;
     cudaEvent_t prof_ev[2 * kProfSlots];

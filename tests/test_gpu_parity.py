@@ -525,29 +525,24 @@ def test_warp_per_unit_walk_on_a_mid_size_graph_and_where_it_does_not_apply(mps,
         _check(orc, rp, col, val, Bx, got, info, 16, 1e-5)
 
 
-def test_hot_column_marking_changes_cache_policy_not_results(mps, graphs, cuda):
-    """mps_plan_mark_hot_columns: the most frequent columns' rows of B are gathered with an L2 evict-last policy, the
-    others with evict-first; the plan reads its own marked copy of col_idx.  Same bits as without marking."""
-    rp, col = graphs.rmat_csr(16, 32, seed=5)
+def test_host_call_reports_a_bad_column_index_without_gathering_by_it(mps, graphs, cuda):
+    """With a device the column indices are checked where they land (and replaced by 0 in the workspace copy before the
+    multiply runs): the call returns MPS_ERR_ARG naming the first bad position, nothing faults, and the next call works."""
+    rp, col = graphs.rmat_csr(19, 32, seed=3)       # large enough for several slabs
     val = graphs.gcn_values(rp, col)
-    n, nnz = len(rp) - 1, len(col)
-    d_rp, d_col, d_val = _dev(rp, cuda), _dev(col, cuda), _dev(val, cuda)
-    for dim, half in ((64, False), (16, False), (128, True)):
-        B = graphs.dense_normal_f16(n, dim, seed=6) if half else graphs.dense_uniform(n, dim, seed=6)
-        v = d_val.to(torch.float16) if half else d_val
-        d_B = _dev(B, cuda)
-        plan = mps.Plan(n, nnz, dim, mps.F16 if half else mps.F32, 16, device=cuda)
-        plan.partition(d_rp)
-        plain = plan.spmm(d_rp, d_col, v, d_B).clone()
-        cols, hits = plan.mark_hot_columns(d_col, n, 2 << 20)           # 2 MB of rows
-        assert 0 < cols <= (2 << 20) // (dim * B.itemsize) and hits > cols
-        marked = plan.spmm(d_rp, d_col, v, d_B)
-        plan.sync_check()
-        assert torch.equal(plain, marked)
-        assert plan.mark_hot_columns(d_col, n, 0) == (0, 0)             # switched off again
-        assert torch.equal(plain, plan.spmm(d_rp, d_col, v, d_B))
-        plan.sync_check()
-        plan.close()
+    n = len(rp) - 1
+    B = graphs.dense_uniform(n, 16, seed=4)
+    good = mps.spmm_host(rp, col, val, B, cost=16)
+    for where, value in ((len(col) - 5, n), (len(col) // 2, -3), (7, 2**31 - 1)):
+        bad = col.copy()
+        bad[where] = value
+        bad[len(col) - 1] = n + 9                    # a later one as well: the first is reported
+        with pytest.raises(mps.MpsError) as e:
+            mps.spmm_host(rp, bad, val, B, cost=16)
+        assert e.value.code == mps.capi.ERR_ARG and f"col_idx[{where}] = {value}" in str(e.value)
+    again = mps.spmm_host(rp, col, val, B, cost=16)
+    assert np.array_equal(_bits(again), _bits(good))
+    mps.capi.lib().mps_host_workspace_release()
 
 
 def test_gather_probe_reports_a_plausible_rate(mps, cuda):
