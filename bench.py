@@ -68,6 +68,7 @@ def parse_args():
     ap.add_argument("--c5-degree", type=int, default=64)
     ap.add_argument("--c5-dim", type=int, default=32)
     ap.add_argument("--c5-steps", type=int, default=20)
+    ap.add_argument("--walk", type=int, default=-1, help="1: a warp walks a unit (mps_plan_set_walk), 0: a lane group per unit, -1: automatic")
     ap.add_argument("--slab", default="", help="R/N: on one GPU, the workload of rank R of an N-GPU run (graph of 2^scale * N nodes, slab R of N) - for profiling")
     ap.add_argument("--no-probe", action="store_true", help="leave out the gather-rate probe (roofline.l2_peak_gbs)")
     return ap.parse_args()
@@ -468,6 +469,8 @@ def run_ours(args):
     plan = mps.Plan(n_slab, nnz_slab, args.dim, dt, cost, args.tpw, device=dev)
     if args.chunks_per_unit or args.unroll or args.no_bulk or args.block or args.fused >= 0:
         plan.tune(args.chunks_per_unit, args.unroll, not args.no_bulk, args.block, args.fused)
+    if args.walk >= 0:
+        plan.set_walk(args.walk)
     partition_first_ms = partition_ms = 0.0
     for i in range(2):  # the first call also loads the library's kernels onto the device
         t0 = time.perf_counter()
@@ -513,7 +516,7 @@ def run_ours(args):
         "vs_baseline": None, "dtype": "f16 storage / f32 accumulate" if w["half"] else "f32", "data": "synthetic",
         "config": {"workload": workload_name(args, world), "nodes": w["n"], "nnz": w["nnz"], "dim": args.dim, "cost": cost,
                    "threads_per_warp": info["threads_per_warp"], "values": "gcn", "parallelism": f"row-slabs x{world} ({args.balance}-balanced, row weight {args.row_weight}), B replicated", "per_rank_ms": per_rank_ms, "per_rank_rows": [int(v) for v in all_ranks(float(n_slab), world)], "per_rank_nnz": [int(v) for v in all_ranks(float(nnz_slab), world)],
-                   "l2": "inputs larger than L2 (B and A each > 126 MB)", "unit_items": info["unit_items"], "units_per_tile": info["units_per_tile"],
+                   "l2": "inputs larger than L2 (B and A each > 126 MB)", "unit_items": info["unit_items"], "units_per_tile": info["units_per_tile"], "groups_per_unit": info["groups_per_unit"],
                    "items_per_chunk": info["items_per_chunk"], "unroll": info["unroll"], "block_threads": info["block_threads"], "tiles": info["n_tiles"],
                    "long_rows": info["long_rows"]},
         "check": check, "roofline": roofline, "e2e": e2e, "gpu_launches": args.steps * info["kernels_per_call"],

@@ -43,6 +43,24 @@ def test_first_line_matches_the_reference(cli, c1_file):
     assert "threads_per_warp 32 exceeds" in r.stderr  # clamped where the reference exits
 
 
+def test_binary_sidecar_is_accepted_in_place_of_the_text_file(cli, c1_file, tmp_path, mps):
+    path, n, nnz = c1_file
+    rp, col = cases.c1_rmat()
+    side = str(tmp_path / "c1.bin")
+    mps.save_csr_bin(side, rp, col)
+    r = subprocess.run([cli, side, "16", "8", "1", "1"], capture_output=True, text=True)
+    assert r.stdout.splitlines()[0] == f"Total number of rows: {n} and non-zeros: {nnz}"
+
+
+def test_any_cost_the_reference_accepts_is_accepted(cli, c1_file):
+    """The reference's command line takes any positive cost (src/MergePathSpMM.cu:121); so does this one - without a
+    device the run stops at the device, not at the cost."""
+    path, n, nnz = c1_file
+    for cost in ("1000", "100000000"):
+        r = subprocess.run([cli, path, "16", cost, "1", "1"], capture_output=True, text=True)
+        assert "shared memory" not in r.stderr and r.stdout.startswith("Total number of rows")
+
+
 @pytest.mark.gpu
 @pytest.mark.parametrize("extra", [[], ["--values=gcn"], ["--dtype=f16", "--values=gcn"]])
 def test_runs_and_checks_on_the_gpu(cli, c1_file, cuda, extra):
@@ -51,6 +69,8 @@ def test_runs_and_checks_on_the_gpu(cli, c1_file, cuda, extra):
         r = subprocess.run([cli, path, dim, "8", "2", "3", "--check"] + extra, capture_output=True, text=True)
         assert r.returncode == 0, r.stdout + r.stderr
         assert "check: 0 elements outside tolerance" in r.stdout and "GFLOP/s" in r.stdout
+    r = subprocess.run([cli, path, "64", "100000", "1", "2", "--check"] + extra, capture_output=True, text=True)   # a cost far beyond one tile
+    assert r.returncode == 0 and "check: 0 elements outside tolerance" in r.stdout, r.stdout + r.stderr
 
 
 @pytest.mark.gpu
