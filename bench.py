@@ -361,8 +361,26 @@ def e2e_through_host_call(mps, args, w, world, rank, dev, cost, dt, n_slab, nnz_
     copy inside the timed region.  One rank: mps_spmm_host.  Several ranks: every rank uploads 1/N of B's rows, an
     NCCL all-gather completes B over NVLink, and mps_spmm_host_resident_b uploads the rank's slab of A meanwhile."""
     import torch
-    from mergepath_spmm_b200 import multi
-    h = {k: (w[k].cpu().pin_memory() if w[k] is not None else None) for k in ("rp", "col", "val")}
+    from mergepath_spmm_b200 import graphs, multi
+    elem = 2 if w["half"] else 4
+    d = {k: w[k] for k in ("rp", "col", "val")}   # this rank's slab of A on the device (for the check afterwards)
+    slabs = "the slabs of the device-timed run"
+    if world > 1:
+        # a rank's call is bound by its own PCIe link: 4 + s bytes up per non-zero, dim * s bytes down per row.  The slabs
+        # that balance the kernel (nnz + 4 rows) give one rank up to 47x the rows of another; for this call A is cut
+        # on link bytes instead (same matrix, same product)
+        row_w = max(1, args.dim * elem // (4 + elem))
+        rp, col = graphs.rmat_csr(w["scale"], args.avg_degree, args.seed, device=dev)
+        val = graphs.gcn_values(rp, col, "f16" if w["half"] else "f32")
+        bounds = mps.slab_bounds(rp.cpu().numpy(), world, "items", row_w)
+        r0, r1 = int(bounds[rank]), int(bounds[rank + 1])
+        k0, k1 = int(rp[r0].item()), int(rp[r1].item())
+        d = {"rp": (rp[r0:r1 + 1] - k0).contiguous(), "col": col[k0:k1].clone(), "val": val[k0:k1].clone()}
+        del rp, col, val
+        torch.cuda.empty_cache()
+        n_slab, nnz_slab = r1 - r0, int(d["col"].numel())
+        slabs = f"balanced on link bytes: nnz + {row_w} rows"
+    h = {k: (d[k].cpu().pin_memory() if d[k] is not None else None) for k in ("rp", "col", "val")}
     h_C = torch.empty((n_slab, args.dim), dtype=w["B"].dtype).pin_memory()
     if world == 1:
         h["B"] = w["B"].cpu().pin_memory()
@@ -385,18 +403,21 @@ def e2e_through_host_call(mps, args, w, world, rank, dev, cost, dt, n_slab, nnz_
     t0 = time.perf_counter()
     for _ in range(steps):
         call()
+    t_mine = time.perf_counter() - t0   # this rank's calls alone (each is blocking); the job's time includes the barrier
     barrier(world)
     e2e_s = max_over_ranks((time.perf_counter() - t0) / steps, world)
+    e2e_rank_s = t_mine / steps
     h2d = sum(h[k].numel() * h[k].element_size() for k in h if h[k] is not None)
     d2h = h_C.numel() * h_C.element_size()
-    chk = check_product(w["rp"], w["col"], w["val"], w["B"], h_C.to(dev), w["half"], seed=100 + rank)   # the C that came back to the host
+    chk = check_product(d["rp"], d["col"], d["val"], w["B"], h_C.to(dev), w["half"], seed=100 + rank)   # the C that came back to the host
     ok = bool(min_over_ranks(1.0 if chk["ok"] else 0.0, world) > 0.5)
     mps.capi.lib().mps_host_workspace_release()
     host = {k: (h[k].numpy() if h[k] is not None else None) for k in h} if world == 1 else None
     flop_nnz = nnz_slab if (args.slab and world == 1) else w["nnz"]
     return {"value": round(2.0 * flop_nnz * args.dim / e2e_s / 1e9, 2), "unit": "GFLOP/s", "h2d_bytes_per_step": int(sum_over_ranks(h2d, world)),
             "d2h_bytes_per_step": int(sum_over_ranks(d2h, world)), "ms_per_step": round(e2e_s * 1e3, 3), "steps": steps,
-            "b_replication": "each rank uploads 1/N of B, NCCL all-gather over NVLink" if world > 1 else "one upload",
+            "b_replication": "each rank uploads 1/N of B, NCCL all-gather over NVLink" if world > 1 else "one upload", "slabs": slabs,
+            "per_rank_ms": all_ranks(e2e_rank_s * 1e3, world),
             "check": {"ok": ok, "max_scaled_err": max_over_ranks(chk["max_scaled_err"], world), "rows": int(sum_over_ranks(chk["rows"], world))}}, host
 
 
@@ -407,25 +428,33 @@ def c5_strong(mps, args, world, rank, dev):
     from mergepath_spmm_b200 import graphs
     torch.cuda.empty_cache()
     t0 = time.perf_counter()
-    rp, col = graphs.rmat_csr(args.c5_scale, args.c5_degree, args.seed, device=dev)
-    n, nnz = rp.numel() - 1, col.numel()
-    val = graphs.gcn_values(rp, col, "f32")
-    if world > 1:
-        bounds = mps.slab_bounds(rp.cpu().numpy(), world, "items", args.row_weight)
-        r0, r1 = int(bounds[rank]), int(bounds[rank + 1])
-        k0, k1 = int(rp[r0].item()), int(rp[r1].item())
-        s_rp, s_col, s_val = (rp[r0:r1 + 1] - k0).contiguous(), col[k0:k1].clone(), val[k0:k1].clone()
-        del rp, col, val
-    else:
-        r0, r1, s_rp, s_col, s_val = 0, n, rp, col, val
-    torch.cuda.empty_cache()
     dim = args.c5_dim
-    B = graphs.dense_uniform(n, dim, args.seed + 1, device=dev)
-    torch.cuda.synchronize()
+    built, why = True, ""
+    try:
+        rp, col = graphs.rmat_csr(args.c5_scale, args.c5_degree, args.seed, device=dev)
+        n, nnz = rp.numel() - 1, col.numel()
+        val = graphs.gcn_values(rp, col, "f32")
+        if world > 1:
+            bounds = mps.slab_bounds(rp.cpu().numpy(), world, "items", args.row_weight)
+            r0, r1 = int(bounds[rank]), int(bounds[rank + 1])
+            k0, k1 = int(rp[r0].item()), int(rp[r1].item())
+            s_rp, s_col, s_val = (rp[r0:r1 + 1] - k0).contiguous(), col[k0:k1].clone(), val[k0:k1].clone()
+            del rp, col, val
+        else:
+            r0, r1, s_rp, s_col, s_val = 0, n, rp, col, val
+        torch.cuda.empty_cache()
+        B = graphs.dense_uniform(n, dim, args.seed + 1, device=dev)
+        torch.cuda.synchronize()
+        n_slab, nnz_slab = r1 - r0, s_col.numel()
+        plan = mps.Plan(n_slab, nnz_slab, dim, mps.F32, args.cost or DEFAULT_COST, args.tpw, device=dev)
+        plan.partition(s_rp)
+    except (torch.cuda.OutOfMemoryError, mps.MpsError) as e:
+        built, why = False, str(e)[:160]
+    # every rank takes the same branch: one that could not build must not leave the others waiting in a collective
+    if min_over_ranks(1.0 if built else 0.0, world) < 0.5:
+        torch.cuda.empty_cache()
+        return {"unavailable": "a rank could not build the workload" + (": " + why if why else "")}
     build_s = time.perf_counter() - t0
-    n_slab, nnz_slab = r1 - r0, s_col.numel()
-    plan = mps.Plan(n_slab, nnz_slab, dim, mps.F32, args.cost or DEFAULT_COST, args.tpw, device=dev)
-    plan.partition(s_rp)
     C_out = torch.empty((n_slab, dim), dtype=torch.float32, device=dev)
     w = dict(rp=s_rp, col=s_col, val=s_val, B=B, half=False, n=n, nnz=nnz)
     for _ in range(3):
@@ -539,10 +568,7 @@ def run_ours(args):
     torch.cuda.empty_cache()
 
     if not args.no_c5:
-        try:
-            out["c5_strong"] = c5_strong(mps, args, world, rank, dev)
-        except torch.cuda.OutOfMemoryError as e:
-            out["c5_strong"] = {"unavailable": "out of device memory: " + str(e)[:120]}
+        out["c5_strong"] = c5_strong(mps, args, world, rank, dev)
     if rank == 0:
         print(json.dumps(out), flush=True)
     if world > 1:
