@@ -68,6 +68,7 @@ def parse_args():
     ap.add_argument("--c5-degree", type=int, default=64)
     ap.add_argument("--c5-dim", type=int, default=32)
     ap.add_argument("--c5-steps", type=int, default=20)
+    ap.add_argument("--c5-sweep", type=int, nargs="*", default=[16, 64, 128], help="other widths timed on the same slabs (the configuration's dim sweep)")
     ap.add_argument("--walk", type=int, default=-1, help="1: a warp walks a unit (mps_plan_set_walk), 0: a lane group per unit, -1: automatic")
     ap.add_argument("--slab", default="", help="R/N: on one GPU, the workload of rank R of an N-GPU run (graph of 2^scale * N nodes, slab R of N) - for profiling")
     ap.add_argument("--no-probe", action="store_true", help="leave out the gather-rate probe (roofline.l2_peak_gbs)")
@@ -467,8 +468,28 @@ def c5_strong(mps, args, world, rank, dev):
     check = check_product(s_rp, s_col, s_val, B, C_out, False, seed=rank)
     info = plan.info()
     plan.close()
+    # the other widths of the configuration's sweep on the same slabs (fewer steps; each with its own look at C)
+    sweep = {}
+    for d2 in [d for d in args.c5_sweep if d != dim]:
+        del B, C_out
+        torch.cuda.empty_cache()
+        B = graphs.dense_uniform(n, d2, args.seed + 1, device=dev)
+        C_out = torch.full((n_slab, d2), float("nan"), dtype=torch.float32, device=dev)
+        p2 = mps.Plan(n_slab, nnz_slab, d2, mps.F32, args.cost or DEFAULT_COST, args.tpw, device=dev)
+        p2.partition(s_rp)
+        w2 = dict(rp=s_rp, col=s_col, val=s_val, B=B)
+        for _ in range(3):
+            p2.spmm(s_rp, s_col, s_val, B, out=C_out)
+        steps2 = max(3, args.c5_steps // 2)
+        ms2, _ = time_multiplies(p2, w2, C_out, steps2, world)
+        p2.sync_check()
+        p2.close()
+        ms2 = max_over_ranks(ms2, world) / steps2
+        c2 = check_product(s_rp, s_col, s_val, B, C_out, False, seed=rank + d2, n_random=1024, n_long=8)
+        sweep[str(d2)] = {"ms_per_step": round(ms2, 4), "value": round(2.0 * nnz * d2 / (ms2 * 1e-3) / 1e9, 2),
+                          "check_ok": bool(min_over_ranks(1.0 if c2["ok"] else 0.0, world) > 0.5)}
     alg = mps.algorithmic_bytes(n_slab, nnz_slab, dim, mps.F32, True)
-    out = {"workload": f"rmat{args.c5_scale}_deg{args.c5_degree}_gcn_f32_dim{dim}", "scaling": "strong", "nodes": n, "nnz": nnz, "dim": dim,
+    out = {"workload": f"rmat{args.c5_scale}_deg{args.c5_degree}_gcn_f32_dim{dim}", "scaling": "strong", "dim_sweep": sweep, "nodes": n, "nnz": nnz, "dim": dim,
            "n_gpus": world, "steps": args.c5_steps, "ms_per_step": round(ms_step, 4), "value": round(2.0 * nnz * dim / (ms_step * 1e-3) / 1e9, 2),
            "unit": "GFLOP/s", "per_rank_ms": all_ranks(ms_mine / args.c5_steps, world), "per_rank_nnz": [int(v) for v in all_ranks(float(nnz_slab), world)],
            "per_rank_rows": [int(v) for v in all_ranks(float(n_slab), world)], "tiles": info["n_tiles"], "long_rows": info["long_rows"],

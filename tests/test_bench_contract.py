@@ -46,4 +46,15 @@ def test_default_arm_line_on_a_small_graph(cuda):
     assert r["nearest_bound"] in ("hbm_compulsory", "l2_gather", "hbm_measured_traffic")
     c5 = out["c5_strong"]
     assert c5["scaling"] == "strong" and c5["check"]["ok"] is True and c5["ms_per_step"] > 0 and c5["n_gpus"] == 1
+    assert set(c5["dim_sweep"]) == {"16", "64", "128"} and all(v["check_ok"] and v["ms_per_step"] > 0 for v in c5["dim_sweep"].values())
     assert out["reference_gpu"].get("best", {}).get("cost") in (8, 32) or "unavailable" in out["reference_gpu"]
+
+
+@pytest.mark.gpu
+def test_profiling_flags_slab_and_walk(cuda):
+    """--slab R/N: one rank's share of an N-GPU weak-scaling run alone on this GPU; --walk 1: a warp per unit."""
+    out = _run("--steps", "3", "--warmup", "3", "--scale", "14", "--dim", "16", "--slab", "1/2", "--walk", "1", "--no-c5", "--skip-baselines",
+               "--no-probe", "--e2e-steps", "1")
+    assert out["config"]["workload"].endswith("_slab1of2") and out["config"]["nodes"] == 1 << 15
+    assert out["config"]["groups_per_unit"] == 8 and out["check"]["ok"] is True and out["e2e"]["check"]["ok"] is True
+    assert "c5_strong" not in out and "cpu_baseline" not in out and "l2_frac" not in out["roofline"]
