@@ -216,12 +216,17 @@ def check_product(rp, col, val, B, C_out, half, seed=0, n_random=4096, n_long=32
             "against": "fp64 product of the sampled rows (torch gather + index_add), after the timed region"}
 
 
-def gather_rates(mps, dev, row_bytes):
-    """The two rates the multiply's gather can be held against (mps_gather_probe): random whole rows of `row_bytes`
-    out of a 32 MB table (L2 -> SM) and out of a 4 GiB table (HBM, ~3 % L2 hits), 128-bit loads, GB/s."""
+def gather_rates(mps, dev, row_bytes, B=None, col=None):
+    """The rates the multiply's gather can be held against (mps_gather_probe): random whole rows of `row_bytes`
+    out of a 32 MB table (L2 -> SM) and out of a 4 GiB table (HBM, ~3 % L2 hits), 128-bit loads, GB/s; and, when the
+    row width allows, the multiply's own stream - the rows of B that col_idx names, in its order - fetched by a kernel
+    that does nothing else (mps_gather_probe_stream)."""
     import torch
+    exact = row_bytes in (32, 64, 128, 256, 512)
     row_bytes = min(512, max(32, 1 << (int(row_bytes) - 1).bit_length()))
     out = {}
+    if exact and B is not None and col is not None and col.numel() > 0:
+        out["stream"] = round(max(mps.gather_probe_stream(B, row_bytes, col) for _ in range(3)), 1)
     for name, size in (("l2", 32 << 20), ("hbm", 4 << 30)):
         table = torch.zeros(size, dtype=torch.uint8, device=dev)
         best = 0.0
@@ -339,6 +344,10 @@ def roofline_of(mps, args, w, n_slab, nnz_slab, dt, tile_ms_avg, ms_step, rates,
         r["probe"] = f"mps_gather_probe, random rows of {probe_row_bytes} B, 128-bit loads: 32 MB table (L2) and 4 GiB table (HBM)"
         r["l2_frac"] = round(gathered / t / 1e9 / rates["l2"], 4)
         fracs["l2_gather"] = r["l2_frac"]
+        if "stream" in rates:
+            # the same rows in the same order, fetched by a kernel that only fetches: what this index stream allows
+            r["stream_gather_gbs"] = rates["stream"]
+            r["stream_frac"] = round(gathered / t / 1e9 / rates["stream"], 4)
     tpath = os.path.join(ROOT, "profiles", "traffic.json")
     if os.path.exists(tpath):
         try:
@@ -553,7 +562,7 @@ def run_ours(args):
 
     # ---- roofline of the dominant kernel (the tile kernel), this rank's slab ----
     tile_ms_avg, tile_launches = kernel_pass(plan, w, C_out, args.steps)
-    rates, probe_row = (None, 0) if args.no_probe else gather_rates(mps, dev, args.dim * (2 if w["half"] else 4))
+    rates, probe_row = (None, 0) if args.no_probe else gather_rates(mps, dev, args.dim * (2 if w["half"] else 4), w["B"], w["col"])
     roofline = roofline_of(mps, args, w, n_slab, nnz_slab, dt, tile_ms_avg, ms_step, rates, probe_row, workload_name(args, world))
     roofline["kernel_pass_launches"] = tile_launches
 

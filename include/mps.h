@@ -207,7 +207,7 @@ MPS_API int mps_plan_info(const mps_plan *plan, int64_t what[16]);
 
 /* The layout behind those facts in merge items (no reference counterpart): what[0]=merge items per unit
  * (one lane group's walk), what[1]=units per tile, what[2]=merge items per tile, what[3]=n_tiles,
- * what[4]=units per reference chunk (1 unless `cost` asks for chunks longer than a tile can stage: then a
+ * what[4]=units per reference chunk (1 unless `cost` asks for chunks longer than a tile should stage: then a
  * unit is the what[4]-th part of a chunk and what[0] = ceil(items_per_chunk / what[4]); any `cost` the
  * reference's command line accepts is therefore accepted here), what[5]=shared bytes per block,
  * what[6]=column slabs, what[7]=1 when the tile kernel performs the cross-tile fix-up itself,
@@ -249,6 +249,16 @@ MPS_API int64_t mps_algorithmic_bytes(int32_t n_rows, int32_t nnz, int32_t dim, 
  * Allocates nothing but two events; blocking. */
 MPS_API int mps_gather_probe(const void *d_table, int64_t table_rows, int32_t row_bytes, int64_t gathers, void *d_sink,
                      int64_t sink_bytes, void *stream, float *ms, int64_t *gathered_bytes);
+
+/* The same fetch loop over the caller's own row numbers (no reference counterpart): d_index holds n_index row numbers
+ * in [0, table_rows) - typically the multiply's col_idx with d_table = B - and every group of threads fetches a
+ * contiguous run of them in order, as a lane group of the multiply walks its unit.  What this launch reaches is the
+ * rate at which this GPU can deliver THIS stream of rows (its reuse, its L2 hit rate, its DRAM misses) to a kernel that
+ * only fetches; the multiply's gathered bytes per second divided by it says how much the multiply's own work (staging,
+ * fused multiply-adds, row ends) costs on top.  The indices are not checked. */
+MPS_API int mps_gather_probe_stream(const void *d_table, int64_t table_rows, int32_t row_bytes, const int32_t *d_index,
+                            int64_t n_index, void *d_sink, int64_t sink_bytes, void *stream, float *ms,
+                            int64_t *gathered_bytes);
 
 /* ------------------------------------------------------------------ host-buffer call ----- */
 

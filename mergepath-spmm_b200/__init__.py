@@ -29,7 +29,7 @@ try:
 except Exception:  # pragma: no cover
     torch = None
 
-__all__ = ["Plan", "MultiGpu", "layout_query", "coo_to_csr", "coo_to_csr_device", "npz_to_csr", "spmm", "spmm_host", "spmm_host_resident_b", "gather_probe", "partition_host", "schedule_host", "load_csr_rect", "spmm_noalloc", "partition_device", "schedule_device", "chunk_count", "load_csr", "save_csr",
+__all__ = ["Plan", "MultiGpu", "layout_query", "coo_to_csr", "coo_to_csr_device", "npz_to_csr", "spmm", "spmm_host", "spmm_host_resident_b", "gather_probe", "gather_probe_stream", "partition_host", "schedule_host", "load_csr_rect", "spmm_noalloc", "partition_device", "schedule_device", "chunk_count", "load_csr", "save_csr",
            "save_csr_bin", "load_csr_bin", "slab_bounds", "slab_rebase", "algorithmic_bytes", "F32", "F16", "MpsError"]
 
 
@@ -242,6 +242,20 @@ def spmm_host_resident_b(row_ptr, col_idx, val, d_B, out, cost: int = 8, threads
                                                        F16 if is_half else F32, cost, threads_per_warp, host_ptr(row_ptr), host_ptr(col_idx),
                                                        host_ptr(val), _dev_ptr(d_B), _stream_ptr(stream), host_ptr(out)))
     return out
+
+
+def gather_probe_stream(table, row_bytes: int, index, stream=None) -> float:
+    """GB/s at which this GPU delivers the rows of `table` named by `index` (int32 CUDA tensor, e.g. the multiply's col_idx
+    with table = B) to a kernel that only fetches them, each group of threads taking a contiguous run in order
+    (mps_gather_probe_stream)."""
+    _need_cuda(table, index)
+    rows = table.numel() * table.element_size() // row_bytes
+    sink = torch.empty(1 << 20, dtype=torch.int32, device=table.device)
+    ms, nbytes = C.c_float(), C.c_int64()
+    with torch.cuda.device(table.device):
+        capi.check(capi.lib().mps_gather_probe_stream(_dev_ptr(table), rows, row_bytes, _dev_ptr(index), index.numel(), _dev_ptr(sink), sink.numel() * 4,
+                                                      _stream_ptr(stream), C.byref(ms), C.byref(nbytes)))
+    return nbytes.value / (ms.value * 1e-3) / 1e9
 
 
 def gather_probe(table, row_bytes: int, gathers: int, stream=None) -> float:

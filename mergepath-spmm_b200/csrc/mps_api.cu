@@ -102,7 +102,10 @@ static int pow2_at_least(int v) {
     return p;
 }
 
-static const int kSmemTargetPer256 = 64 * 1024;   // three tile blocks per SM, which the registers allow anyway
+// Shared memory a tile may use.  The resident blocks of an SM (768 threads' worth: the registers allow no more) must fit a
+// 196 KiB shared-memory carve-out, each with the 1 KiB the runtime reserves per block: one step more (228 KiB) leaves
+// 28 KiB of L1, and the gathers in flight then wait for L1 lines - measured 1.9 ms against 1.2 ms per multiply at dim 64.
+static const int kCarveoutBytes = 196 * 1024;
 static const int kVeryLongFused = 8192;       // chain length (tiles) above which even the fused form hands a row to a block of fixup_kernel
 static const int kFuseMaxTiles = 2048;       // up to here a second launch costs more than the fence the fused fix-up needs
 static const int kTilesPerSm = 6;            // smaller tiles rather than idle SMs on small problems
@@ -111,7 +114,6 @@ static const int kTileItemsPerThread = 17;          // merge items per tile the 
 static const int kSmemLimit = 200 * 1024;
 
 static const int kWalkWarpMaxLanes = 0;  // lanes per group up to which a whole warp walks a unit by default (0: never)
-static const int kSmemSplitAbove = 48 * 1024;  // a whole-chunk tile beyond this is cut into sub-chunk units instead
 
 static int plan_layout(mps_plan *p) {
     const int elem = p->dtype == MPS_F16 ? 2 : 4;
@@ -124,7 +126,7 @@ static int plan_layout(mps_plan *p) {
     if (!can_spread) p->walk = 0;
     const int groups = p->walk ? 32 / p->gl : 1;          // lane groups that share a unit
     const int gpc = p->block / (p->gl * groups);          // units per tile
-    const int kSmemTarget = kSmemTargetPer256 * p->block / 256, kTileItems = kTileItemsPerThread * p->block;
+    const int kSmemTarget = kCarveoutBytes / (kWarpsPerSm * 32 / p->block) - 1024 - 64, kTileItems = kTileItemsPerThread * p->block;
     if (!p->user_unroll) p->unroll = 8;
     if (p->vec == 1) p->unroll = 4;
     auto smem_of = [&](long long unit) -> long long {  // shared memory of a tile whose units hold `unit` merge items (64-bit: no wrap)
@@ -154,10 +156,15 @@ static int plan_layout(mps_plan *p) {
         while (cpu > 1 && smem_of((long long)cpu * p->ipt) > kSmemTarget) --cpu;
         p->cpu = cpu;
         unit = (long long)cpu * p->ipt;
-        if (cpu == 1 && smem_of(unit) > (kSmemTarget > kSmemSplitAbove ? kSmemTarget : kSmemSplitAbove)) {
-            // `cost` asks for chunks longer than a tile can stage: a unit becomes the k-th part of a chunk (the merge
+        const long long unit_cap = (long long)groups * kUnitItems;  // the same "keep each walk short" as above
+        if (cpu == 1 && (smem_of(unit) > kSmemTarget || unit > unit_cap)) {
+            // `cost` asks for chunks longer than a unit should be: a unit becomes the k-th part of a chunk (the merge
             // path is cut at multiples of ceil(ipt / k) instead of ipt; the partition search takes any step)
-            long long k = 2;
+            long long goal = items / gpc;  // what a unit of the automatic layout holds: at most the cap, less on small problems
+            if (goal > unit_cap) goal = unit_cap;
+            if (goal < 1) goal = 1;
+            long long k = (p->ipt + goal - 1) / goal;
+            if (k < 2) k = 2;
             while ((p->ipt + k - 1) / k > 1 && smem_of((p->ipt + k - 1) / k) > kSmemTarget) ++k;
             unit = (p->ipt + k - 1) / k;
             p->sub_chunk = (int)k;

@@ -551,6 +551,9 @@ def test_gather_probe_reports_a_plausible_rate(mps, cuda):
     assert 1000.0 < rate < 100000.0, rate                              # GB/s
     with pytest.raises(mps.MpsError):
         mps.gather_probe(small, 100, 1 << 20)
+    idx = torch.randint(0, small.numel() // 256, (1 << 22,), dtype=torch.int32, device=cuda)
+    rate = mps.gather_probe_stream(small, 256, idx)
+    assert 1000.0 < rate < 100000.0, rate
 
 
 # ------------------------------------------------------------------ slabs
