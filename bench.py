@@ -348,6 +348,7 @@ def roofline_of(mps, args, w, n_slab, nnz_slab, dt, tile_ms_avg, ms_step, rates,
             # the same rows in the same order, fetched by a kernel that only fetches: what this index stream allows
             r["stream_gather_gbs"] = rates["stream"]
             r["stream_frac"] = round(gathered / t / 1e9 / rates["stream"], 4)
+            fracs["own_stream_gather"] = r["stream_frac"]
     tpath = os.path.join(ROOT, "profiles", "traffic.json")
     if os.path.exists(tpath):
         try:

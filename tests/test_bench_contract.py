@@ -43,7 +43,8 @@ def test_default_arm_line_on_a_small_graph(cuda):
     assert out["e2e"]["check"]["ok"] is True
     r = out["roofline"]
     assert 0 < r["compulsory_frac"] < 1.5 and r["l2_peak_gbs"] > r["hbm_gather_gbs"] > 0 and 0 < r["l2_frac"] < 1.5
-    assert r["nearest_bound"] in ("hbm_compulsory", "l2_gather", "hbm_measured_traffic")
+    assert r["nearest_bound"] in ("hbm_compulsory", "l2_gather", "hbm_measured_traffic", "own_stream_gather")
+    assert 0 < r["stream_frac"] < 1.5 and r["stream_gather_gbs"] > 0
     c5 = out["c5_strong"]
     assert c5["scaling"] == "strong" and c5["check"]["ok"] is True and c5["ms_per_step"] > 0 and c5["n_gpus"] == 1
     assert set(c5["dim_sweep"]) == {"16", "64", "128"} and all(v["check_ok"] and v["ms_per_step"] > 0 for v in c5["dim_sweep"].values())
