@@ -352,6 +352,8 @@ static int spmm_launch(mps_plan *p, const int32_t *d_row_ptr, const int32_t *d_c
     tp.total = (long long)p->n_rows + 1 + p->nnz;
     tp.n_rows = p->n_rows; tp.nnz = p->nnz; tp.dim = p->dim;
     tp.unit_items = p->unit_items; tp.tile_items = p->tile_items; tp.n_tiles = p->n_tiles;
+    // a product without stored values (unit values, or the scaled form) stages no value window: a third less shared memory
+    tp.smem_bytes = d_val ? p->smem_bytes : TileSmem(p->tile_items / p->unit_items, p->tile_items, p->slab_cols, 0).bytes;
     const bool aligned16 = !((uintptr_t)d_row_ptr % 16) && !((uintptr_t)d_col_idx % 16) && !((uintptr_t)d_val % 16);
     tp.bulk = (p->bulk && aligned16) ? 1 : 0;
     cudaStream_t st = (cudaStream_t)stream;

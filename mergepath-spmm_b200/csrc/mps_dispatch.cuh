@@ -20,9 +20,9 @@ namespace mps {
 template <typename T, int VEC, int GL, int U, int BLOCK, bool SCALED>
 static int launch_tile_k(const mps_plan *p, const TileParams &tp, cudaStream_t st) {
     auto kern = spmm_tile_kernel<T, VEC, GL, U, BLOCK, SCALED>;
-    if (p->smem_bytes > 48 * 1024) MPS_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, p->smem_bytes));
+    if (tp.smem_bytes > 48 * 1024) MPS_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, tp.smem_bytes));
     dim3 grid((unsigned)p->n_tiles, (unsigned)p->n_col_slabs);
-    kern<<<grid, BLOCK, p->smem_bytes, st>>>(tp);
+    kern<<<grid, BLOCK, tp.smem_bytes, st>>>(tp);
     MPS_CUDA(cudaGetLastError());
     return MPS_OK;
 }
@@ -68,9 +68,9 @@ static int launch_tile_gl(const mps_plan *p, const TileParams &tp, cudaStream_t 
 template <typename T, int VEC, int GL>
 static int launch_tile_warp_k(const mps_plan *p, const TileParams &tp, cudaStream_t st) {
     auto kern = spmm_tile_kernel<T, VEC, GL, 8, 64, false, true>;
-    if (p->smem_bytes > 48 * 1024) MPS_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, p->smem_bytes));
+    if (tp.smem_bytes > 48 * 1024) MPS_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, tp.smem_bytes));
     dim3 grid((unsigned)p->n_tiles, (unsigned)p->n_col_slabs);
-    kern<<<grid, 64, p->smem_bytes, st>>>(tp);
+    kern<<<grid, 64, tp.smem_bytes, st>>>(tp);
     MPS_CUDA(cudaGetLastError());
     return MPS_OK;
 }

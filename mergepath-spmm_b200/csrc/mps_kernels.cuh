@@ -54,6 +54,7 @@ struct TileParams {
     long long total;  // N + 1 + nnz
     int n_rows, nnz, dim;
     int unit_items, tile_items, n_tiles;  // merge items per unit, per tile (= units per tile x unit_items)
+    int smem_bytes;                       // dynamic shared memory of this launch (no value window when val is nullptr)
     int bulk;  // 1: bulk async staging (needs 16-byte aligned rp/col/val)
 };
 
@@ -391,7 +392,7 @@ __global__ void __launch_bounds__(BLOCK, kWarpsPerSm * 32 / BLOCK) spmm_tile_ker
     constexpr int GPC = kBlock / UL;       // units per block
     constexpr int SLAB = GL * VEC;         // columns covered by one block
     extern __shared__ __align__(128) unsigned char smem[];
-    const TileSmem L(GPC, p.tile_items, SLAB, (int)sizeof(T));
+    const TileSmem L(GPC, p.tile_items, SLAB, p.val != nullptr ? (int)sizeof(T) : 0);
     uint64_t *s_bar = reinterpret_cast<uint64_t *>(smem);
     int *s_fx = reinterpret_cast<int *>(smem + L.off_fx);
     int *s_fy = reinterpret_cast<int *>(smem + L.off_fy);
