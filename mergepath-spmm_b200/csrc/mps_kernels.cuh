@@ -6,7 +6,8 @@
 //   tile   = `nch` consecutive chunks, one thread block.  Its two boundary coordinates come from
 //            the plan (searched once per row_ptr by partition_kernel); the block stages the tile's
 //            row_ptr / col_idx / val windows into shared memory with bulk async copies that
-//            complete on an mbarrier.
+//            complete on an mbarrier (no val window without stored values; a tile with more row ends
+//            than the row_ptr window holds reads row_ptr from global memory).
 //   unit   = `cpu` consecutive chunks of the tile, walked in order by one group of GL lanes; the
 //            unit boundaries (a subset of the chunk diagonals) are re-searched in shared memory.
 //            A lane owns VEC adjacent columns and gathers its part of every B row with one 128-bit
@@ -283,12 +284,19 @@ __device__ __forceinline__ void gmem_put_f32(float *dst, const float (&v)[VEC]) 
 struct TileSmem {
     int off_fx, off_fy, off_rp, off_col, off_val, off_carry, off_head, bytes;
     __host__ __device__ static int up16(int v) { return (v + 15) & ~15; }
+    // row_ptr entries the window holds: a quarter of the tile's merge items (rows of three non-zeros on average still
+    // fit).  A tile with more markers than that reads row_ptr from global memory instead (shorter rows are rare, and
+    // a row end touches row_ptr once); the shared memory this saves goes to the L1, which holds the gathers in flight.
+    __host__ __device__ static int rp_entries(int tile_items) {
+        const int q = tile_items / 4 < 64 ? 64 : tile_items / 4;
+        return (q < tile_items ? q : tile_items) + 2 * kAlign + 8;
+    }
     __host__ __device__ TileSmem(int n_units, int tile_items, int slab_cols, int elem_bytes) {
         const int win = tile_items + 2 * kAlign + 8;  // window plus alignment slack on both sides
         int o = 16;                                   // mbarrier
         off_fx = o; o = up16(o + 4 * (n_units + 1));
         off_fy = o; o = up16(o + 4 * (n_units + 1));
-        off_rp = o; o = up16(o + 4 * win);
+        off_rp = o; o = up16(o + 4 * rp_entries(tile_items));
         off_col = o; o = up16(o + 4 * win);
         off_val = o; o = up16(o + elem_bytes * win);
         off_carry = o; o = up16(o + 4 * n_units * slab_cols);
@@ -424,12 +432,13 @@ __global__ void __launch_bounds__(BLOCK, kWarpsPerSm * 32 / BLOCK) spmm_tile_ker
     const int y_base = Y0 & ~(kAlign - 1);
 
     // ---- stage the tile's windows ----
+    const bool rp_staged = X1 - rp_base + kAlign <= TileSmem::rp_entries(p.tile_items);  // block-uniform (the copy rounds its end up)
     bool staged = false;
     if (p.bulk) {
         const uint32_t bar = smem_u32(s_bar);
         if (tid == 0) mbar_init(bar, 1);
         __syncthreads();
-        const long long rp_be = bulk_end_of(rp_base, X1, (long long)p.n_rows + 1);
+        const long long rp_be = rp_staged ? bulk_end_of(rp_base, X1, (long long)p.n_rows + 1) : (long long)rp_base;
         const long long y_be = bulk_end_of(y_base, Y1, p.nnz);
         if (tid == 0) {
             const uint32_t n_rp = (uint32_t)(rp_be - rp_base) * 4u;
@@ -441,7 +450,7 @@ __global__ void __launch_bounds__(BLOCK, kWarpsPerSm * 32 / BLOCK) spmm_tile_ker
             if (n_col) bulk_g2s(smem_u32(s_col), p.col + y_base, n_col, bar, once);
             if (n_val) bulk_g2s(smem_u32(s_val), static_cast<const T *>(p.val) + y_base, n_val, bar, once);
         }
-        stage_ragged<int>(s_rp, p.rp, rp_base, rp_be, X1, tid);
+        if (rp_staged) stage_ragged<int>(s_rp, p.rp, rp_base, rp_be, X1, tid);
         stage_ragged<int>(s_col, p.col, y_base, y_be, Y1, tid);
         if (has_val) stage_ragged<T>(s_val, static_cast<const T *>(p.val), y_base, y_be, Y1, tid);
         // the first warp watches the mbarrier; the others park at the block barrier below
@@ -457,13 +466,14 @@ __global__ void __launch_bounds__(BLOCK, kWarpsPerSm * 32 / BLOCK) spmm_tile_ker
         staged = !__syncthreads_or(!ok);
     }
     if (!staged) {
-        for (int i = rp_base + tid; i < X1; i += kBlock) s_rp[i - rp_base] = p.rp[i];
+        if (rp_staged)
+            for (int i = rp_base + tid; i < X1; i += kBlock) s_rp[i - rp_base] = p.rp[i];
         for (int i = y_base + tid; i < Y1; i += kBlock) s_col[i - y_base] = p.col[i];
         if (has_val)
             for (int i = y_base + tid; i < Y1; i += kBlock) s_val[i - y_base] = static_cast<const T *>(p.val)[i];
         __syncthreads();
     }
-    const int *__restrict__ w_rp = s_rp - rp_base;   // indexable by global row_ptr index
+    const int *w_rp = rp_staged ? s_rp - rp_base : p.rp;  // indexable by global row_ptr index (shared window, or the array itself)
     const int *__restrict__ w_col = s_col - y_base;  // indexable by global non-zero index
     const T *__restrict__ w_val = s_val - y_base;
 

@@ -172,6 +172,22 @@ def test_edge_case_graphs(mps, orc, cuda, name):
             _check(orc, rp, col, val, B, got, info, cost, 1e-5)
 
 
+@pytest.mark.parametrize("dim,half,walk", [(64, False, None), (16, False, None), (128, True, None), (20, False, None), (16, False, 1)])
+def test_tiles_with_more_row_ends_than_the_row_ptr_window_holds(mps, orc, cuda, dim, half, walk):
+    """The shared-memory window for row_ptr holds a quarter of a tile's merge items; tiles of very short and empty rows
+    have more markers than that and read row_ptr from global memory instead.  Same sums either way."""
+    rng = np.random.default_rng(17)
+    lens = rng.integers(0, 3, 300_000)
+    lens[1000:1200] = 0                      # a run of empty rows
+    lens[50_000] = 40_000                    # and one long row among them
+    rp, col = cases.from_lengths(lens, 200_000, 23)
+    val = rng.uniform(-1, 1, len(col)).astype(np.float16 if half else np.float32)
+    B = rng.uniform(-1, 1, (200_000, dim)).astype(np.float16 if half else np.float32)
+    got, info = _run(mps, cuda, rp, col, val, B, 16, walk=walk)
+    assert info["tile_items"] >= 400 and (lens <= 2).mean() > 0.99   # markers per tile ~ tile_items / 2 > tile_items / 4
+    _check(orc, rp, col, val, B, got, info, 16, 1e-2 if half else 1e-5)
+
+
 def test_long_rows_take_the_strand_order(mps, orc, cuda):
     """A row spanning more than long_chain tiles is summed in 16 interleaved strands, still by the tile
     block whose contribution arrives last: one kernel per SpMM."""
