@@ -3,13 +3,14 @@
 // Work decomposition (all diagonals are the reference's: chunk c covers merge items
 // [ipt*c, ipt*(c+1)) of the merge of row_ptr[0..N] with 0..nnz-1, src/MergePathSpMM.cu:327-334):
 //
-//   tile   = `nch` consecutive chunks, one thread block.  Its two boundary coordinates come from
+//   tile   = `tile_items` consecutive merge items (a whole number of units), one thread block.  Its two boundary coordinates come from
 //            the plan (searched once per row_ptr by partition_kernel); the block stages the tile's
 //            row_ptr / col_idx / val windows into shared memory with bulk async copies that
 //            complete on an mbarrier (no val window without stored values; a tile with more row ends
 //            than the row_ptr window holds reads row_ptr from global memory).
-//   unit   = `cpu` consecutive chunks of the tile, walked in order by one group of GL lanes; the
-//            unit boundaries (a subset of the chunk diagonals) are re-searched in shared memory.
+//   unit   = `unit_items` consecutive merge items of the tile - a run of whole chunks, or the k-th part of one chunk
+//            when the cost asks for chunks longer than a unit should be - walked in order by one group of GL
+//            lanes (or by a whole warp, SPREAD); the unit boundaries are re-searched in the staged row_ptr window.
 //            A lane owns VEC adjacent columns and gathers its part of every B row with one 128-bit
 //            load, U loads in flight before the first fused multiply-add; the accumulator stays in
 //            registers across the chunk boundaries inside the unit.  Rows that end inside the unit
