@@ -913,7 +913,9 @@ def run_reference_cpu(args):
         "impl": "reference", "metric": "SpMM GFLOP/s (2*nnz*dim/t)", "value": v, "unit": "GFLOP/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": max(args.warmup, 1), "ms_per_step": round(s * 1e3, 3), "higher_is_better": True,
         "scaling": "strong" if args.strong else "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": workload_name(args, max(world, args.gpus)), "nodes": n, "nnz": nnz, "dim": args.dim, "values": "gcn",
+        "config": {"workload": workload_name(args, max(world, args.gpus)), "nodes": n, "nnz": nnz, "dim": args.dim, "cost": args.cost or DEFAULT_COST,
+                   "threads_per_warp": args.tpw, "values": "gcn", "l2": "inputs larger than L2 (B and A each > 126 MB)",
+                   "parallelism": f"{cores} host threads, rows split at equal non-zero counts",
                    "fp16_note": "fp16 storage is multiplied as fp32 on the host" if half else None},
         "cpu_baseline": {"value": v, "unit": "GFLOP/s", "cores": int(cores), "kind": "port", "sample": sample},
         "e2e": {"value": v, "unit": "GFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
