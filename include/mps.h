@@ -159,7 +159,7 @@ MPS_API void mps_plan_destroy(mps_plan *plan);
 
 /* Optional tuning before mps_plan_partition: chunks per unit (0 = automatic; a unit is the run of
  * consecutive chunks one lane group walks with its accumulator kept in registers, a tile holds
- * block_threads/lanes_per_chunk units), gather unroll (4 or 8, 0 = automatic), staging through
+ * block_threads/lanes_per_chunk units), gathers in flight per thread (4, 8 or 10; 0 = automatic: 10, the most that fits the registers of 12 resident blocks), staging through
  * bulk async copies (1, default) or plain loads (0), threads per tile block (64, 128, 256; 0 =
  * automatic: 64), cross-tile fix-up inside the tile kernel (1) or as a kernel of its own (0; -1 =
  * automatic: inside for up to 2048 tiles, where a second launch costs more than it saves). */

@@ -122,12 +122,14 @@ static int plan_layout(mps_plan *p) {
     // a warp per unit exists for full-width lanes, 64-thread blocks and batches of eight; it pays where a warp holds
     // several lane groups (see kWalkWarpMaxLanes)
     const bool can_spread = p->vec > 1 && p->gl < 32 && p->block == 64 && (!p->user_unroll || p->unroll == 8);
+    // ten gathers in flight per thread: the most that 80 registers hold (12 resident blocks); 12 and 16 lose warps
     if (!p->user_walk) p->walk = (can_spread && p->gl <= kWalkWarpMaxLanes) ? 1 : 0;
     if (!can_spread) p->walk = 0;
     const int groups = p->walk ? 32 / p->gl : 1;          // lane groups that share a unit
     const int gpc = p->block / (p->gl * groups);          // units per tile
     const int kSmemTarget = kCarveoutBytes / (kWarpsPerSm * 32 / p->block) - 1024 - 64, kTileItems = kTileItemsPerThread * p->block;
-    if (!p->user_unroll) p->unroll = 8;
+    if (!p->user_unroll) p->unroll = 10;
+    if (p->walk) p->unroll = 8;  // the warp-per-unit kernel exists for batches of eight
     if (p->vec == 1) p->unroll = 4;
     auto smem_of = [&](long long unit) -> long long {  // shared memory of a tile whose units hold `unit` merge items (64-bit: no wrap)
         const long long items = (long long)gpc * unit;
@@ -271,7 +273,7 @@ extern "C" void mps_plan_destroy(mps_plan *plan) {
 extern "C" int mps_plan_tune(mps_plan *p, int32_t chunks_per_unit, int32_t unroll, int32_t bulk_staging, int32_t block_threads,
                              int32_t fused_fixup) {
     if (!p) return fail(MPS_ERR_ARG, "mps_plan_tune: plan is NULL");
-    if (unroll != 0 && unroll != 4 && unroll != 8) return fail(MPS_ERR_ARG, "mps_plan_tune: unroll must be 0, 4 or 8");
+    if (unroll != 0 && unroll != 4 && unroll != 8 && unroll != 10) return fail(MPS_ERR_ARG, "mps_plan_tune: unroll must be 0, 4, 8 or 10");
     if (chunks_per_unit < 0 || chunks_per_unit > 4096) return fail(MPS_ERR_ARG, "mps_plan_tune: chunks_per_unit out of range");
     if (block_threads != 0 && block_threads != 64 && block_threads != 128 && block_threads != 256)
         return fail(MPS_ERR_ARG, "mps_plan_tune: block_threads must be 0, 64, 128 or 256");

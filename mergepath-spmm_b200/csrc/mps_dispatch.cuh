@@ -48,6 +48,7 @@ static int launch_tile_b(const mps_plan *p, const TileParams &tp, cudaStream_t s
 
 template <typename T, int VEC, int GL, bool SCALED>
 static int launch_tile_u(const mps_plan *p, const TileParams &tp, cudaStream_t st) {
+    if (p->unroll == 10) return launch_tile_b<T, VEC, GL, 10, SCALED>(p, tp, st);
     if (p->unroll == 8) return launch_tile_b<T, VEC, GL, 8, SCALED>(p, tp, st);
     return launch_tile_b<T, VEC, GL, 4, SCALED>(p, tp, st);
 }

@@ -12,7 +12,7 @@
 //            when the cost asks for chunks longer than a unit should be - walked in order by one group of GL
 //            lanes (or by a whole warp, SPREAD); the unit boundaries are re-searched in the staged row_ptr window.
 //            A lane owns VEC adjacent columns and gathers its part of every B row with one 128-bit
-//            load, U loads in flight before the first fused multiply-add; the accumulator stays in
+//            load, U (10) loads in flight before the first fused multiply-add; the accumulator stays in
 //            registers across the chunk boundaries inside the unit.  Rows that end inside the unit
 //            and began there are stored directly; a row that began earlier leaves its share as the
 //            unit's "head", what is left at the unit's end is its "carry" (shared memory, fp32).
@@ -29,6 +29,8 @@
 namespace mps {
 
 constexpr int kWarpsPerSm = 24;      // resident warps per SM the register allocation is held to (768 threads)
+// ... for a kernel with U gathers in flight per thread: deeper batches hold more registers and trade resident warps for them
+constexpr int warps_per_sm(int u) { return u <= 8 ? kWarpsPerSm : (u <= 10 ? 22 : 20); }
 constexpr int kMaxBlock = 256;       // largest tile block (threads); 64 and 128 are the other sizes
 constexpr int kStrands = 16;         // interleaved partial sums of the long-row fix-up
 constexpr int kAlign = 8;            // staging windows start on multiples of 8 elements (>= 16 bytes)
@@ -394,7 +396,7 @@ __device__ __forceinline__ void block_fixup(const TileParams &p, int e, int chai
 // neighbouring groups would end their rows at different places - which is what costs at small dim, where a warp holds
 // eight groups.
 template <typename T, int VEC, int GL, int U, int BLOCK, bool SCALED, bool SPREAD = false>
-__global__ void __launch_bounds__(BLOCK, kWarpsPerSm * 32 / BLOCK) spmm_tile_kernel(const TileParams p) {
+__global__ void __launch_bounds__(BLOCK, warps_per_sm(U) * 32 / BLOCK) spmm_tile_kernel(const TileParams p) {
     constexpr int kBlock = BLOCK;
     constexpr int UL = SPREAD ? 32 : GL;   // lanes that walk one unit
     constexpr int G = UL / GL;             // lane groups per unit (1 unless SPREAD)
