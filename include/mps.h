@@ -272,7 +272,9 @@ MPS_API int mps_gather_probe_stream(const void *d_table, int64_t table_rows, int
  * row_ptr[n_rows] == nnz, every col_idx inside [0, n_cols) - else MPS_ERR_ARG naming the position.  row_ptr
  * is checked on the host; col_idx where each slab of it lands on the device, ahead of the multiply on the
  * same stream (an index outside B is replaced by 0 in the workspace copy before any kernel gathers by it,
- * and C is then meaningless), so the check costs the uploads nothing.  A bad index is reported in preference
+ * and C is then meaningless), so the check costs the uploads nothing.  The uploads of row_ptr and B are queued
+ * before the host check (nothing on the device reads row_ptr until the host has passed it); a call that fails
+ * the check returns once they have drained.  A bad index is reported in preference
  * to any other failure of the call, also on a machine without a device (there the host scans col_idx). */
 MPS_API int mps_spmm_host(int32_t n_rows, int32_t n_cols, int32_t nnz, int32_t dim, int dtype, int32_t cost,
                   int32_t threads_per_warp, const int32_t *row_ptr, const int32_t *col_idx,
