@@ -422,6 +422,27 @@ def e2e_through_host_call(mps, args, w, world, rank, dev, cost, dt, n_slab, nnz_
     d2h = h_C.numel() * h_C.element_size()
     chk = check_product(d["rp"], d["col"], d["val"], w["B"], h_C.to(dev), w["half"], seed=100 + rank)   # the C that came back to the host
     ok = bool(min_over_ranks(1.0 if chk["ok"] else 0.0, world) > 0.5)
+    scaled = None
+    if world == 1 and not w["half"] and not args.slab:
+        # the same GCN product with the two factor vectors (degree^-1/2) instead of a value per non-zero - the shape of
+        # the reference program, which uploads one number per node and forms the values in the kernel
+        deg = (d["rp"][1:] - d["rp"][:-1]).to(torch.float64)
+        h_s = (1.0 / torch.sqrt(deg)).to(torch.float32).cpu().pin_memory()
+        h_C2 = torch.full_like(h_C, float("nan")).pin_memory()
+
+        def call_scaled():
+            mps.spmm_host_scaled(h["rp"], h["col"], h_s, h_s, h["B"], out=h_C2, cost=cost, threads_per_warp=args.tpw)
+        call_scaled()
+        t1 = time.perf_counter()
+        for _ in range(steps):
+            call_scaled()
+        s_s = (time.perf_counter() - t1) / steps
+        chk2 = check_product(d["rp"], d["col"], d["val"], w["B"], h_C2.to(dev), False, seed=200)
+        scaled = {"call": "mps_spmm_host_scaled (row and column factors instead of a value per non-zero)", "ms_per_step": round(s_s * 1e3, 3),
+                  "value": round(2.0 * w["nnz"] * args.dim / s_s / 1e9, 2), "unit": "GFLOP/s",
+                  "h2d_bytes_per_step": int(sum(h[k].numel() * h[k].element_size() for k in ("rp", "col", "B")) + 2 * h_s.numel() * 4),
+                  "d2h_bytes_per_step": int(d2h), "check_ok": bool(chk2["ok"])}
+        del h_C2
     mps.capi.lib().mps_host_workspace_release()
     host = {k: (h[k].numpy() if h[k] is not None else None) for k in h} if world == 1 else None
     flop_nnz = nnz_slab if (args.slab and world == 1) else w["nnz"]
@@ -429,7 +450,8 @@ def e2e_through_host_call(mps, args, w, world, rank, dev, cost, dt, n_slab, nnz_
             "d2h_bytes_per_step": int(sum_over_ranks(d2h, world)), "ms_per_step": round(e2e_s * 1e3, 3), "steps": steps,
             "b_replication": "each rank uploads 1/N of B, NCCL all-gather over NVLink" if world > 1 else "one upload", "slabs": slabs,
             "per_rank_ms": all_ranks(e2e_rank_s * 1e3, world),
-            "check": {"ok": ok, "max_scaled_err": max_over_ranks(chk["max_scaled_err"], world), "rows": int(sum_over_ranks(chk["rows"], world))}}, host
+            "check": {"ok": ok, "max_scaled_err": max_over_ranks(chk["max_scaled_err"], world), "rows": int(sum_over_ranks(chk["rows"], world))},
+            **({"scaled_call": scaled} if scaled else {})}, host
 
 
 def c5_strong(mps, args, world, rank, dev):

@@ -290,6 +290,16 @@ MPS_API int mps_spmm_host(int32_t n_rows, int32_t n_cols, int32_t nnz, int32_t d
 MPS_API int mps_spmm_host_resident_b(int32_t n_rows, int32_t n_cols, int32_t nnz, int32_t dim, int dtype, int32_t cost,
                              int32_t threads_per_warp, const int32_t *row_ptr, const int32_t *col_idx,
                              const void *val, const void *d_B, void *b_ready_stream, void *C);
+
+/* mps_spmm_host for the product mps_spmm_scaled forms: C[i,:] = row_scale[i] * sum_k col_scale[col[k]] * B[col[k],:].
+ * This is the shape of the reference program itself, which uploads one number per node (its `degrees`,
+ * src/MergePathSpMM.cu:183-190,207-209) and forms every value in the kernel (:436-441) instead of storing one per
+ * non-zero: the call moves n_rows + n_cols floats where mps_spmm_host moves nnz values (GCN on a graph of average
+ * degree 32, dim 64: a quarter fewer bytes to the device).  fp32; row_scale has n_rows entries, col_scale n_cols,
+ * either may be NULL (= all ones), not both.  Validation, slabs and workspace as for mps_spmm_host. */
+MPS_API int mps_spmm_host_scaled(int32_t n_rows, int32_t n_cols, int32_t nnz, int32_t dim, int32_t cost,
+                         int32_t threads_per_warp, const int32_t *row_ptr, const int32_t *col_idx,
+                         const float *row_scale, const float *col_scale, const void *B, void *C);
 MPS_API void mps_host_workspace_release(void);
 
 /* ------------------------------------------------------------------ no-allocation call --- */

@@ -29,7 +29,7 @@ try:
 except Exception:  # pragma: no cover
     torch = None
 
-__all__ = ["Plan", "MultiGpu", "layout_query", "coo_to_csr", "coo_to_csr_device", "npz_to_csr", "spmm", "spmm_host", "spmm_host_resident_b", "gather_probe", "gather_probe_stream", "partition_host", "schedule_host", "load_csr_rect", "spmm_noalloc", "partition_device", "schedule_device", "chunk_count", "load_csr", "save_csr",
+__all__ = ["Plan", "MultiGpu", "layout_query", "coo_to_csr", "coo_to_csr_device", "npz_to_csr", "spmm", "spmm_host", "spmm_host_resident_b", "spmm_host_scaled", "gather_probe", "gather_probe_stream", "partition_host", "schedule_host", "load_csr_rect", "spmm_noalloc", "partition_device", "schedule_device", "chunk_count", "load_csr", "save_csr",
            "save_csr_bin", "load_csr_bin", "slab_bounds", "slab_rebase", "algorithmic_bytes", "F32", "F16", "MpsError"]
 
 
@@ -221,6 +221,24 @@ def spmm_host(row_ptr, col_idx, val, B, out=None, cost: int = 8, threads_per_war
         out = np.empty((n_rows, dim), np.float16 if is_half else np.float32)
     capi.check(capi.lib().mps_spmm_host(n_rows, int(B.shape[0]), nnz, dim, F16 if is_half else F32, cost, threads_per_warp, host_ptr(row_ptr),
                                         host_ptr(col_idx), host_ptr(val), host_ptr(B), host_ptr(out)))
+    return out
+
+
+def spmm_host_scaled(row_ptr, col_idx, row_scale, col_scale, B, out=None, cost: int = 8, threads_per_warp: int = 1):
+    """mps_spmm_host_scaled: C[i] = row_scale[i] * sum_k col_scale[col[k]] * B[col[k]] on host (numpy or pinned torch CPU)
+    arrays, fp32; either scale may be None (all ones), not both.  Returns C as a numpy array (or fills `out`)."""
+    def host_ptr(a):
+        if a is None:
+            return None
+        if torch is not None and isinstance(a, torch.Tensor):
+            return C.c_void_p(a.data_ptr())
+        return a.ctypes.data_as(C.c_void_p)
+
+    n_rows, dim = int(row_ptr.shape[0]) - 1, int(B.shape[1])
+    if out is None:
+        out = np.empty((n_rows, dim), np.float32)
+    capi.check(capi.lib().mps_spmm_host_scaled(n_rows, int(B.shape[0]), int(col_idx.shape[0]), dim, cost, threads_per_warp, host_ptr(row_ptr),
+                                               host_ptr(col_idx), host_ptr(row_scale), host_ptr(col_scale), host_ptr(B), host_ptr(out)))
     return out
 
 

@@ -18,7 +18,7 @@ SYMBOLS = [
     "mps_last_error", "mps_version", "mps_csr_load", "mps_csr_load_rect", "mps_csr_free", "mps_csr_save", "mps_csr_save_bin",
     "mps_csr_load_bin", "mps_coo_to_csr", "mps_coo_to_csr_device", "mps_csr_transpose_device", "mps_npz_to_csr", "mps_chunk_count", "mps_partition_device", "mps_schedule_device", "mps_plan_create",
     "mps_plan_destroy", "mps_plan_tune", "mps_plan_partition", "mps_spmm", "mps_spmm_scaled", "mps_plan_sync_check", "mps_plan_info", "mps_plan_set_walk", "mps_plan_layout", "mps_layout_query", "mps_plan_profile", "mps_plan_profile_read",
-    "mps_algorithmic_bytes", "mps_gather_probe", "mps_gather_probe_stream", "mps_spmm_host", "mps_spmm_host_resident_b", "mps_partition_host", "mps_schedule_host", "mps_host_workspace_release", "mps_spmm_noalloc", "mps_slab_bounds", "mps_slab_bounds_items", "mps_slab_rebase", "mps_multi_create", "mps_multi_destroy", "mps_multi_slab",
+    "mps_algorithmic_bytes", "mps_gather_probe", "mps_gather_probe_stream", "mps_spmm_host", "mps_spmm_host_resident_b", "mps_spmm_host_scaled", "mps_partition_host", "mps_schedule_host", "mps_host_workspace_release", "mps_spmm_noalloc", "mps_slab_bounds", "mps_slab_bounds_items", "mps_slab_rebase", "mps_multi_create", "mps_multi_destroy", "mps_multi_slab",
     "mps_multi_set_b", "mps_multi_spmm", "mps_multi_get_c",
 ]
 
@@ -81,6 +81,7 @@ def lib():
     L.mps_algorithmic_bytes.restype = i64
     L.mps_spmm_host.argtypes = [i32, i32, i32, i32, C.c_int, i32, i32, vp, vp, vp, vp, vp]
     L.mps_spmm_host_resident_b.argtypes = [i32, i32, i32, i32, C.c_int, i32, i32, vp, vp, vp, vp, vp, vp]
+    L.mps_spmm_host_scaled.argtypes = [i32, i32, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp]
     L.mps_partition_host.argtypes = [vp, i32, i32, vp, C.c_int]
     L.mps_schedule_host.argtypes = [vp, i32, i32, vp, C.c_int]
     L.mps_gather_probe.argtypes = [vp, i64, i32, i64, vp, i64, vp, C.POINTER(C.c_float), C.POINTER(i64)]

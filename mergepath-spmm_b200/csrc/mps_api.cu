@@ -479,8 +479,9 @@ const int kMaxHostSlabs = 16;  // measured on a 2^21-node graph: 8 and 12 slabs 
 const long long kHostSlabMinItems = 4ll << 20;  // below this the call is one slab
 
 struct HostWorkspace {
-    void *buf[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};  // rp, col, val, B, C, rebased rp slabs
-    size_t cap[6] = {0, 0, 0, 0, 0, 0};
+    static const int kBuffers = 8;
+    void *buf[kBuffers] = {};  // rp, col, val, B, C, rebased rp slabs, row scale, column scale
+    size_t cap[kBuffers] = {};
     mps_plan *plan[kMaxHostSlabs] = {};
     cudaStream_t s_in = nullptr, s_b = nullptr, s_work = nullptr, s_out = nullptr;  // plan, upload, work, download
     cudaEvent_t ev_b = nullptr, ev_slab[kMaxHostSlabs] = {}, ev_done[kMaxHostSlabs] = {};
@@ -488,7 +489,7 @@ struct HostWorkspace {
     int device = -1;
     void release() {
         cudaFree(d_bad); d_bad = nullptr;
-        for (int i = 0; i < 6; ++i) { cudaFree(buf[i]); buf[i] = nullptr; cap[i] = 0; }
+        for (int i = 0; i < kBuffers; ++i) { cudaFree(buf[i]); buf[i] = nullptr; cap[i] = 0; }
         for (int i = 0; i < kMaxHostSlabs; ++i) {
             mps_plan_destroy(plan[i]); plan[i] = nullptr;
             if (ev_slab[i]) cudaEventDestroy(ev_slab[i]);
@@ -546,8 +547,8 @@ static int host_slabs(int32_t n_rows, int32_t nnz, const int32_t *row_ptr, HostS
 // arrays: nothing on the device reads row_ptr until the host has checked it.  B already on the device: it is complete
 // when the work queued so far on the caller's stream has run (another GPU's share of it may still be arriving over
 // NVLink meanwhile).
-static int host_begin(int32_t n_rows, int32_t n_cols, int32_t dim, int dtype, const int32_t *row_ptr, const void *B, bool b_on_device,
-                      cudaStream_t b_stream) {
+static int host_begin(int32_t n_rows, int32_t n_cols, int32_t dim, int dtype, const int32_t *row_ptr, const float *row_scale,
+                      const float *col_scale, const void *B, bool b_on_device, cudaStream_t b_stream) {
     int dev = 0;
     MPS_CUDA(cudaGetDevice(&dev));
     if (g_ws.device != dev) { g_ws.release(); g_ws.device = dev; }
@@ -565,6 +566,15 @@ static int host_begin(int32_t n_rows, int32_t n_cols, int32_t dim, int dtype, co
     }
     if (int rc = ws_reserve(0, 4 * ((size_t)n_rows + 1))) return rc;
     MPS_CUDA(cudaMemcpyAsync(g_ws.buf[0], row_ptr, 4 * ((size_t)n_rows + 1), cudaMemcpyHostToDevice, g_ws.s_in));
+    // scaled product: the two factor vectors take the place of a value per non-zero; they are small and go ahead of B too
+    if (row_scale) {
+        if (int rc = ws_reserve(6, 4 * (size_t)n_rows)) return rc;
+        MPS_CUDA(cudaMemcpyAsync(g_ws.buf[6], row_scale, 4 * (size_t)n_rows, cudaMemcpyHostToDevice, g_ws.s_in));
+    }
+    if (col_scale) {
+        if (int rc = ws_reserve(7, 4 * (size_t)n_cols)) return rc;
+        MPS_CUDA(cudaMemcpyAsync(g_ws.buf[7], col_scale, 4 * (size_t)n_cols, cudaMemcpyHostToDevice, g_ws.s_in));
+    }
     if (b_on_device) {
         MPS_CUDA(cudaEventRecord(g_ws.ev_b, b_stream));
         return MPS_OK;
@@ -577,8 +587,8 @@ static int host_begin(int32_t n_rows, int32_t n_cols, int32_t dim, int dtype, co
 }
 
 static int host_call(int32_t n_rows, int32_t n_cols, int32_t nnz, int32_t dim, int dtype, int32_t cost, int32_t threads_per_warp,
-                     const int32_t *row_ptr, const int32_t *col_idx, const void *val, const void *B, bool b_on_device, cudaStream_t b_stream,
-                     void *C, const HostSlabs &hs, long long *bad_column) {
+                     const int32_t *row_ptr, const int32_t *col_idx, const void *val, bool row_scaled, bool col_scaled, const void *B,
+                     bool b_on_device, cudaStream_t b_stream, void *C, const HostSlabs &hs, long long *bad_column) {
     const size_t elem = dtype == MPS_F16 ? 2 : 4;
     const int n_slabs = hs.n;
     const int32_t *bounds = hs.bounds;
@@ -649,8 +659,12 @@ static int host_call(int32_t n_rows, int32_t n_cols, int32_t nnz, int32_t dim, i
             MPS_CUDA(cudaGetLastError());
         }
         char *c_slab = d_C + elem * (size_t)r0 * dim;
-        if (int rc = mps_spmm(g_ws.plan[s], d_rps + rps_off[s], d_col + off[s], val ? (const void *)(d_val + elem * off[s]) : nullptr,
-                              d_B, c_slab, s_work))
+        if (row_scaled || col_scaled) {  // the factors landed on the plan stream ahead of the partitions the host has waited for
+            if (int rc = mps_spmm_scaled(g_ws.plan[s], d_rps + rps_off[s], d_col + off[s], row_scaled ? (const float *)g_ws.buf[6] + r0 : nullptr,
+                                         col_scaled ? (const float *)g_ws.buf[7] : nullptr, d_B, c_slab, s_work))
+                return rc;
+        } else if (int rc = mps_spmm(g_ws.plan[s], d_rps + rps_off[s], d_col + off[s], val ? (const void *)(d_val + elem * off[s]) : nullptr,
+                                     d_B, c_slab, s_work))
             return rc;
         MPS_CUDA(cudaEventRecord(g_ws.ev_done[s], s_work));
         MPS_CUDA(cudaStreamWaitEvent(s_out, g_ws.ev_done[s], 0));
@@ -668,7 +682,8 @@ static int host_call(int32_t n_rows, int32_t n_cols, int32_t nnz, int32_t dim, i
 }
 
 static int host_entry(const char *who, int32_t n_rows, int32_t n_cols, int32_t nnz, int32_t dim, int dtype, int32_t cost, int32_t threads_per_warp,
-                      const int32_t *row_ptr, const int32_t *col_idx, const void *val, const void *B, bool b_on_device, void *b_stream, void *C) {
+                      const int32_t *row_ptr, const int32_t *col_idx, const void *val, const float *row_scale, const float *col_scale,
+                      const void *B, bool b_on_device, void *b_stream, void *C) {
     if (!row_ptr || !B || !C || (!col_idx && nnz > 0)) return fail(MPS_ERR_ARG, "%s: NULL argument", who);
     if (dim < 1 || cost < 1 || n_cols < 0) return fail(MPS_ERR_ARG, "%s: dim and cost must be >= 1, n_cols >= 0", who);
     if (dtype != MPS_F32 && dtype != MPS_F16) return fail(MPS_ERR_ARG, "%s: unknown dtype %d", who, dtype);
@@ -681,7 +696,7 @@ static int host_entry(const char *who, int32_t n_rows, int32_t n_cols, int32_t n
             if (st) cudaStreamSynchronize(st);
         g_error = kept;
     };
-    int rc = host_begin(n_rows, n_cols, dim, dtype, row_ptr, B, b_on_device, (cudaStream_t)b_stream);
+    int rc = host_begin(n_rows, n_cols, dim, dtype, row_ptr, row_scale, col_scale, B, b_on_device, (cudaStream_t)b_stream);
     const std::string begin_error = rc != MPS_OK ? g_error : std::string();
     // the caller's arrays are checked before any kernel can index by them: row_ptr here on the host (small, and the slab
     // bounds are taken from it), col_idx on the device where each slab lands; a bad index is reported in preference to any
@@ -695,7 +710,9 @@ static int host_entry(const char *who, int32_t n_rows, int32_t n_cols, int32_t n
         return bad_arg;
     }
     long long bad = -1;
-    if (rc == MPS_OK) rc = host_call(n_rows, n_cols, nnz, dim, dtype, cost, threads_per_warp, row_ptr, col_idx, val, B, b_on_device, (cudaStream_t)b_stream, C, hs, &bad);
+    if (rc == MPS_OK)
+        rc = host_call(n_rows, n_cols, nnz, dim, dtype, cost, threads_per_warp, row_ptr, col_idx, val, row_scale != nullptr, col_scale != nullptr, B, b_on_device,
+                       (cudaStream_t)b_stream, C, hs, &bad);
     else g_error = begin_error;
     // without a usable device nothing was checked there: the same check on host threads, so that a bad index is
     // reported in preference to the missing device
@@ -718,14 +735,22 @@ static int host_entry(const char *who, int32_t n_rows, int32_t n_cols, int32_t n
 
 extern "C" int mps_spmm_host(int32_t n_rows, int32_t n_cols, int32_t nnz, int32_t dim, int dtype, int32_t cost, int32_t threads_per_warp,
                              const int32_t *row_ptr, const int32_t *col_idx, const void *val, const void *B, void *C) {
-    return host_entry("mps_spmm_host", n_rows, n_cols, nnz, dim, dtype, cost, threads_per_warp, row_ptr, col_idx, val, B, false, nullptr, C);
+    return host_entry("mps_spmm_host", n_rows, n_cols, nnz, dim, dtype, cost, threads_per_warp, row_ptr, col_idx, val, nullptr, nullptr, B, false, nullptr, C);
 }
 
 extern "C" int mps_spmm_host_resident_b(int32_t n_rows, int32_t n_cols, int32_t nnz, int32_t dim, int dtype, int32_t cost,
                                         int32_t threads_per_warp, const int32_t *row_ptr, const int32_t *col_idx, const void *val,
                                         const void *d_B, void *b_ready_stream, void *C) {
-    return host_entry("mps_spmm_host_resident_b", n_rows, n_cols, nnz, dim, dtype, cost, threads_per_warp, row_ptr, col_idx, val, d_B, true,
-                      b_ready_stream, C);
+    return host_entry("mps_spmm_host_resident_b", n_rows, n_cols, nnz, dim, dtype, cost, threads_per_warp, row_ptr, col_idx, val, nullptr, nullptr, d_B,
+                      true, b_ready_stream, C);
+}
+
+extern "C" int mps_spmm_host_scaled(int32_t n_rows, int32_t n_cols, int32_t nnz, int32_t dim, int32_t cost, int32_t threads_per_warp,
+                                    const int32_t *row_ptr, const int32_t *col_idx, const float *row_scale, const float *col_scale,
+                                    const void *B, void *C) {
+    if (!row_scale && !col_scale) return fail(MPS_ERR_ARG, "mps_spmm_host_scaled: both scale arrays are NULL (use mps_spmm_host)");
+    return host_entry("mps_spmm_host_scaled", n_rows, n_cols, nnz, dim, MPS_F32, cost, threads_per_warp, row_ptr, col_idx, nullptr, row_scale, col_scale,
+                      B, false, nullptr, C);
 }
 
 // ------------------------------------------------------------------------------------- slabs (host)

@@ -41,6 +41,8 @@ def test_default_arm_line_on_a_small_graph(cuda):
     # the line looks at what it timed, and carries bounds that are fractions of a peak
     assert out["check"]["ok"] is True and out["check"]["rows"] >= 4000 and out["check"]["max_scaled_err"] <= 1.0
     assert out["e2e"]["check"]["ok"] is True
+    sc = out["e2e"]["scaled_call"]   # the same product through mps_spmm_host_scaled: fewer bytes up, same C
+    assert sc["check_ok"] is True and sc["h2d_bytes_per_step"] < out["e2e"]["h2d_bytes_per_step"]
     r = out["roofline"]
     assert 0 < r["compulsory_frac"] < 1.5 and r["l2_peak_gbs"] > r["hbm_gather_gbs"] > 0 and 0 < r["l2_frac"] < 1.5
     assert r["nearest_bound"] in ("hbm_compulsory", "l2_gather", "hbm_measured_traffic", "own_stream_gather")

@@ -340,7 +340,7 @@ def test_host_buffer_call_pipelines_large_inputs_over_row_slabs(mps, orc, graphs
     rp, col = graphs.rmat_csr(19, 32, seed=3)
     val = graphs.gcn_values(rp, col)
     n, nnz = len(rp) - 1, len(col)
-    n_slabs = min(8, (n + nnz) // (4 << 20))
+    n_slabs = min(16, (n + nnz) // (4 << 20))
     assert n_slabs >= 2
     B = graphs.dense_uniform(n, 32, seed=4)
     pinned = [torch.from_numpy(a).pin_memory() for a in (rp, col, val, B)]
@@ -357,6 +357,53 @@ def test_host_buffer_call_pipelines_large_inputs_over_row_slabs(mps, orc, graphs
             assert np.array_equal(_bits(got), _bits(host[r0:r1])), s
     scale = orc.spmm_abs_f64(rp, col, val, B)
     assert (np.abs(host.astype(np.float64) - orc.spmm_f64(rp, col, val, B)) <= 1e-6 + 1e-5 * scale).all()
+    mps.capi.lib().mps_host_workspace_release()
+
+
+def test_scaled_host_call_equals_the_scaled_device_path(mps, orc, graphs, cuda):
+    """mps_spmm_host_scaled: the factor vectors travel instead of a value per non-zero; one slab: bit-equal to
+    mps_spmm_scaled on device buffers; several slabs: each slab bit-equal to the device path on that slab, the whole
+    within tolerance of the fp64 product with values row_scale[i] * col_scale[j]."""
+    rp, col = cases.c1_rmat()
+    n, nnz = len(rp) - 1, len(col)
+    rng = np.random.default_rng(5)
+    rs = (1.0 / np.sqrt(np.maximum(np.diff(rp), 1).astype(np.float64))).astype(np.float32)
+    cs = rng.uniform(0.5, 1.5, n).astype(np.float32)
+    B = graphs.dense_uniform(n, 64, seed=1)
+
+    def device_path(srp, scol, srs):
+        plan = mps.Plan(len(srp) - 1, len(scol), B.shape[1], mps.F32, 16, device=cuda)
+        d = [torch.from_numpy(a).to(cuda) if a is not None else None for a in (srp, scol, srs, cs, B)]
+        plan.partition(d[0])
+        out = plan.spmm_scaled(d[0], d[1], d[2], d[3], d[4])
+        plan.sync_check()
+        plan.close()
+        return out.cpu().numpy()
+
+    host = mps.spmm_host_scaled(rp, col, rs, cs, B, cost=16)
+    assert np.array_equal(_bits(host), _bits(device_path(rp, col, rs)))
+    only_cols = mps.spmm_host_scaled(rp, col, None, cs, B, cost=16)
+    assert np.array_equal(_bits(only_cols), _bits(device_path(rp, col, None)))
+
+    rp, col = graphs.rmat_csr(19, 32, seed=3)
+    n, nnz = len(rp) - 1, len(col)
+    n_slabs = min(16, (n + nnz) // (4 << 20))
+    assert n_slabs >= 2
+    rs = (1.0 / np.sqrt(np.maximum(np.diff(rp), 1).astype(np.float64))).astype(np.float32)
+    cs = rs.copy()
+    B = graphs.dense_uniform(n, 32, seed=4)
+    pinned = [torch.from_numpy(a).pin_memory() for a in (rp, col, rs, cs, B)]
+    out = torch.full((n, 32), float("nan"), dtype=torch.float32).pin_memory()
+    mps.spmm_host_scaled(*pinned, out=out, cost=16)
+    host = out.numpy()
+    b = mps.slab_bounds(rp, n_slabs, "items", 4)
+    for s in (0, n_slabs - 1):
+        r0, r1 = int(b[s]), int(b[s + 1])
+        got = device_path(mps.slab_rebase(rp, r0, r1), col[rp[r0]:rp[r1]], rs[r0:r1])
+        assert np.array_equal(_bits(got), _bits(host[r0:r1])), s
+    val = (np.repeat(rs, np.diff(rp)).astype(np.float64) * cs[col].astype(np.float64)).astype(np.float32)
+    scale = orc.spmm_abs_f64(rp, col, val, B)
+    assert (np.abs(host.astype(np.float64) - orc.spmm_f64(rp, col, val, B)) <= 1e-6 + 2e-5 * scale).all()
     mps.capi.lib().mps_host_workspace_release()
 
 

@@ -72,6 +72,30 @@ def test_host_buffer_call_rejects_a_bad_csr_before_anything_runs(mps):
         assert _host_call(mps, rp, col, n) == mps.capi.ERR_CUDA  # valid arrays: only the device is missing
 
 
+def test_scaled_host_call_checks_its_arguments(mps):
+    """mps_spmm_host_scaled: both factors NULL is an argument error; a bad CSR is reported as for mps_spmm_host."""
+    rp, col = cases.c2_batched(40)
+    n = len(rp) - 1
+    B = np.zeros((n, 8), np.float32)
+    ones = np.ones(n, np.float32)
+    with pytest.raises(mps.MpsError) as e:
+        mps.spmm_host_scaled(rp, col, None, None, B)
+    assert e.value.code == mps.capi.ERR_ARG
+    bad = col.copy(); bad[5] = n
+    with pytest.raises(mps.MpsError) as e:
+        mps.spmm_host_scaled(rp, bad, ones, ones, B)
+    assert e.value.code == mps.capi.ERR_ARG and f"col_idx[5] = {n}" in str(e.value)
+    dec = rp.copy(); dec[7] = dec[8] + 1
+    with pytest.raises(mps.MpsError) as e:
+        mps.spmm_host_scaled(dec, col, ones, None, B)
+    assert e.value.code == mps.capi.ERR_ARG
+    import torch
+    if not torch.cuda.is_available():
+        with pytest.raises(mps.MpsError) as e:
+            mps.spmm_host_scaled(rp, col, ones, ones, B)
+        assert e.value.code == mps.capi.ERR_CUDA
+
+
 def test_multi_gpu_driver_rejects_a_bad_csr_before_touching_a_device(mps):
     rp, col = cases.c2_batched(40)
     n = len(rp) - 1
