@@ -57,20 +57,67 @@ std::vector<Span> cut_at_commas(const char *b, const char *e, int n) {
 // A piece holds one cell per ',' plus one more if text follows its last ','.
 size_t count_cells(Span s) {
     size_t n = 0;
-    const char *p = s.b;
-    while (p < s.e) {
-        const void *c = memchr(p, ',', (size_t)(s.e - p));
-        if (!c) { ++n; break; }
-        ++n;
-        p = (const char *)c + 1;
+    const char *last = nullptr;
+    for (const char *b = s.b; b < s.e;) {  // blocks keep the per-byte sum in a narrow counter: the loop vectorises
+        const char *stop = s.e - b > 4096 ? b + 4096 : s.e;
+        unsigned hits = 0;
+        for (const char *p = b; p < stop; ++p) hits += *p == ',';
+        n += hits;
+        b = stop;
     }
+    for (const char *p = s.e; p > s.b; --p)
+        if (p[-1] == ',') { last = p - 1; break; }
+    if (s.e > s.b && (!last || last + 1 < s.e)) ++n;  // text after the last ',' (or no ',' at all) is one more cell
     return n;
+}
+
+// Eight ASCII digits, first digit in the lowest byte -> their value (three multiplications, no loop).
+inline uint32_t eight_digits(uint64_t v) {
+    const uint64_t mask = 0x000000FF000000FFull;
+    const uint64_t mul1 = 0x000F424000000064ull;  // 100 + (1000000 << 32)
+    const uint64_t mul2 = 0x0000271000000001ull;  // 1 + (10000 << 32)
+    v = (v * 10) + (v >> 8);
+    v = (((v & mask) * mul1) + (((v >> 16) & mask) * mul2)) >> 32;
+    return (uint32_t)v;
+}
+
+// Plain cells - one to eight digits and a ',' with nothing else - eight bytes at a time: the position of the ',' from a
+// zero-byte test, the digits checked and converted in the same word.  Stops at the first cell that is anything else
+// (blanks, a sign, nine or ten digits, a bad byte) or too near the end of the piece for an 8-byte read, and leaves
+// it to the byte-wise loop of parse_cells.  Little-endian hosts (the first character is the lowest byte).
+inline const char *parse_plain_cells(const char *p, const char *e, int32_t *&out) {
+    const uint64_t ones = 0x0101010101010101ull, high = 0x8080808080808080ull;
+    while (e - p >= 16) {
+        uint64_t x;
+        memcpy(&x, p, 8);
+        const uint64_t c = x ^ 0x2C2C2C2C2C2C2C2Cull;               // a zero byte where a ',' stands
+        const uint64_t comma = (c - ones) & ~c & high;
+        unsigned len;
+        if (comma) {
+            len = (unsigned)__builtin_ctzll(comma) >> 3;            // digits before the first ','
+            if (len == 0) return p;                                  // empty cell: the byte-wise loop reports it
+        } else {
+            if (p[8] != ',') return p;                               // nine digits or more, or something else
+            len = 8;
+        }
+        const uint64_t keep = len == 8 ? ~0ull : (1ull << (8 * len)) - 1;
+        const uint64_t d = (x & keep) - (0x3030303030303030ull & keep);  // digit values, if digits they are
+        // every byte of d must be 0..9: no high nibble, and adding 6 must not carry into one
+        if (((d | (d + 0x0606060606060606ull)) & 0xF0F0F0F0F0F0F0F0ull) != 0) return p;
+        // (a byte below '0' made the subtraction borrow: its own byte then reads >= 0xF0 or it spoilt its neighbour - both
+        // show as a high nibble)
+        *out++ = (int32_t)eight_digits(len == 8 ? d : d << (8 * (8 - len)));  // shifted up: the missing digits lead as zeros
+        p += len + 1;
+    }
+    return p;
 }
 
 // Parses the cells of a piece into out[]; returns the offset of the first bad byte or -1.
 long parse_cells(Span s, int32_t *out) {
     const char *p = s.b;
     while (p < s.e) {
+        p = parse_plain_cells(p, s.e, out);  // runs of plain cells; what follows is one cell the long way
+        if (p >= s.e) break;
         while (p < s.e && (*p == ' ' || *p == '\t')) ++p;
         bool neg = false;
         if (p < s.e && (*p == '-' || *p == '+')) { neg = *p == '-'; ++p; }

@@ -94,6 +94,49 @@ def test_parallel_parse_matches_single_thread_on_a_larger_file(tmp_path, mps, gr
     assert np.array_equal(b[0], rp) and np.array_equal(b[1], col)
 
 
+def _long_file(cells2, n_rows=40, seed=3):
+    """Two long lines: a monotone row_ptr whose last cell is len(cells2), then the given cells of line 2."""
+    rng = np.random.default_rng(seed)
+    inner = np.sort(rng.integers(0, len(cells2) + 1, n_rows - 1))
+    rp = [0] + inner.tolist() + [len(cells2)]
+    return ",".join(map(str, rp)) + ",\n" + ",".join(cells2) + ","
+
+
+def test_cells_of_every_shape_in_long_lines(tmp_path, mps):
+    """Long lines go through the eight-bytes-at-a-time path; cells it must hand to the byte-wise loop (blanks, signs,
+    nine and ten digits, leading zeros) are mixed with plain ones of one to eight digits."""
+    rng = np.random.default_rng(8)
+    want, cells = [], []
+    for i in range(3000):
+        digits = int(rng.integers(1, 11))
+        lo, hi = 10 ** (digits - 1) if digits > 1 else 0, min(10 ** digits - 1, 2 ** 31 - 2)
+        v = int(rng.integers(lo, hi + 1))
+        text = str(v)
+        shape = int(rng.integers(0, 8))
+        text = {0: " " + text, 1: text + " ", 2: "+" + text, 3: "00" + text, 4: "\t" + text + "\t"}.get(shape, text)
+        want.append(v)
+        cells.append(text)
+    p = str(tmp_path / "mixed.csr")
+    _write(p, _long_file(cells))
+    for threads in (1, 4):
+        rp, col, n_cols = mps.load_csr_rect(p, threads)
+        assert col.tolist() == want and n_cols == max(want) + 1 and rp[-1] == len(want)
+
+
+@pytest.mark.parametrize("bad", ["12a4", "", "1/2", "1:2", "12 3", "99999999999", "2147483648", "-", "1+", "١٢"])
+def test_a_bad_cell_in_the_middle_of_a_long_line_is_a_format_error(tmp_path, mps, bad):
+    cells = [str(i % 977) for i in range(4000)]
+    for at in (0, 1999, 3999):
+        mixed = list(cells)
+        mixed[at] = bad
+        p = str(tmp_path / f"bad{at}.csr")
+        _write(p, _long_file(mixed))
+        for threads in (1, 4):
+            with pytest.raises(mps.MpsError) as e:
+                mps.load_csr_rect(p, threads)
+            assert e.value.code == mps.capi.ERR_FORMAT, (bad, at)
+
+
 def test_reads_the_reference_converter_output(tmp_path, mps):
     """The independent writer: scipy's coo->csr plus the cell-by-cell text of the reference's
     scripts/npz_to_csr.py:13-28, restated here (the script itself is not shipped)."""
