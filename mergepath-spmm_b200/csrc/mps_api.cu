@@ -586,9 +586,9 @@ static int host_begin(int32_t n_rows, int32_t n_cols, int32_t dim, int dtype, co
     return MPS_OK;
 }
 
-static int host_call(int32_t n_rows, int32_t n_cols, int32_t nnz, int32_t dim, int dtype, int32_t cost, int32_t threads_per_warp,
+static int host_call(int32_t n_rows, int32_t n_cols, int32_t dim, int dtype, int32_t cost, int32_t threads_per_warp,
                      const int32_t *row_ptr, const int32_t *col_idx, const void *val, bool row_scaled, bool col_scaled, const void *B,
-                     bool b_on_device, cudaStream_t b_stream, void *C, const HostSlabs &hs, long long *bad_column) {
+                     bool b_on_device, void *C, const HostSlabs &hs, long long *bad_column) {
     const size_t elem = dtype == MPS_F16 ? 2 : 4;
     const int n_slabs = hs.n;
     const int32_t *bounds = hs.bounds;
@@ -711,8 +711,8 @@ static int host_entry(const char *who, int32_t n_rows, int32_t n_cols, int32_t n
     }
     long long bad = -1;
     if (rc == MPS_OK)
-        rc = host_call(n_rows, n_cols, nnz, dim, dtype, cost, threads_per_warp, row_ptr, col_idx, val, row_scale != nullptr, col_scale != nullptr, B, b_on_device,
-                       (cudaStream_t)b_stream, C, hs, &bad);
+        rc = host_call(n_rows, n_cols, dim, dtype, cost, threads_per_warp, row_ptr, col_idx, val, row_scale != nullptr, col_scale != nullptr, B, b_on_device,
+                       C, hs, &bad);
     else g_error = begin_error;
     // without a usable device nothing was checked there: the same check on host threads, so that a bad index is
     // reported in preference to the missing device
