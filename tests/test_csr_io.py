@@ -137,6 +137,48 @@ def test_a_bad_cell_in_the_middle_of_a_long_line_is_a_format_error(tmp_path, mps
             assert e.value.code == mps.capi.ERR_FORMAT, (bad, at)
 
 
+def _cell_model(text):
+    """The loader's grammar for one cell: blanks, an optional sign, digits, blanks; the value must fit int32.
+    Returns the value, or None for a cell the loader must refuse."""
+    import re
+    m = re.fullmatch(r"[ \t]*([+-]?)([0-9]+)[ \t]*", text)
+    if not m:
+        return None
+    v = int(m.group(2)) * (-1 if m.group(1) == "-" else 1)
+    return v if -2 ** 31 <= v < 2 ** 31 else None
+
+
+def test_loader_against_a_model_of_its_grammar_on_random_cells(tmp_path, mps):
+    """Property test: lines of random cells - plain, decorated and malformed, of every length - parse to what a
+    regular-expression model of the grammar says, or are refused where the model refuses (or a column is negative)."""
+    from hypothesis import given, settings, strategies as st, HealthCheck
+    plain = st.integers(0, 2 ** 31 - 2).map(str)
+    decorated = st.tuples(st.sampled_from(["", " ", "\t", "  "]), st.sampled_from(["", "+", "-"]), st.integers(0, 2 ** 33).map(str),
+                          st.sampled_from(["", " ", "\t "])).map("".join)
+    zeros = st.tuples(st.sampled_from(["0", "00", "0000000"]), st.integers(0, 99999999).map(str)).map("".join)
+    junk = st.text(alphabet="0123456789+- \t./:;abcxyz", min_size=0, max_size=12)
+    cell = st.one_of(plain, plain, plain, decorated, zeros, junk)
+    path = str(tmp_path / "fuzz.csr")
+
+    @settings(max_examples=150, deadline=None, suppress_health_check=list(HealthCheck))
+    @given(st.lists(cell, min_size=1, max_size=40), st.integers(0, 3), st.integers(1, 4))
+    def run(odd, where, threads):
+        cells = [str(i % 9973) for i in range(300)]
+        at = (0, 100, 299, 150)[where]
+        cells[at:at] = odd                       # the random cells sit at the start, in the middle or at the end
+        want = [_cell_model(c) for c in cells]
+        _write(path, _long_file(cells))
+        if any(v is None or v < 0 for v in want):
+            with pytest.raises(mps.MpsError) as e:
+                mps.load_csr_rect(path, threads)
+            assert e.value.code == mps.capi.ERR_FORMAT
+        else:
+            rp, col, n_cols = mps.load_csr_rect(path, threads)
+            assert col.tolist() == want
+
+    run()
+
+
 def test_reads_the_reference_converter_output(tmp_path, mps):
     """The independent writer: scipy's coo->csr plus the cell-by-cell text of the reference's
     scripts/npz_to_csr.py:13-28, restated here (the script itself is not shipped)."""
