@@ -39,6 +39,23 @@ def test_host_partition_on_a_mid_size_graph_equals_the_oracle(mps, orc, graphs):
     assert e.value.code == mps.capi.ERR_ARG
 
 
+def test_host_partition_and_schedule_equal_the_oracle_on_random_row_lengths(mps, orc):
+    """Property test: any row-length sequence (empty rows, one huge row, runs of equal lengths) and any chunk count
+    give the coordinates and the six schedule arrays of the oracle, which is pinned to the reference's vectors."""
+    from hypothesis import given, settings, strategies as st, HealthCheck
+    lengths = st.lists(st.one_of(st.just(0), st.integers(0, 5), st.integers(0, 300)), min_size=1, max_size=200)
+
+    @settings(max_examples=120, deadline=None, suppress_health_check=list(HealthCheck))
+    @given(lengths, st.integers(1, 64), st.integers(0, 2))
+    def run(lens, cost, threads):
+        rp = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+        p, _ = mps.chunk_count(len(rp) - 1, int(rp[-1]), cost)
+        assert np.array_equal(mps.partition_host(rp, p, threads), orc.partition(rp, p))
+        assert np.array_equal(mps.schedule_host(rp, p, threads), orc.schedule(rp, p))
+
+    run()
+
+
 def _host_call(mps, rp, col, n_cols, dim=8):
     n = len(rp) - 1
     B = np.zeros((n_cols, dim), np.float32)
