@@ -318,6 +318,32 @@ def test_errors_are_codes_not_faults(mps, cuda):
     assert e.value.code == mps.capi.ERR_ARG
 
 
+def test_random_matrices_bit_exact_with_the_model(mps, orc, cuda):
+    """Property test: random row lengths (empty rows, a few long rows, runs of short ones), random column indices and
+    values, random dim / cost / dtype / layout knob - C is bit-equal to the CPU model of the summation order and
+    within tolerance of the fp64 loop, whatever the shape."""
+    from hypothesis import given, settings, strategies as st, HealthCheck
+    lengths = st.lists(st.one_of(st.just(0), st.integers(0, 6), st.integers(0, 90), st.integers(200, 3000)), min_size=1, max_size=120)
+    tunes = st.sampled_from([None, None, dict(fused_fixup=0), dict(chunks_per_unit=1), dict(unroll=4), dict(block_threads=128), dict(bulk_staging=False)])
+
+    @settings(max_examples=150, deadline=None, suppress_health_check=list(HealthCheck))
+    @given(lengths, st.sampled_from([4, 16, 20, 32, 64, 128]), st.sampled_from([1, 3, 8, 16, 600]), st.booleans(), st.booleans(), tunes,
+           st.integers(0, 2 ** 31 - 1))
+    def run(lens, dim, cost, half, with_values, tune, seed):
+        rng = np.random.default_rng(seed)
+        rp = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+        n, nnz = len(rp) - 1, int(rp[-1])
+        n_cols = n
+        col = rng.integers(0, n_cols, nnz).astype(np.int32)
+        dt = np.float16 if half else np.float32
+        val = rng.uniform(-1, 1, nnz).astype(dt) if with_values else None
+        B = rng.uniform(-1, 1, (n_cols, dim)).astype(dt)
+        got, info = _run(mps, cuda, rp, col, val, B, cost, tune)
+        _check(orc, rp, col, val, B, got, info, cost, 1e-2 if half else 1e-5)
+
+    run()
+
+
 def test_host_buffer_call_equals_device_path(mps, orc, graphs, cuda):
     rp, col = cases.c1_rmat()
     val = graphs.gcn_values(rp, col)
