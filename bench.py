@@ -13,7 +13,8 @@ A is cut into N row slabs of equal weighted item count, B is replicated, each ra
 (weak scaling, no collective on the data path).  One step = one SpMM of the whole matrix.  The line also
 carries "check" (sampled rows of the C that the timed steps wrote, against fp64), a roofline with bounds
 that can read <= 1 (compulsory HBM bytes, measured DRAM traffic, L2 -> SM gather rate from a probe kernel),
-"e2e" through the host-buffer call, and "c5_strong": the fixed 2^24-node, degree-64 graph at dim 32 cut over
+"e2e" through the host-buffer call (at one GPU also "e2e.scaled_call": the same product with the two GCN factor vectors
+in place of a value per non-zero, as the reference program uploads it), and "c5_strong": the fixed 2^24-node, degree-64 graph at dim 32 cut over
 the same N GPUs (strong scaling).
 
 The reference has no CPU SpMM (its hot path is CUDA); the host arm that `--impl reference` times is
