@@ -151,7 +151,9 @@ typedef struct mps_plan mps_plan;
  * element type and the reference's two tuning arguments.  `cost` = merge items per chunk as in
  * the reference.  `threads_per_warp` is accepted for command-line compatibility; where the
  * reference exits when it exceeds 32/dim (:224-228) the value is clamped instead (the number of
- * chunks a warp walks at once is fixed by the 128-bit row loads: 128/dim chunks for fp32).
+ * chunks a warp walks at once is fixed by the 128-bit row loads: 128/dim chunks for fp32; fp16 rows of up to 28
+ * columns that are a multiple of 4 are read with 64-bit loads, four columns per lane, so that a warp walks at most
+ * eight units - B and C then need 8-byte alignment, otherwise 16 bytes when dim is a multiple of 4 (fp32) or 8 (fp16)).
  * Allocates the plan's device scratch on the current device. */
 MPS_API int mps_plan_create(int32_t n_rows, int32_t nnz, int32_t dim, int dtype, int32_t cost,
                     int32_t threads_per_warp, mps_plan **out);
@@ -224,7 +226,7 @@ MPS_API int mps_layout_query(int32_t n_rows, int32_t nnz, int32_t dim, int dtype
  * walks one unit - its lane groups take consecutive non-zeros, keep partial sums of the row in progress and combine
  * them with xor-shuffles in a fixed tree at every row end - so no lane idles where neighbouring units would end
  * their rows at different places.  -1: automatic.  Full-width lanes (dim a multiple of 4 fp32 / 8 fp16, fewer than 32
- * lanes per row), 64-thread blocks and unroll 8 only; elsewhere the setting is ignored.  Changes the summation order
+ * lanes per row; not the narrow fp16 rows of four columns per lane), 64-thread blocks and unroll 8 only; elsewhere the setting is ignored.  Changes the summation order
  * (still fixed and reproducible); call before mps_plan_partition. */
 MPS_API int mps_plan_set_walk(mps_plan *plan, int32_t warp_per_unit);
 

@@ -121,7 +121,7 @@ static int plan_layout(mps_plan *p) {
     if (p->block < p->gl) p->block = p->gl;
     // a warp per unit exists for full-width lanes, 64-thread blocks and batches of eight; it pays where a warp holds
     // several lane groups (see kWalkWarpMaxLanes)
-    const bool can_spread = p->vec > 1 && p->gl < 32 && p->block == 64 && (!p->user_unroll || p->unroll == 8);
+    const bool can_spread = p->vec == (p->dtype == MPS_F16 ? 8 : 4) && p->gl < 32 && p->block == 64 && (!p->user_unroll || p->unroll == 8);
     // ten gathers in flight per thread: the most that 80 registers hold (12 resident blocks); 12 and 16 lose warps
     if (!p->user_walk) p->walk = (can_spread && p->gl <= kWalkWarpMaxLanes) ? 1 : 0;
     if (!can_spread) p->walk = 0;
@@ -198,7 +198,12 @@ void mps::plan_init_shape(mps_plan *p, int n_rows, int nnz, int dim, int dtype, 
     p->tpw_effective = threads_per_warp < 1 ? 1 : (threads_per_warp > tpw_max ? tpw_max : threads_per_warp);
     chunking(n_rows, nnz, cost, &p->n_chunks, &p->ipt);
     const int full_vec = dtype == MPS_F16 ? 8 : 4;
-    if (dim % full_vec == 0) {
+    if (dtype == MPS_F16 && dim % 4 == 0 && dim <= 32 && (dim % 8 != 0 || dim / 8 < 4)) {
+        // narrow fp16 rows: four columns per lane (64-bit loads), so that a warp holds at most eight lane groups (dim 16:
+        // groups of 4 lanes as for fp32) and widths that are multiples of 4 but not of 8 need no scalar lanes
+        p->vec = 4;
+        p->gl = pow2_at_least(dim / 4 < 2 ? 2 : dim / 4);
+    } else if (dim % full_vec == 0) {
         p->vec = full_vec;
         int lanes = dim / full_vec;
         p->gl = lanes >= 32 ? 32 : pow2_at_least(lanes < 2 ? 2 : lanes);
@@ -341,7 +346,7 @@ static int spmm_launch(mps_plan *p, const int32_t *d_row_ptr, const int32_t *d_c
     if (!p || !d_row_ptr || !d_B || !d_C || (!d_col_idx && p->nnz > 0)) return fail(MPS_ERR_ARG, "mps_spmm: NULL argument");
     if (!p->partitioned) return fail(MPS_ERR_STATE, "mps_spmm: call mps_plan_partition first");
     const uintptr_t elem = p->dtype == MPS_F16 ? 2 : 4;
-    const uintptr_t need = p->vec > 1 ? 16 : elem;
+    const uintptr_t need = p->vec > 1 ? (uintptr_t)p->vec * elem : elem;  // one lane's load: 16 bytes, 8 for narrow fp16 rows
     if (((uintptr_t)d_B % need) || ((uintptr_t)d_C % need))
         return fail(MPS_ERR_ALIGN, "mps_spmm: B and C must be %d-byte aligned for dim=%d", (int)need, p->dim);
     if (((uintptr_t)d_row_ptr % 4) || ((uintptr_t)d_col_idx % 4) || ((uintptr_t)d_val % elem))

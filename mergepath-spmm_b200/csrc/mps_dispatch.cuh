@@ -65,6 +65,18 @@ static int launch_tile_gl(const mps_plan *p, const TileParams &tp, cudaStream_t 
     return fail(MPS_ERR_STATE, "no kernel for %d lanes per chunk", p->gl);
 }
 
+// Narrow rows with half the columns per lane (fp16, four columns per lane): groups of 2, 4 or 8 lanes only - wider rows
+// take the full vector.
+template <typename T, int VEC, bool SCALED>
+static int launch_tile_gl_narrow(const mps_plan *p, const TileParams &tp, cudaStream_t st) {
+    switch (p->gl) {
+        case 2: return launch_tile_u<T, VEC, 2, SCALED>(p, tp, st);
+        case 4: return launch_tile_u<T, VEC, 4, SCALED>(p, tp, st);
+        case 8: return launch_tile_u<T, VEC, 8, SCALED>(p, tp, st);
+    }
+    return fail(MPS_ERR_STATE, "no narrow-row kernel for %d lanes per chunk", p->gl);
+}
+
 // The variant with a warp per unit: one block size (64), one unroll (8).
 template <typename T, int VEC, int GL>
 static int launch_tile_warp_k(const mps_plan *p, const TileParams &tp, cudaStream_t st) {
@@ -92,7 +104,10 @@ static int spmm_typed(mps_plan *p, const TileParams &tp, cudaStream_t st) {
     const bool prof = p->profiling && p->prof_used < kProfSlots;
     if (prof) MPS_CUDA(cudaEventRecord(p->prof_ev[2 * p->prof_used], st));
     if (p->vec == 1) rc = launch_tile_b<T, 1, 32, 4, SCALED>(p, tp, st);
-    else if (p->walk && !SCALED) {
+    else if (p->vec != FULLVEC) {
+        if constexpr (FULLVEC == 8 && !SCALED) rc = launch_tile_gl_narrow<T, 4, SCALED>(p, tp, st);
+        else rc = fail(MPS_ERR_STATE, "no kernel with %d columns per lane", p->vec);
+    } else if (p->walk && !SCALED) {
         if constexpr (!SCALED) rc = launch_tile_warp<T, FULLVEC>(p, tp, st);
         else rc = MPS_ERR_STATE;
     } else rc = launch_tile_gl<T, FULLVEC, SCALED>(p, tp, st);

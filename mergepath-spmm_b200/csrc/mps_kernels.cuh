@@ -232,6 +232,28 @@ struct Lane<__half, 8> {
         __stcs(reinterpret_cast<uint4 *>(p), o);
     }
 };
+// Four fp16 columns per lane (one 64-bit load): narrow fp16 rows, where eight columns per lane would leave a warp with
+// sixteen lane groups walking sixteen units.
+template <>
+struct Lane<__half, 4> {
+    typedef uint2 raw;
+    typedef unsigned short scalar;
+    static __device__ __forceinline__ scalar value(__half v) { return __half_as_ushort(v); }
+    static __device__ __forceinline__ scalar from_float(float) { return (unsigned short)0x3C00; }  // scaled products are fp32-only
+    static __device__ __forceinline__ scalar one() { return (unsigned short)0x3C00; }
+    static __device__ __forceinline__ raw load(const __half *p) { return __ldg(reinterpret_cast<const uint2 *>(p)); }
+    static __device__ __forceinline__ void fma(float (&acc)[4], scalar a, const raw &b) {
+        fma_f32_f16x2(acc[0], acc[1], a, b.x);
+        fma_f32_f16x2(acc[2], acc[3], a, b.y);
+    }
+    static __device__ __forceinline__ void store(__half *p, const float (&v)[4]) {
+        uint2 o;
+        __half2 *h = reinterpret_cast<__half2 *>(&o);
+        h[0] = __floats2half2_rn(v[0], v[1]);
+        h[1] = __floats2half2_rn(v[2], v[3]);
+        __stcs(reinterpret_cast<uint2 *>(p), o);
+    }
+};
 template <>
 struct Lane<__half, 1> {
     typedef __half raw;

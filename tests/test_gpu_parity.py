@@ -573,7 +573,7 @@ def test_host_call_with_b_already_on_the_device(mps, graphs, cuda):
     mps.capi.lib().mps_host_workspace_release()
 
 
-@pytest.mark.parametrize("dim,half", [(16, False), (32, False), (64, False), (8, False), (12, False), (24, False), (32, True), (64, True), (128, True), (16, True)])
+@pytest.mark.parametrize("dim,half", [(16, False), (32, False), (64, False), (8, False), (12, False), (24, False), (32, True), (64, True), (128, True)])
 def test_warp_per_unit_walk_is_bit_exact_with_its_model(mps, orc, graphs, cuda, dim, half):
     """mps_plan_set_walk(1): a warp walks one unit, its 32/lanes groups take consecutive non-zeros and their partial sums
     are combined with shuffles in a fixed tree at row ends.  Power-law graph (fused and unfused fix-up), the structured
@@ -612,6 +612,11 @@ def test_warp_per_unit_walk_on_a_mid_size_graph_and_where_it_does_not_apply(mps,
         got, info = _run(mps, cuda, rp, col, val, Bx, 16, tune, walk=1)
         assert info["groups_per_unit"] == (1 if dim != 20 else info["groups_per_unit"])
         _check(orc, rp, col, val, Bx, got, info, 16, 1e-5)
+    # narrow fp16 rows (four columns per lane) have no warp-per-unit kernel either
+    Bh = graphs.dense_normal_f16(len(rp) - 1, 16, seed=6)
+    got, info = _run(mps, cuda, rp, col, val.astype(np.float16), Bh, 16, walk=1)
+    assert info["groups_per_unit"] == 1 and info["lanes_per_chunk"] == 4
+    _check(orc, rp, col, val.astype(np.float16), Bh, got, info, 16, 1e-2)
 
 
 def test_host_call_reports_a_bad_column_index_without_gathering_by_it(mps, graphs, cuda):
