@@ -320,14 +320,14 @@ def test_errors_are_codes_not_faults(mps, cuda):
 
 def test_random_matrices_bit_exact_with_the_model(mps, orc, cuda):
     """Property test: random row lengths (empty rows, a few long rows, runs of short ones), random column indices and
-    values, random dim / cost / dtype / layout knob - C is bit-equal to the CPU model of the summation order and
+    values, random dim (vector lanes, narrow fp16 lanes, scalar lanes, column slabs) / cost / dtype / layout knob - C is bit-equal to the CPU model of the summation order and
     within tolerance of the fp64 loop, whatever the shape."""
     from hypothesis import given, settings, strategies as st, HealthCheck
     lengths = st.lists(st.one_of(st.just(0), st.integers(0, 6), st.integers(0, 90), st.integers(200, 3000)), min_size=1, max_size=120)
     tunes = st.sampled_from([None, None, dict(fused_fixup=0), dict(chunks_per_unit=1), dict(unroll=4), dict(block_threads=128), dict(bulk_staging=False)])
 
     @settings(max_examples=150, deadline=None, suppress_health_check=list(HealthCheck))
-    @given(lengths, st.sampled_from([4, 16, 20, 32, 64, 128]), st.sampled_from([1, 3, 8, 16, 600]), st.booleans(), st.booleans(), tunes,
+    @given(lengths, st.sampled_from([3, 4, 6, 12, 16, 20, 30, 32, 50, 64, 100, 128]), st.sampled_from([1, 3, 8, 16, 600]), st.booleans(), st.booleans(), tunes,
            st.integers(0, 2 ** 31 - 1))
     def run(lens, dim, cost, half, with_values, tune, seed):
         rng = np.random.default_rng(seed)
